@@ -1,0 +1,387 @@
+#!/usr/bin/env python
+"""Benchmark of the attention hot path: decode attention over the q8_0 KV cache.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload (N = 1): the decode-attention context sweep -- batch 1, 32 query heads / 8 KV heads,
+head_dim 128, contexts 8K..256K, a full-causal layer and a sliding-window layer (window 4096) per
+context; fp16 Q, fp32 accumulation, fp16 output.  One *step* = one decode-attention call on every
+(context, layer) of the sweep, i.e. one pass of the hot path over the whole batch of caches.
+The metric is the KV stream rate: algorithmic KV bytes (visible keys x 2176 B) / time.
+
+    value      device-timed, inputs resident in HBM
+    e2e        the same sweep through the C ABI with HOST buffers: per call the query row, the new
+               K/V row and the position are copied from pinned host memory, the row is appended to
+               the cache, attention runs, and the output row is copied back
+    roofline   the flash-decode kernel at the longest context, timed live with CUDA event pairs
+               around each of its launches inside the timed region
+    cpu_baseline  the CPU oracle (a scalar restatement of the reference arithmetic) on a bounded
+               sample of the same sweep, on this machine's host cores
+
+With N > 1 (torchrun, one rank per GPU) every rank serves its own sequence (slots are sharded over
+GPUs, no collective on the data path): weak scaling, value = bytes of all ranks / max time.
+
+`--impl reference` times the reference arithmetic on the host cores (the reference engine is CUDA
+only and has no CPU implementation of this path; its attention math is restated in oracle/).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+CTXS = [8192, 16384, 32768, 65536, 131072, 262144]
+CPU_SAMPLE_CTXS = [8192, 16384, 32768, 65536]
+WINDOW = 4096
+POS_BYTES = 2176                      # K+V bytes per cached position per layer
+METRIC = "decode-attn HBM TB/s (ctx sweep 8K-256K, full + window-4096 layer per ctx)"
+# DRAM bytes (read + write) of one flash-decode launch at 256K from the ncu capture summarised in
+# profiles/; None until a capture exists
+NCU_TRAFFIC_256K = None
+
+
+def visible(ctx: int, is_swa: bool) -> int:
+    return min(ctx, WINDOW) if is_swa else ctx
+
+
+def step_bytes(ctxs) -> int:
+    return sum((visible(c, False) + visible(c, True)) * POS_BYTES for c in ctxs)
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+# ------------------------------------------------------------------------------------------------
+# clocks
+# ------------------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1]))
+            except Exception:
+                continue
+            for name, val in zip(self.NAMES, r[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU arm (oracle): used for cpu_baseline and for --impl reference
+# ------------------------------------------------------------------------------------------------
+def cpu_workload(ctxs):
+    """Host-side caches for the sample contexts: valid q8_0 records with random payload."""
+    from oracle import oracle as O
+    rng = np.random.default_rng(0)
+    items = []
+    for ctx in ctxs:
+        g = O.Geom(n_head=32, n_kv=8, head_dim=128, window=WINDOW, slot_ctx=ctx, n_slots=1)
+        q = rng.standard_normal((1, 1, g.n_head, g.head_dim), dtype=np.float32).astype(np.float16).astype(np.float32)
+        for is_swa in (False, True):
+            caches = []
+            for _ in range(2):
+                c = O.new_cache(g, is_swa)
+                view = O.np_cache_view(g, c, is_swa)
+                view[...] = rng.integers(0, 256, size=view.shape, dtype=np.uint8)
+                view[..., :8] = np.full(4, 0.0236, np.float16).view(np.uint8)     # ~ amax 3 / 127
+                caches.append(c)
+            items.append((g, q, caches[0], caches[1], ctx - 1, is_swa))
+    return items
+
+
+def cpu_step(items, nthreads=0):
+    from oracle import oracle as O
+    for g, q, kvk, kvv, pos, is_swa in items:
+        O.attend(g, q, kvk, kvv, [pos], rows=1, is_swa=is_swa, nthreads=nthreads)
+
+
+def cpu_baseline(budget_s: float = 10.0):
+    from oracle import oracle as O
+    items = cpu_workload(CPU_SAMPLE_CTXS)
+    cpu_step(items)                                    # warm-up
+    n, t0 = 0, time.perf_counter()
+    while True:
+        cpu_step(items)
+        n += 1
+        dt = time.perf_counter() - t0
+        if dt >= budget_s or n >= 200:
+            break
+    tbs = n * step_bytes(CPU_SAMPLE_CTXS) / dt / 1e12
+    return {"value": tbs, "unit": "TB/s", "cores": O.num_threads(), "kind": "port",
+            "sample": f"decode sweep restricted to ctx {CPU_SAMPLE_CTXS} (full + window layer), {n} passes in {dt:.1f} s, "
+                      "double-accumulating scalar C oracle, OpenMP over KV heads"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    from oracle import oracle as O
+    items = cpu_workload(CPU_SAMPLE_CTXS)
+    for _ in range(max(1, args.warmup)):
+        cpu_step(items)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_step(items)
+    dt = time.perf_counter() - t0
+    val = args.steps * step_bytes(CPU_SAMPLE_CTXS) / dt / 1e12
+    sample = (f"each step = decode sweep restricted to ctx {CPU_SAMPLE_CTXS} (full + window layer); the reference "
+              "engine is CUDA-only, so its attention arithmetic runs here as the scalar C restatement in oracle/")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": "TB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 (int8 KV, fp16 scales)",
+        "data": "synthetic",
+        "config": {"workload": "decode-attention context sweep (BASELINE config 1), CPU sample", "ctxs": CPU_SAMPLE_CTXS,
+                   "n_head": 32, "n_kv": 8, "head_dim": 128, "window": WINDOW, "batch": 1},
+        "cpu_baseline": {"value": val, "unit": "TB/s", "cores": O.num_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "TB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+# ------------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------------
+class Layer:
+    """One (context, layer kind) of the sweep: its own engine, cache, query, output and scratch."""
+
+    def __init__(self, ctx, is_swa, gen, torch, AttnEngine, G_B, device):
+        self.ctx, self.is_swa = ctx, is_swa
+        g = G_B.with_(slot_ctx=ctx, window=WINDOW)
+        self.g = g
+        self.eng = AttnEngine(g, device)
+        dev = self.eng.device
+        self.kvk, self.kvv = self.eng.alloc_kv_layer(is_swa)
+        start = max(0, ctx - 2 * WINDOW) if is_swa else 0
+        pos = torch.zeros(1, dtype=torch.int32, device=dev)
+        for a in range(start, ctx, 512):
+            n = min(512, ctx - a)
+            k = torch.randn((1, n, g.n_kv, g.head_dim), generator=gen, device=dev, dtype=torch.float32)
+            v = torch.randn((1, n, g.n_kv, g.head_dim), generator=gen, device=dev, dtype=torch.float32)
+            pos.fill_(a)
+            self.eng.qkv_prep_store(k, v, self.kvk, self.kvv, pos, rows=n, is_swa=is_swa)
+        self.pos = torch.full((1,), ctx - 1, dtype=torch.int32, device=dev)
+        self.q = torch.randn((1, 1, g.n_head, g.head_dim), generator=gen, device=dev, dtype=torch.float32).half()
+        self.out = torch.zeros((1, 1, g.n_head, g.head_dim), dtype=torch.float16, device=dev)
+        self.part = self.eng.alloc_part(1, 1)
+        # host side of the end-to-end path
+        self.h_q = self.q.cpu().pin_memory()
+        self.h_k = torch.randn((1, 1, g.n_kv, g.head_dim), dtype=torch.float32).pin_memory()
+        self.h_v = torch.randn((1, 1, g.n_kv, g.head_dim), dtype=torch.float32).pin_memory()
+        self.h_pos = torch.full((1,), ctx - 1, dtype=torch.int32).pin_memory()
+        self.h_out = torch.zeros((1, 1, g.n_head, g.head_dim), dtype=torch.float16).pin_memory()
+        self.d_k = torch.empty_like(self.h_k, device=dev)
+        self.d_v = torch.empty_like(self.h_v, device=dev)
+        self.bytes = visible(ctx, is_swa) * POS_BYTES
+
+    def decode(self):
+        self.eng.launch_attn_m(self.out, self.q, self.kvk, self.kvv, self.pos, self.part, 1, self.is_swa)
+
+    def decode_e2e(self):
+        self.q.copy_(self.h_q, non_blocking=True)
+        self.d_k.copy_(self.h_k, non_blocking=True)
+        self.d_v.copy_(self.h_v, non_blocking=True)
+        self.pos.copy_(self.h_pos, non_blocking=True)
+        self.eng.qkv_prep_store(self.d_k, self.d_v, self.kvk, self.kvv, self.pos, rows=1, is_swa=self.is_swa)
+        self.eng.launch_attn_m(self.out, self.q, self.kvk, self.kvv, self.pos, self.part, 1, self.is_swa)
+        self.h_out.copy_(self.out, non_blocking=True)
+
+    def e2e_bytes(self):
+        h2d = self.h_q.numel() * 2 + self.h_k.numel() * 4 + self.h_v.numel() * 4 + 4
+        return h2d, self.h_out.numel() * 2
+
+
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+
+    from bruce_engine_b200.engine import AttnEngine
+    from bruce_engine_b200.layout import G_B
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the attention path has no CPU implementation")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    gen = torch.Generator(device=f"cuda:{local}")
+    gen.manual_seed(1000 + rank)                   # every rank serves its own sequence
+    layers = [Layer(c, s, gen, torch, AttnEngine, G_B, local) for c in CTXS for s in (False, True)]
+    torch.cuda.synchronize()
+
+    def step():
+        for L in layers:
+            L.decode()
+
+    def step_e2e():
+        for L in layers:
+            L.decode_e2e()
+        torch.cuda.current_stream().synchronize()   # the host reads the step's outputs
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms: float) -> float:
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    K, W = args.steps, max(3, args.warmup)
+    sampler = ClockSampler(local)
+
+    # ---- device-resident timed region ----------------------------------------------------------------
+    for _ in range(W):
+        step()
+    barrier()
+    launches0 = sum(L.eng.launch_count() for L in layers)
+    for L in layers:
+        L.eng.profile_start(K)
+    if rank == 0:
+        sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record()
+    for _ in range(K):
+        step()
+    ev1.record()
+    barrier()
+    ms_local = ev0.elapsed_time(ev1)
+    clocks = sampler.stop() if rank == 0 else None
+    kernel_ms = {(L.ctx, L.is_swa): L.eng.profile_stop() for L in layers}
+    launches = sum(L.eng.launch_count() for L in layers) - launches0
+    ms = max_over_ranks(ms_local)
+
+    # ---- end-to-end timed region (host buffers, copies inside) ------------------------------------------
+    for _ in range(W):
+        step_e2e()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(K):
+        step_e2e()
+    e1.record()
+    barrier()
+    ms_e2e = max_over_ranks(e0.elapsed_time(e1))
+
+    status = sum(L.eng.device_status() for L in layers)
+    sb = step_bytes(CTXS)
+    value = world * K * sb / (ms * 1e-3) / 1e12
+    e2e_value = world * K * sb / (ms_e2e * 1e-3) / 1e12
+    h2d = sum(L.e2e_bytes()[0] for L in layers)
+    d2h = sum(L.e2e_bytes()[1] for L in layers)
+
+    peak, peak_kind = measured_peak()
+    sweep = []
+    for c in CTXS:
+        tf = statistics.mean(kernel_ms[(c, False)]) * 1e-3
+        ts = statistics.mean(kernel_ms[(c, True)]) * 1e-3
+        sweep.append({"ctx": c, "full_us": tf * 1e6, "full_TBps": c * POS_BYTES / tf / 1e12,
+                      "full_frac_of_peak": c * POS_BYTES / tf / 1e9 / peak,
+                      "swa_us": ts * 1e6, "swa_TBps": visible(c, True) * POS_BYTES / ts / 1e12,
+                      "attn_tok_per_s_layer_pair": 1.0 / (tf + ts)})
+    top = CTXS[-1]
+    t_top = statistics.mean(kernel_ms[(top, False)]) * 1e-3
+    alg_bytes = top * POS_BYTES + 2 * 32 * 128 * 2
+    achieved = alg_bytes / t_top / 1e9
+    roofline = {"bound": "hbm", "kernel": "k_flash_decode<128,1> @ ctx 262144, full layer", "achieved": achieved,
+                "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": achieved / peak,
+                "frac_of_nominal_8TBps": achieved / 8000.0, "launch_us": t_top * 1e6,
+                "algorithmic_bytes_per_launch": alg_bytes, "traffic": NCU_TRAFFIC_256K}
+
+    if rank == 0:
+        cpu = cpu_baseline() if world == 1 else None
+        line = {
+            "metric": METRIC, "value": value, "unit": "TB/s", "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32 (int8 KV, fp16 scales, fp16 MMA operands, fp32 accumulate)", "data": "synthetic",
+            "config": {"workload": "decode-attention context sweep (BASELINE config 1)", "ctxs": CTXS, "n_head": 32,
+                       "n_kv": 8, "head_dim": 128, "window": WINDOW, "batch": 1, "q_dtype": "f16", "out_dtype": "f16",
+                       "parallelism": f"one sequence per GPU x{world}" if world > 1 else "1 GPU",
+                       "l2": "each (context, layer) has its own cache; 1.18 GB are streamed between two reads of "
+                             "the same buffer (inputs larger than L2)",
+                       "launch": "eager launches through the C ABI"},
+            "e2e": {"value": e2e_value, "unit": "TB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": ms_e2e / K},
+            "gpu_launches": launches, "roofline": roofline, "sweep": sweep, "clocks": clocks,
+            "device_status": status,
+        }
+        if cpu is not None:
+            line["cpu_baseline"] = cpu
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+    return run_gpu(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

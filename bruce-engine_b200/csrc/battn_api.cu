@@ -1,0 +1,373 @@
+// C ABI of the attention library (see include/battn.h): argument checks, launch geometry, dispatch.
+// No allocation, synchronisation or host read of device state happens inside the per-step entry
+// points, so they can be recorded into CUDA graphs like the reference's launches
+// (engine/src/bruce.cu:7877-7900, 8046-8055).
+#include <new>
+
+#include "common.cuh"
+#include "exact.cuh"
+#include "flash_decode.cuh"
+#include "kv_append.cuh"
+
+using namespace battn;
+
+namespace {
+
+constexpr size_t SMEM_MAX = 227 * 1024;     // opt-in dynamic shared memory per CTA on sm_100
+constexpr int FD_MAX_CTAS_PER_SM = 4;
+
+inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+inline int cuda_fail(battn_handle* h, cudaError_t e) {
+    h->last_cuda_error = (int)e;
+    return BATTN_ERR_CUDA;
+}
+
+inline int nt_index(int RG) { return RG <= 8 ? 0 : (RG <= 16 ? 1 : 2); }
+
+template <int HD, int NT>
+cudaError_t fd_prepare(battn_handle* h, int idx) {
+    auto kern = fd::k_flash_decode<HD, NT>;
+    cudaError_t e = cudaFuncSetAttribute((const void*)kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX);
+    if (e != cudaSuccess) return e;
+    int nb = 0;
+    const size_t sm = fd::smem_bytes<HD, NT>(NT * 8, 1);
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, (const void*)kern, fd::NTHREADS, sm);
+    if (e != cudaSuccess) return e;
+    h->fd_ctas_per_sm[idx] = nb < 1 ? 1 : (nb > FD_MAX_CTAS_PER_SM ? FD_MAX_CTAS_PER_SM : nb);
+    h->fd_smem[idx] = (int)sm;
+    return cudaSuccess;
+}
+
+template <int HD>
+cudaError_t fd_prepare_all(battn_handle* h) {
+    cudaError_t e;
+    if ((e = fd_prepare<HD, 1>(h, 0)) != cudaSuccess) return e;
+    if ((e = fd_prepare<HD, 2>(h, 1)) != cudaSuccess) return e;
+    if ((e = fd_prepare<HD, 4>(h, 2)) != cudaSuccess) return e;
+    return cudaSuccess;
+}
+
+// workspace of the flash-decode path: header + one record slot per (CTA + item)
+struct FdWs {
+    size_t hdr_bytes, rec_bytes, total;
+    int max_ctas;
+};
+inline FdWs fd_workspace(const battn_handle* h, int n_seq, int rows) {
+    const Geom& g = h->g;
+    FdWs w;
+    w.max_ctas = h->num_sms * FD_MAX_CTAS_PER_SM;
+    w.hdr_bytes = align_up((size_t)(n_seq + 3) * sizeof(int), 256);
+    w.rec_bytes = (size_t)(w.max_ctas + (size_t)n_seq * g.Hkv) * rows * g.G * (g.HD + 2) * sizeof(float);
+    w.total = w.hdr_bytes + w.rec_bytes;
+    return w;
+}
+
+inline int exact_default_splits(int rows) { return rows > 64 ? 2 : (rows > 8 ? 8 : 32); }
+
+inline size_t exact_workspace(const battn_handle* h, int n_seq, int rows, int nsplit) {
+    const Geom& g = h->g;
+    return (size_t)n_seq * rows * g.Hq * nsplit * (g.HD + 2) * sizeof(float);
+}
+
+int check_seq_args(const battn_handle* h, const void* a, const void* b, const void* c, const void* d,
+                   const int* pos, const int* kslot, int n_seq, int rows, int max_rows) {
+    if (!h || !a || !b || !c || !d || !pos) return BATTN_ERR_ARG;
+    if (n_seq < 1 || rows < 1) return BATTN_ERR_ARG;
+    if (!kslot && n_seq != 1) return BATTN_ERR_ARG;
+    if (n_seq > MAX_SEQ || rows > max_rows) return BATTN_ERR_CAPACITY;
+    return BATTN_OK;
+}
+
+// event pair around the main kernel of a call while profiling is on
+struct ProfScope {
+    battn_handle* h; cudaStream_t st; int idx;
+    ProfScope(battn_handle* h_, cudaStream_t st_) : h(h_), st(st_), idx(-1) {
+        if (h->prof_ev && h->prof_n < h->prof_cap) { idx = h->prof_n++; cudaEventRecord(h->prof_ev[2 * idx], st); }
+    }
+    ~ProfScope() { if (idx >= 0) cudaEventRecord(h->prof_ev[2 * idx + 1], st); }
+};
+
+int launch_exact(battn_handle* h, void* out, float* rec_out, const void* q, const uint8_t* kvk, const uint8_t* kvv,
+                 const int* pos, const int* kslot, const int* act, void* ws, int n_seq, int rows, int nsplit,
+                 int is_swa, cudaStream_t st) {
+    const Geom& g = h->g;
+    ExactParams P;
+    P.q = q; P.kvk = kvk; P.kvv = kvv; P.pos = pos; P.kslot = kslot; P.act = act;
+    P.part = reinterpret_cast<float*>(ws);
+    P.n_seq = n_seq; P.rows = rows; P.Hq = g.Hq; P.Hkv = g.Hkv; P.G = g.G;
+    P.W = g.W; P.pstride = is_swa ? g.ring : g.slot_ctx; P.ring_mask = is_swa ? g.ring - 1 : -1;
+    P.slot_ctx = g.slot_ctx; P.n_slots = g.n_slots; P.is_swa = is_swa; P.q_f16 = g.q_f16;
+    P.scale = g.scale; P.status = h->d_status;
+    const dim3 grid(n_seq * g.Hkv, nsplit, rows), block(32 * g.G);
+    {
+        ProfScope prof(h, st);
+        if (g.HD == 128) k_attn_exact<128><<<grid, block, 0, st>>>(P);
+        else             k_attn_exact<256><<<grid, block, 0, st>>>(P);
+    }
+    MergeParams M{};
+    M.mode = MERGE_REGULAR; M.part = P.part; M.out = out; M.rec_out = rec_out;
+    M.n_rows = n_seq * rows; M.rows = rows; M.Hq = g.Hq; M.Hkv = g.Hkv; M.G = g.G;
+    M.count = nsplit; M.log2_domain = 0; M.out_f16 = g.out_f16;
+    M.pos = pos; M.kslot = kslot; M.act = act; M.is_swa = is_swa; M.W = g.W; M.slot_ctx = g.slot_ctx;
+    M.n_slots = g.n_slots; M.status = h->d_status; M.hdr = nullptr;
+    if (g.HD == 128) k_merge<128><<<n_seq * rows * g.Hq, 64, 0, st>>>(M);
+    else             k_merge<256><<<n_seq * rows * g.Hq, 128, 0, st>>>(M);
+    h->launches += 2;
+    const cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? BATTN_OK : cuda_fail(h, e);
+}
+
+template <int HD, int NT>
+cudaError_t launch_fd_kernel(const fd::Params& P, int grid, size_t smem, cudaStream_t st) {
+    fd::k_flash_decode<HD, NT><<<grid, fd::NTHREADS, smem, st>>>(P);
+    return cudaGetLastError();
+}
+
+// decode / verify / multi-slot decode through the flash-decode kernel and the balanced merge
+int launch_flash(battn_handle* h, void* out, float* rec_out, const void* q, const uint8_t* kvk, const uint8_t* kvv,
+                 const int* pos, const int* kslot, const int* act, void* ws, int n_seq, int rows, int is_swa,
+                 cudaStream_t st) {
+    const Geom& g = h->g;
+    const int RG = rows * g.G;
+    if (RG > 32) return BATTN_ERR_CAPACITY;
+    const int idx = nt_index(RG);
+    const FdWs w = fd_workspace(h, n_seq, rows);
+    fd::Params P;
+    P.q = q; P.kvk = kvk; P.kvv = kvv; P.pos = pos; P.kslot = kslot; P.act = act;
+    P.hdr = reinterpret_cast<int*>(ws);
+    P.part = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(ws) + w.hdr_bytes);
+    P.n_seq = n_seq; P.rows = rows; P.Hq = g.Hq; P.Hkv = g.Hkv; P.G = g.G; P.RG = RG;
+    P.W = g.W; P.pstride = is_swa ? g.ring : g.slot_ctx; P.ring_mask = is_swa ? g.ring - 1 : -1;
+    P.slot_ctx = g.slot_ctx; P.n_slots = g.n_slots; P.is_swa = is_swa; P.q_f16 = g.q_f16;
+    P.scale_log2 = g.scale * LOG2E; P.status = h->d_status;
+
+    size_t smem;
+    if (g.HD == 128) smem = idx == 0 ? fd::smem_bytes<128, 1>(RG, n_seq) : idx == 1 ? fd::smem_bytes<128, 2>(RG, n_seq) : fd::smem_bytes<128, 4>(RG, n_seq);
+    else             smem = idx == 0 ? fd::smem_bytes<256, 1>(RG, n_seq) : idx == 1 ? fd::smem_bytes<256, 2>(RG, n_seq) : fd::smem_bytes<256, 4>(RG, n_seq);
+    if (smem > SMEM_MAX) return BATTN_ERR_CAPACITY;
+    int per_sm = (int)(SMEM_MAX / (smem + 1024));
+    if (per_sm > h->fd_ctas_per_sm[idx]) per_sm = h->fd_ctas_per_sm[idx];
+    if (per_sm < 1) per_sm = 1;
+    const int grid = h->num_sms * per_sm;
+
+    cudaError_t e;
+    {
+    ProfScope prof(h, st);
+    if (g.HD == 128) e = idx == 0 ? launch_fd_kernel<128, 1>(P, grid, smem, st) : idx == 1 ? launch_fd_kernel<128, 2>(P, grid, smem, st) : launch_fd_kernel<128, 4>(P, grid, smem, st);
+    else             e = idx == 0 ? launch_fd_kernel<256, 1>(P, grid, smem, st) : idx == 1 ? launch_fd_kernel<256, 2>(P, grid, smem, st) : launch_fd_kernel<256, 4>(P, grid, smem, st);
+    }
+    if (e != cudaSuccess) return cuda_fail(h, e);
+
+    MergeParams M{};
+    M.mode = MERGE_BALANCED; M.part = P.part; M.out = out; M.rec_out = rec_out;
+    M.n_rows = n_seq * rows; M.rows = rows; M.Hq = g.Hq; M.Hkv = g.Hkv; M.G = g.G;
+    M.count = 0; M.log2_domain = 1; M.out_f16 = g.out_f16; M.hdr = P.hdr; M.status = h->d_status;
+    if (g.HD == 128) k_merge<128><<<n_seq * rows * g.Hq, 64, 0, st>>>(M);
+    else             k_merge<256><<<n_seq * rows * g.Hq, 128, 0, st>>>(M);
+    h->launches += 2;
+    e = cudaGetLastError();
+    return e == cudaSuccess ? BATTN_OK : cuda_fail(h, e);
+}
+
+}  // namespace
+
+extern "C" {
+
+int battn_version(void) { return BATTN_VERSION; }
+
+int battn_init(const battn_geom* geom, int device, battn_handle** out_handle) {
+    if (!geom || !out_handle) return BATTN_ERR_ARG;
+    *out_handle = nullptr;
+    if (geom->head_dim != 128 && geom->head_dim != 256) return BATTN_ERR_ARG;
+    if (geom->n_head < 1 || geom->n_kv < 1 || geom->n_head % geom->n_kv) return BATTN_ERR_ARG;
+    const int G = geom->n_head / geom->n_kv;
+    if (G > 8) return BATTN_ERR_ARG;
+    if (geom->window < 32 || (geom->window & (geom->window - 1))) return BATTN_ERR_ARG;
+    if (geom->slot_ctx < 2 || (geom->slot_ctx & 1) || geom->n_slots < 1) return BATTN_ERR_ARG;
+    if ((geom->q_dtype != BATTN_F32 && geom->q_dtype != BATTN_F16) ||
+        (geom->out_dtype != BATTN_F32 && geom->out_dtype != BATTN_F16)) return BATTN_ERR_ARG;
+
+    battn_handle* h = new (std::nothrow) battn_handle();
+    if (!h) return BATTN_ERR_ARG;
+    Geom& g = h->g;
+    g.Hq = geom->n_head; g.Hkv = geom->n_kv; g.HD = geom->head_dim; g.G = G;
+    g.W = geom->window; g.ring = 2 * geom->window;
+    g.slot_ctx = geom->slot_ctx; g.n_slots = geom->n_slots;
+    g.nblk = g.HD / 32; g.rec = g.HD + 2 * g.nblk;
+    g.q_f16 = geom->q_dtype == BATTN_F16; g.out_f16 = geom->out_dtype == BATTN_F16;
+    g.scale = geom->softmax_scale != 0.f ? geom->softmax_scale : 1.f / sqrtf((float)g.HD);
+    h->device = device; h->last_cuda_error = 0; h->launches = 0; h->d_status = nullptr;
+    h->prof_ev = nullptr; h->prof_cap = 0; h->prof_n = 0;
+
+    cudaError_t e = cudaSetDevice(device);
+    cudaDeviceProp prop;
+    if (e == cudaSuccess) e = cudaGetDeviceProperties(&prop, device);
+    if (e == cudaSuccess && prop.major < 10) e = cudaErrorInvalidDevice;      // sm_100a only
+    if (e == cudaSuccess) { h->num_sms = prop.multiProcessorCount; e = cudaMalloc(&h->d_status, 16); }
+    if (e == cudaSuccess) e = cudaMemset(h->d_status, 0, 16);
+    if (e == cudaSuccess) e = g.HD == 128 ? fd_prepare_all<128>(h) : fd_prepare_all<256>(h);
+    if (e != cudaSuccess) {
+        if (h->d_status) cudaFree(h->d_status);
+        delete h;
+        return BATTN_ERR_CUDA;
+    }
+    *out_handle = h;
+    return BATTN_OK;
+}
+
+int battn_destroy(battn_handle* h) {
+    if (!h) return BATTN_ERR_ARG;
+    cudaSetDevice(h->device);
+    if (h->prof_ev) { int n = 0; battn_profile_stop(h, nullptr, 0, &n); }
+    if (h->d_status) cudaFree(h->d_status);
+    delete h;
+    return BATTN_OK;
+}
+
+int battn_kv_layer_bytes(const battn_handle* h, int is_swa, size_t* out_bytes) {
+    if (!h || !out_bytes) return BATTN_ERR_ARG;
+    const Geom& g = h->g;
+    *out_bytes = (size_t)g.n_slots * (is_swa ? g.ring : g.slot_ctx) * g.Hkv * g.rec;   // bruce.cu:5476-5481
+    return BATTN_OK;
+}
+
+int battn_workspace_bytes(const battn_handle* h, int n_seq, int rows_per_seq, size_t* out_bytes) {
+    if (!h || !out_bytes || n_seq < 1 || rows_per_seq < 1) return BATTN_ERR_ARG;
+    if (n_seq > MAX_SEQ || rows_per_seq > MAX_PREFILL) return BATTN_ERR_CAPACITY;
+    size_t need = exact_workspace(h, n_seq, rows_per_seq, exact_default_splits(rows_per_seq));
+    if (rows_per_seq * h->g.G <= 32) {
+        const size_t f = fd_workspace(h, n_seq, rows_per_seq).total;
+        if (f > need) need = f;
+    }
+    *out_bytes = align_up(need, 256);
+    return BATTN_OK;
+}
+
+int battn_exact_workspace_bytes(const battn_handle* h, int n_seq, int rows_per_seq, int nsplit, size_t* out_bytes) {
+    if (!h || !out_bytes || n_seq < 1 || rows_per_seq < 1 || nsplit < 1 || nsplit > MAX_SPLITS) return BATTN_ERR_ARG;
+    *out_bytes = align_up(exact_workspace(h, n_seq, rows_per_seq, nsplit), 256);
+    return BATTN_OK;
+}
+
+int battn_kv_append(battn_handle* h, const float* k, const float* v, uint8_t* kvk, uint8_t* kvv, const int* pos,
+                    const int* kslot, const int* act, int n_seq, int rows_per_seq, int is_swa, void* stream) {
+    const int rc = check_seq_args(h, k, v, kvk, kvv, pos, kslot, n_seq, rows_per_seq, MAX_PREFILL);
+    if (rc) return rc;
+    const Geom& g = h->g;
+    AppendParams P;
+    P.k = k; P.v = v; P.kvk = kvk; P.kvv = kvv; P.pos = pos; P.kslot = kslot; P.act = act;
+    P.n_seq = n_seq; P.rows = rows_per_seq; P.Hkv = g.Hkv;
+    P.pstride = is_swa ? g.ring : g.slot_ctx; P.ring_mask = is_swa ? g.ring - 1 : -1;
+    P.n_slots = g.n_slots; P.status = h->d_status;
+    const long long warps = (long long)n_seq * rows_per_seq * g.Hkv * 2;
+    const int blocks = (int)((warps + 7) / 8);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (g.HD == 128) k_kv_append<128><<<blocks, 256, 0, st>>>(P);
+    else             k_kv_append<256><<<blocks, 256, 0, st>>>(P);
+    h->launches += 1;
+    const cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? BATTN_OK : cuda_fail(h, e);
+}
+
+int battn_decode(battn_handle* h, void* out, const void* q, const uint8_t* kvk, const uint8_t* kvv, const int* pos,
+                 const int* kslot, const int* act, void* ws, int n_seq, int is_swa, void* stream) {
+    const int rc = check_seq_args(h, out, q, kvk, kvv, pos, kslot, n_seq, 1, 1);
+    if (rc) return rc;
+    if (!ws) return BATTN_ERR_ARG;
+    return launch_flash(h, out, nullptr, q, kvk, kvv, pos, kslot, act, ws, n_seq, 1, is_swa, (cudaStream_t)stream);
+}
+
+int battn_verify(battn_handle* h, void* out, const void* q, const uint8_t* kvk, const uint8_t* kvv, const int* pos,
+                 const int* kslot, const int* act, void* ws, int rows, int batch, int is_swa, void* stream) {
+    const int rc = check_seq_args(h, out, q, kvk, kvv, pos, kslot, batch, rows, MAX_VERIFY);
+    if (rc) return rc;
+    if (!ws) return BATTN_ERR_ARG;
+    return launch_flash(h, out, nullptr, q, kvk, kvv, pos, kslot, act, ws, batch, rows, is_swa, (cudaStream_t)stream);
+}
+
+int battn_partials(battn_handle* h, float* rec, const void* q, const uint8_t* kvk, const uint8_t* kvv,
+                   const int* pos, const int* kslot, const int* act, void* ws, int rows, int batch, int is_swa,
+                   void* stream) {
+    const int rc = check_seq_args(h, rec, q, kvk, kvv, pos, kslot, batch, rows, MAX_VERIFY);
+    if (rc) return rc;
+    if (!ws) return BATTN_ERR_ARG;
+    return launch_flash(h, nullptr, rec, q, kvk, kvv, pos, kslot, act, ws, batch, rows, is_swa, (cudaStream_t)stream);
+}
+
+int battn_prefill(battn_handle* h, void* out, const void* q, const uint8_t* kvk, const uint8_t* kvv, const int* pos,
+                  void* ws, int rows, int is_swa, void* stream) {
+    const int rc = check_seq_args(h, out, q, kvk, kvv, pos, nullptr, 1, rows, MAX_PREFILL);
+    if (rc) return rc;
+    if (!ws) return BATTN_ERR_ARG;
+    return launch_exact(h, out, nullptr, q, kvk, kvv, pos, nullptr, nullptr, ws, 1, rows, exact_default_splits(rows),
+                        is_swa, (cudaStream_t)stream);
+}
+
+int battn_attend_exact(battn_handle* h, void* out, const void* q, const uint8_t* kvk, const uint8_t* kvv,
+                       const int* pos, const int* kslot, const int* act, void* ws, int n_seq, int rows_per_seq,
+                       int nsplit, int is_swa, void* stream) {
+    const int rc = check_seq_args(h, out, q, kvk, kvv, pos, kslot, n_seq, rows_per_seq, MAX_PREFILL);
+    if (rc) return rc;
+    if (!ws || nsplit < 1 || nsplit > MAX_SPLITS) return BATTN_ERR_ARG;
+    return launch_exact(h, out, nullptr, q, kvk, kvv, pos, kslot, act, ws, n_seq, rows_per_seq, nsplit, is_swa,
+                        (cudaStream_t)stream);
+}
+
+int battn_merge(battn_handle* h, void* out, const float* parts, int n_parts, int n_rows, void* stream) {
+    if (!h || !out || !parts || n_parts < 1 || n_rows < 1) return BATTN_ERR_ARG;
+    const Geom& g = h->g;
+    MergeParams M{};
+    M.mode = MERGE_GATHERED; M.part = parts; M.out = out; M.rec_out = nullptr;
+    M.n_rows = n_rows; M.rows = 1; M.Hq = g.Hq; M.Hkv = g.Hkv; M.G = g.G;
+    M.count = n_parts; M.log2_domain = 0; M.out_f16 = g.out_f16; M.status = h->d_status;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (g.HD == 128) k_merge<128><<<n_rows * g.Hq, 64, 0, st>>>(M);
+    else             k_merge<256><<<n_rows * g.Hq, 128, 0, st>>>(M);
+    h->launches += 1;
+    const cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? BATTN_OK : cuda_fail(h, e);
+}
+
+int battn_device_status(battn_handle* h, int* out_bits, int clear) {
+    if (!h || !out_bits) return BATTN_ERR_ARG;
+    cudaError_t e = cudaMemcpy(out_bits, h->d_status, sizeof(int), cudaMemcpyDeviceToHost);
+    if (e == cudaSuccess && clear) e = cudaMemset(h->d_status, 0, sizeof(int));
+    return e == cudaSuccess ? BATTN_OK : cuda_fail(h, e);
+}
+
+int battn_profile_start(battn_handle* h, int max_launches) {
+    if (!h || max_launches < 1 || h->prof_ev) return BATTN_ERR_ARG;
+    cudaEvent_t* ev = new (std::nothrow) cudaEvent_t[2 * (size_t)max_launches];
+    if (!ev) return BATTN_ERR_ARG;
+    for (int i = 0; i < 2 * max_launches; ++i) {
+        const cudaError_t e = cudaEventCreate(&ev[i]);
+        if (e != cudaSuccess) {
+            for (int j = 0; j < i; ++j) cudaEventDestroy(ev[j]);
+            delete[] ev;
+            return cuda_fail(h, e);
+        }
+    }
+    h->prof_ev = ev; h->prof_cap = max_launches; h->prof_n = 0;
+    return BATTN_OK;
+}
+
+int battn_profile_stop(battn_handle* h, float* ms_out, int cap, int* n_out) {
+    if (!h || !h->prof_ev || !n_out) return BATTN_ERR_ARG;
+    cudaError_t e = cudaSuccess;
+    const int n = h->prof_n;
+    if (n > 0) e = cudaEventSynchronize(h->prof_ev[2 * n - 1]);
+    for (int i = 0; i < n && i < cap && ms_out && e == cudaSuccess; ++i)
+        e = cudaEventElapsedTime(&ms_out[i], h->prof_ev[2 * i], h->prof_ev[2 * i + 1]);
+    for (int i = 0; i < 2 * h->prof_cap; ++i) cudaEventDestroy(h->prof_ev[i]);
+    delete[] h->prof_ev;
+    h->prof_ev = nullptr; h->prof_cap = 0; h->prof_n = 0;
+    *n_out = n;
+    return e == cudaSuccess ? BATTN_OK : cuda_fail(h, e);
+}
+
+int battn_last_cuda_error(const battn_handle* h) { return h ? h->last_cuda_error : 0; }
+
+long long battn_launch_count(const battn_handle* h) { return h ? h->launches : 0; }
+
+}  // extern "C"

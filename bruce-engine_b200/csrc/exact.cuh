@@ -1,0 +1,188 @@
+// The exact fp32 attention path and the log-sum-exp merge.
+//
+// k_attn_exact restates, for run-time geometry, what k_attn / k_attn_rows / k_attn_m compute
+// (engine/src/bruce.cu:713-785, 1921-1997, 2087-2143): per-key online softmax in fp32, one warp per
+// query head, the reference's key-split rule (:724-729) and its split record (o[HD], m, l).
+// It is the slow, tensor-core-free path used to validate the fast kernels at sizes the CPU oracle
+// cannot reach, and the reference's own "--prefill-tc 0" behaviour.
+//
+// k_merge is the merge of k_attn_combine / k_attn_combine_rows (bruce.cu:992-1007, 1999-2016) for
+// three record layouts: the reference's regular [row][kvh][split][head] layout, the layout of
+// records gathered from several devices, and the work-balanced layout of the flash-decode kernel.
+#pragma once
+#include "common.cuh"
+
+namespace battn {
+
+struct ExactParams {
+    const void* q;
+    const uint8_t* kvk;
+    const uint8_t* kvv;
+    const int* pos;
+    const int* kslot;
+    const int* act;
+    float* part;          // [(seq*rows + r)][kvh][split][head-in-group][HD+2]
+    int n_seq, rows, Hq, Hkv, G;
+    int W, pstride, ring_mask, slot_ctx, n_slots, is_swa;
+    int q_f16;
+    float scale;
+    int* status;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(256) k_attn_exact(const ExactParams P) {
+    constexpr int NBLK = HD / 32, REC = HD + 2 * NBLK, DPL = HD / 32;   // dims per lane
+    const int item = blockIdx.x, i = item / P.Hkv, kvh = item % P.Hkv;
+    const int split = blockIdx.y, ns = gridDim.y, r = blockIdx.z;
+    const int h = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const SeqRange sr = seq_range(P.pos, P.kslot, P.act, i, P.rows, P.is_swa, P.W, P.slot_ctx, P.n_slots, P.status);
+    if (!sr.active) return;
+
+    const int p = sr.p0 + r, kend = p + 1;
+    const int kstart = P.is_swa ? max(0, kend - P.W) : 0;
+    const int nkeys = kend - kstart, per = (nkeys + ns - 1) / ns;      // bruce.cu:727-729
+    const int a0 = kstart + split * per, a1 = min(kend, a0 + per);
+
+    const size_t rowidx = (size_t)i * P.rows + r;
+    const int hq = kvh * P.G + h;
+    float qv[DPL];
+#pragma unroll
+    for (int j = 0; j < DPL; ++j) {
+        const size_t qi = (rowidx * P.Hq + hq) * HD + lane * DPL + j;
+        qv[j] = P.q_f16 ? __half2float(reinterpret_cast<const __half*>(P.q)[qi])
+                        : reinterpret_cast<const float*>(P.q)[qi];
+    }
+    const int blk = (lane * DPL) >> 5;
+    const size_t hb = ((size_t)sr.slot * P.Hkv + kvh) * P.pstride * (size_t)REC;
+    const uint8_t* kb = P.kvk + hb;
+    const uint8_t* vb = P.kvv + hb;
+    const int off = 2 * NBLK + lane * DPL;
+
+    float m = NEG_BIG, l = 0.f, o[DPL];
+#pragma unroll
+    for (int j = 0; j < DPL; ++j) o[j] = 0.f;
+
+    for (int key = a0; key < a1; ++key) {
+        const size_t ro = (size_t)(key & P.ring_mask) * REC;           // ring slot (bruce.cu:740)
+        const uint8_t* kk = kb + ro;
+        const uint8_t* vv = vb + ro;
+        const float d = __half2float(reinterpret_cast<const __half*>(kk)[blk]);
+        const float dv = __half2float(reinterpret_cast<const __half*>(vv)[blk]);
+        uint32_t kw[DPL / 4], vw[DPL / 4];
+        if (DPL == 4) {
+            kw[0] = *reinterpret_cast<const uint32_t*>(kk + off);
+            vw[0] = *reinterpret_cast<const uint32_t*>(vv + off);
+        } else {
+            const uint2 a = *reinterpret_cast<const uint2*>(kk + off);
+            const uint2 b = *reinterpret_cast<const uint2*>(vv + off);
+            kw[0] = a.x; kw[DPL / 4 - 1] = a.y;
+            vw[0] = b.x; vw[DPL / 4 - 1] = b.y;
+        }
+        float kq[DPL], vq[DPL];
+#pragma unroll
+        for (int j = 0; j < DPL; ++j) {
+            kq[j] = (float)(int)(int8_t)((kw[j >> 2] >> (8 * (j & 3))) & 0xffu);   // bruce.cu:748
+            vq[j] = (float)(int)(int8_t)((vw[j >> 2] >> (8 * (j & 3))) & 0xffu);
+        }
+        float dot = 0.f;
+#pragma unroll
+        for (int j = 0; j < DPL; ++j) dot = fmaf(qv[j], d * kq[j], dot);   // bruce.cu:749
+#pragma unroll
+        for (int s = 16; s > 0; s >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, s);
+        dot *= P.scale;
+        const float mnew = fmaxf(m, dot);
+        const float pw = __expf(dot - mnew), corr = __expf(m - mnew);   // bruce.cu:757-761
+        l = l * corr + pw;
+        m = mnew;
+#pragma unroll
+        for (int j = 0; j < DPL; ++j) o[j] = fmaf(o[j], corr, pw * dv * vq[j]);   // :769
+    }
+    float* base = P.part + ((((rowidx * P.Hkv + kvh) * ns + split) * P.G + h) * (size_t)(HD + 2));
+#pragma unroll
+    for (int j = 0; j < DPL; ++j) base[lane * DPL + j] = o[j];
+    if (lane == 0) { base[HD] = m; base[HD + 1] = l; }                 // bruce.cu:781-783
+}
+
+// ------------------------------------------------------------------------------------------------
+
+enum { MERGE_REGULAR = 0, MERGE_GATHERED = 1, MERGE_BALANCED = 2 };
+
+struct MergeParams {
+    int mode;
+    const float* part;     // records
+    void* out;             // normalised output (out_f16 ? half : float), or null
+    float* rec_out;        // merged record [row][head][HD+2] in natural-log units, or null
+    int n_rows;            // total rows = n_seq * rows
+    int rows;              // rows per sequence
+    int Hq, Hkv, G;
+    int count;             // REGULAR: splits; GATHERED: parts
+    int log2_domain;       // records carry m in log2 units (flash-decode partials)
+    int out_f16;
+    // REGULAR only: skip rows of inactive sequences
+    const int* pos; const int* kslot; const int* act;
+    int is_swa, W, slot_ctx, n_slots;
+    int* status;
+    // BALANCED only: header written by the flash-decode kernel: {tiles_per_cta, total, cum[n_seq+1]}
+    const int* hdr;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(HD / 2) k_merge(const MergeParams P) {
+    const int hq = blockIdx.x % P.Hq, rowidx = blockIdx.x / P.Hq;
+    const int i = rowidx / P.rows, r = rowidx % P.rows;
+    const int kvh = hq / P.G, h = hq % P.G;
+    const int d2 = threadIdx.x * 2;
+    const float* base;
+    size_t stride;
+    int count;
+    if (P.mode == MERGE_REGULAR) {
+        const SeqRange sr = seq_range(P.pos, P.kslot, P.act, i, P.rows, P.is_swa, P.W, P.slot_ctx, P.n_slots, P.status);
+        if (!sr.active) return;
+        count = P.count;
+        base = P.part + (((size_t)rowidx * P.Hkv + kvh) * count * P.G + h) * (size_t)(HD + 2);
+        stride = (size_t)P.G * (HD + 2);
+    } else if (P.mode == MERGE_GATHERED) {
+        count = P.count;
+        base = P.part + ((size_t)rowidx * P.Hq + hq) * (size_t)(HD + 2);
+        stride = (size_t)P.n_rows * P.Hq * (HD + 2);
+    } else {
+        const int per = P.hdr[0];
+        const int c0 = P.hdr[2 + i], c1 = P.hdr[3 + i];
+        const int nt = c1 - c0;
+        if (nt <= 0) return;                                            // inactive sequence
+        const int item = i * P.Hkv + kvh;
+        const long long t0 = (long long)P.Hkv * c0 + (long long)kvh * nt, t1 = t0 + nt;
+        const int clo = (int)(t0 / per), chi = (int)((t1 - 1) / per);
+        const int RG = P.rows * P.G;
+        count = chi - clo + 1;
+        base = P.part + ((size_t)(clo + item) * RG + r * P.G + h) * (size_t)(HD + 2);
+        stride = (size_t)RG * (HD + 2);
+    }
+    float M = NEG_BIG;
+    for (int s = 0; s < count; ++s) M = fmaxf(M, base[s * stride + HD]);
+    float L = 0.f, a0 = 0.f, a1 = 0.f;
+    for (int s = 0; s < count; ++s) {
+        const float* b = base + s * stride;
+        const float w = P.log2_domain ? fast_exp2(b[HD] - M) : __expf(b[HD] - M);   // bruce.cu:1000
+        L = fmaf(b[HD + 1], w, L);
+        const float2 o = *reinterpret_cast<const float2*>(b + d2);
+        a0 = fmaf(o.x, w, a0);
+        a1 = fmaf(o.y, w, a1);
+    }
+    if (P.out) {
+        const float il = L > 0.f ? 1.f / L : 0.f;
+        const size_t oi = ((size_t)rowidx * P.Hq + hq) * HD + d2;
+        if (P.out_f16) reinterpret_cast<__half2*>(P.out)[oi >> 1] = __floats2half2_rn(a0 * il, a1 * il);
+        else *reinterpret_cast<float2*>(reinterpret_cast<float*>(P.out) + oi) = make_float2(a0 * il, a1 * il);
+    }
+    if (P.rec_out) {
+        float* ro = P.rec_out + ((size_t)rowidx * P.Hq + hq) * (size_t)(HD + 2);
+        *reinterpret_cast<float2*>(ro + d2) = make_float2(a0, a1);
+        if (threadIdx.x == 0) {
+            ro[HD] = (P.log2_domain && M > -1e29f) ? M * LN2 : M;
+            ro[HD + 1] = L;
+        }
+    }
+}
+
+}  // namespace battn

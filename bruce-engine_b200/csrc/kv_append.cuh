@@ -1,0 +1,73 @@
+// Quantise-on-append: fp32 K/V rows -> q8_0 records in the scale-first, head-major cache.
+// Replaces the store half of k_qkv_prep / k_qkv_prep_rows / k_qkv_prep_fast / k_qkv_prep_fast_ms
+// (engine/src/bruce.cu:690-710, 1713-1725, 1789-1812, 1888-1918).  HBM-bound byte work: one warp
+// per (sequence, row, kv head, K|V) record, 16-byte loads, 4-byte packed stores.
+#pragma once
+#include "common.cuh"
+
+namespace battn {
+
+struct AppendParams {
+    const float* k;
+    const float* v;
+    uint8_t* kvk;
+    uint8_t* kvv;
+    const int* pos;
+    const int* kslot;   // null: single sequence, caches point at the slot base
+    const int* act;     // null: every sequence active
+    int n_seq, rows, Hkv;
+    int pstride;        // slot_ctx or 2*W
+    int ring_mask;      // 2*W-1 for a sliding-window layer, -1 (all ones) otherwise
+    int n_slots;
+    int* status;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(256) k_kv_append(const AppendParams P) {
+    constexpr int NBLK = HD / 32;
+    constexpr int REC = HD + 2 * NBLK;
+    const int lane = threadIdx.x & 31;
+    const long long wid = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const long long total = (long long)P.n_seq * P.rows * P.Hkv * 2;
+    if (wid >= total) return;
+    const int which = (int)(wid & 1);                 // 0 = K, 1 = V
+    long long t = wid >> 1;
+    const int kvh = (int)(t % P.Hkv); t /= P.Hkv;
+    const int r = (int)(t % P.rows);
+    const int i = (int)(t / P.rows);
+
+    if (P.act && !P.act[i]) return;                   // idle rows never write KV (bruce.cu:1869)
+    const int slot = P.kslot ? P.kslot[i] : 0;
+    const int p = P.pos[i] + r;
+    const bool bad = p < 0 || (P.ring_mask < 0 && p >= P.pstride) || slot < 0 ||
+                     (P.kslot && slot >= P.n_slots);
+    if (bad) {
+        if (lane == 0) atomicOr(P.status, BATTN_DEV_BAD_POSITION);
+        return;
+    }
+    const int pp = p & P.ring_mask;                   // ring slot (bruce.cu:691); identity when -1
+    const float* src = (which ? P.v : P.k) + (((size_t)i * P.rows + r) * P.Hkv + kvh) * HD;
+    uint8_t* dst = (which ? P.kvv : P.kvk) + (((size_t)slot * P.Hkv + kvh) * P.pstride + pp) * (size_t)REC;
+
+#pragma unroll
+    for (int it = 0; it < HD / 128; ++it) {
+        const float4 x = *reinterpret_cast<const float4*>(src + it * 128 + lane * 4);
+        float amax = fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w)));
+        // 8 lanes x 4 values = one 32-value block
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+        const float d = __fdiv_rn(amax, 127.f);                       // IEEE divide (bruce.cu:704)
+        const float id = d != 0.f ? __fdiv_rn(1.f, d) : 0.f;          // (bruce.cu:705)
+        // lrintf(x * id): one fp32 multiply, round half to even, no clamp (bruce.cu:709)
+        const uint32_t q0 = (uint32_t)(uint8_t)(int8_t)__float2int_rn(__fmul_rn(x.x, id));
+        const uint32_t q1 = (uint32_t)(uint8_t)(int8_t)__float2int_rn(__fmul_rn(x.y, id));
+        const uint32_t q2 = (uint32_t)(uint8_t)(int8_t)__float2int_rn(__fmul_rn(x.z, id));
+        const uint32_t q3 = (uint32_t)(uint8_t)(int8_t)__float2int_rn(__fmul_rn(x.w, id));
+        *reinterpret_cast<uint32_t*>(dst + 2 * NBLK + it * 128 + lane * 4) = q0 | (q1 << 8) | (q2 << 16) | (q3 << 24);
+        if ((lane & 7) == 0)
+            reinterpret_cast<__half*>(dst)[it * 4 + (lane >> 3)] = __float2half_rn(d);   // (bruce.cu:708)
+    }
+}
+
+}  // namespace battn

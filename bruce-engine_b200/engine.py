@@ -1,0 +1,170 @@
+"""Host-side mirror of the reference engine's attention call surface, over the C ABI.
+
+Method names follow the reference's launches (engine/src/bruce.cu): `qkv_prep_store` is the
+quantise-and-store half of k_qkv_prep / k_qkv_prep_fast / k_qkv_prep_fast_ms (:644, :1732, :1835),
+`launch_attn_m` is launch_attn_m + the merge (:3942, :928, :1999), `launch_attn_ms` is
+launch_attn_ms + the merge (:4158), `attn_combine` is k_attn_combine (:992).  Arguments keep the
+reference's meaning: device buffers owned by the caller, device-resident positions, `part` scratch.
+
+torch is used only for device memory and streams; every computation is a call into libbattn.so.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import capi
+from .layout import F16, Geom
+
+
+def _ptr(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+class AttnEngine:
+    """One attention context (geometry + device), the replacement of the reference's lazily-set
+    kernel attributes and its g_kv_nctx symbol (bruce.cu:65, 3948-3955, 5482)."""
+
+    def __init__(self, geom: Geom, device: int = 0):
+        if not torch.cuda.is_available():
+            raise RuntimeError("AttnEngine needs a CUDA device (sm_100a); there is no CPU path")
+        self.lib = capi.load()
+        self.geom = geom
+        self.device = torch.device("cuda", device)
+        cg = capi.CGeom(geom.n_head, geom.n_kv, geom.head_dim, geom.window, geom.slot_ctx,
+                        geom.n_slots, geom.q_dtype, geom.out_dtype, geom.softmax_scale)
+        h = C.c_void_p()
+        rc = self.lib.battn_init(C.byref(cg), device, C.byref(h))
+        if rc:
+            raise capi.BattnError("battn_init", rc)
+        self.h = h
+        self.q_torch = torch.float16 if geom.q_dtype == F16 else torch.float32
+        self.out_torch = torch.float16 if geom.out_dtype == F16 else torch.float32
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.lib.battn_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # ---- sizes and allocation (alloc_buffers, bruce.cu:5460-5507, 5564) --------------------------
+    def _check(self, fn: str, rc: int):
+        if rc:
+            raise capi.BattnError(fn, rc, self.lib.battn_last_cuda_error(self.h))
+
+    def kv_layer_bytes(self, is_swa: bool) -> int:
+        n = C.c_size_t()
+        self._check("battn_kv_layer_bytes", self.lib.battn_kv_layer_bytes(self.h, int(is_swa), C.byref(n)))
+        return n.value
+
+    def alloc_kv_layer(self, is_swa: bool, fill: int | None = None):
+        """One layer's K and V buffers for all slots."""
+        n = self.kv_layer_bytes(is_swa)
+        mk = (lambda: torch.empty(n, dtype=torch.uint8, device=self.device)) if fill is None else \
+             (lambda: torch.full((n,), fill, dtype=torch.uint8, device=self.device))
+        return mk(), mk()
+
+    def workspace_bytes(self, n_seq: int, rows: int) -> int:
+        n = C.c_size_t()
+        self._check("battn_workspace_bytes", self.lib.battn_workspace_bytes(self.h, n_seq, rows, C.byref(n)))
+        return n.value
+
+    def exact_workspace_bytes(self, n_seq: int, rows: int, nsplit: int) -> int:
+        n = C.c_size_t()
+        self._check("battn_exact_workspace_bytes",
+                    self.lib.battn_exact_workspace_bytes(self.h, n_seq, rows, nsplit, C.byref(n)))
+        return n.value
+
+    def alloc_part(self, n_seq: int, rows: int) -> torch.Tensor:
+        """The split-K scratch (`part`, bruce.cu:5564)."""
+        return torch.empty(self.workspace_bytes(n_seq, rows), dtype=torch.uint8, device=self.device)
+
+    @staticmethod
+    def _stream():
+        return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    # ---- KV append ---------------------------------------------------------------------------------
+    def qkv_prep_store(self, k, v, kvk, kvv, pos, kslot=None, act=None, rows: int = 1, is_swa: bool = False):
+        """k, v: fp32 [n_seq][rows][n_kv][head_dim]; pos/kslot/act: int32 device tensors."""
+        n_seq = pos.numel()
+        self._check("battn_kv_append", self.lib.battn_kv_append(
+            self.h, _ptr(k), _ptr(v), _ptr(kvk), _ptr(kvv), _ptr(pos), _ptr(kslot), _ptr(act),
+            n_seq, rows, int(is_swa), self._stream()))
+
+    # ---- attention ---------------------------------------------------------------------------------
+    def launch_attn_m(self, out, q, kvk, kvv, pos, part, rows: int, is_swa: bool = False):
+        """Single-sequence attention: rows == 1 decode, 2..8 speculative verify, > 8 prompt chunk
+        (the dispatch of launch_attn_m, bruce.cu:3942-4122), merge included."""
+        st = self._stream()
+        if rows == 1:
+            rc = self.lib.battn_decode(self.h, _ptr(out), _ptr(q), _ptr(kvk), _ptr(kvv), _ptr(pos), None, None,
+                                       _ptr(part), 1, int(is_swa), st)
+            self._check("battn_decode", rc)
+        elif rows <= 8 and rows * self.geom.group <= 32:
+            rc = self.lib.battn_verify(self.h, _ptr(out), _ptr(q), _ptr(kvk), _ptr(kvv), _ptr(pos), None, None,
+                                       _ptr(part), rows, 1, int(is_swa), st)
+            self._check("battn_verify", rc)
+        else:
+            rc = self.lib.battn_prefill(self.h, _ptr(out), _ptr(q), _ptr(kvk), _ptr(kvv), _ptr(pos), _ptr(part),
+                                        rows, int(is_swa), st)
+            self._check("battn_prefill", rc)
+
+    def launch_attn_ms(self, out, q, kvk, kvv, pos, kslot, act, part, rows: int, is_swa: bool = False,
+                       rows_per_seq: int = 1):
+        """Multi-slot attention: `rows` independent sequences (launch_attn_ms, bruce.cu:4158-4177);
+        rows_per_seq > 1 runs a batched speculative verify."""
+        st = self._stream()
+        if rows_per_seq == 1:
+            rc = self.lib.battn_decode(self.h, _ptr(out), _ptr(q), _ptr(kvk), _ptr(kvv), _ptr(pos), _ptr(kslot),
+                                       _ptr(act), _ptr(part), rows, int(is_swa), st)
+            self._check("battn_decode", rc)
+        else:
+            rc = self.lib.battn_verify(self.h, _ptr(out), _ptr(q), _ptr(kvk), _ptr(kvv), _ptr(pos), _ptr(kslot),
+                                       _ptr(act), _ptr(part), rows_per_seq, rows, int(is_swa), st)
+            self._check("battn_verify", rc)
+
+    def attn_exact(self, out, q, kvk, kvv, pos, part, n_seq: int, rows: int, nsplit: int, is_swa: bool = False,
+                   kslot=None, act=None):
+        """The exact fp32 path (k_attn / k_attn_rows / k_attn_m + k_attn_combine_rows)."""
+        rc = self.lib.battn_attend_exact(self.h, _ptr(out), _ptr(q), _ptr(kvk), _ptr(kvv), _ptr(pos), _ptr(kslot),
+                                         _ptr(act), _ptr(part), n_seq, rows, nsplit, int(is_swa), self._stream())
+        self._check("battn_attend_exact", rc)
+
+    def attn_partials(self, rec, q, kvk, kvv, pos, part, rows: int = 1, batch: int = 1, is_swa: bool = False,
+                      kslot=None, act=None):
+        """Split records (o, m, l) instead of the normalised output (bruce.cu:781-783)."""
+        rc = self.lib.battn_partials(self.h, _ptr(rec), _ptr(q), _ptr(kvk), _ptr(kvv), _ptr(pos), _ptr(kslot),
+                                     _ptr(act), _ptr(part), rows, batch, int(is_swa), self._stream())
+        self._check("battn_partials", rc)
+
+    def attn_combine(self, out, parts, n_parts: int, n_rows: int):
+        """k_attn_combine over records gathered from several devices (bruce.cu:992-1007)."""
+        rc = self.lib.battn_merge(self.h, _ptr(out), _ptr(parts), n_parts, n_rows, self._stream())
+        self._check("battn_merge", rc)
+
+    # ---- diagnostics -------------------------------------------------------------------------------
+    def device_status(self, clear: bool = True) -> int:
+        bits = C.c_int()
+        self._check("battn_device_status", self.lib.battn_device_status(self.h, C.byref(bits), int(clear)))
+        return bits.value
+
+    def profile_start(self, max_launches: int):
+        """Bracket the main kernel of every following attention call with CUDA events."""
+        self._check("battn_profile_start", self.lib.battn_profile_start(self.h, max_launches))
+        self._prof_cap = max_launches
+
+    def profile_stop(self):
+        """Elapsed milliseconds of each bracketed launch since profile_start, in call order."""
+        buf = (C.c_float * self._prof_cap)()
+        n = C.c_int()
+        self._check("battn_profile_stop", self.lib.battn_profile_stop(self.h, buf, self._prof_cap, C.byref(n)))
+        return [buf[i] for i in range(min(n.value, self._prof_cap))]
+
+    def launch_count(self) -> int:
+        return int(self.lib.battn_launch_count(self.h))

@@ -1,0 +1,181 @@
+/*
+ * battn.h -- C ABI of the B200 (sm_100a) attention hot path for the Bruce inference engine.
+ *
+ * The reference engine (engine/src/bruce.cu) has no FFI: its attention path is a handful of
+ * `static` launches in one translation unit.  This header is the boundary a host engine binds
+ * instead of those launches.  Every entry point cites the reference call it replaces.
+ *
+ * Conventions
+ *   - Plain pointers and sizes only.  Every pointer named q/k/v/out/kvk/kvv/pos/kslot/act/ws is a
+ *     DEVICE pointer owned by the caller (the reference allocates them once in alloc_buffers,
+ *     bruce.cu:5460-5588) and merely borrowed for the duration of the call.
+ *   - `stream` is a cudaStream_t passed as void*.  Launches are asynchronous and contain no
+ *     allocation, no synchronisation and no host read of device state, so they can be recorded
+ *     into a CUDA graph exactly like the reference's launches (bruce.cu:7877-7900, 8046-8055).
+ *   - Positions are device-resident ints read inside the kernels (bruce.cu:653, 724, 1054), so a
+ *     captured graph replays at new positions.
+ *   - Every function returns an int status (BATTN_OK == 0).  Nothing prints, nothing exits
+ *     (the reference's CK()/exit(1), bruce.cu:70-71, 3961-3962, becomes a status code).
+ *
+ * KV cache layout (bruce.cu:56-65, 690-693, 1888-1892, 5473-5503), one K and one V buffer per layer:
+ *     [slot s][kv head h][position p'][record]
+ *     record  = [HD/32 fp16 scales][HD int8 values]            (136 B for HD 128, 272 B for HD 256)
+ *     address = base + ((s * n_kv + h) * pstride + p') * record_bytes
+ *     pstride = slot_ctx (full-attention layer) or 2*window (sliding-window layer, a ring)
+ *     p'      = p (full) or p & (2*window - 1) (sliding window)
+ * Requirements added by this implementation: the buffers are 16-byte aligned, slot_ctx is even,
+ * window is a power of two >= 32.
+ */
+#ifndef BATTN_H
+#define BATTN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define BATTN_VERSION 1
+
+/* status codes */
+enum {
+    BATTN_OK            = 0,
+    BATTN_ERR_ARG       = 1,   /* null pointer, unsupported geometry, rows out of range          */
+    BATTN_ERR_CAPACITY  = 2,   /* more sequences / rows than the call supports                  */
+    BATTN_ERR_CUDA      = 3,   /* a CUDA runtime call failed; battn_last_cuda_error() has it    */
+    BATTN_ERR_DEVICE    = 4    /* a kernel recorded a fault (bad position, bounded wait ran out) */
+};
+
+/* element types of q and out */
+enum { BATTN_F32 = 0, BATTN_F16 = 1 };
+
+/* bits of the device status word (battn_device_status) */
+enum {
+    BATTN_DEV_BAD_POSITION = 1,  /* a row's position fell outside the cache; the row was skipped  */
+    BATTN_DEV_WAIT_TIMEOUT = 2   /* a bounded in-kernel wait ran out; results of that launch void */
+};
+
+/* Geometry: the reference fixes these with #defines (bruce.cu:43-53); here they are run-time. */
+typedef struct battn_geom {
+    int   n_head;         /* query heads (reference 16; graded configs 32)                        */
+    int   n_kv;           /* KV heads    (reference 4;  graded configs 8); n_head % n_kv == 0     */
+    int   head_dim;       /* 128 or 256                                                           */
+    int   window;         /* sliding window W (reference 1024; graded 4096); ring holds 2*W       */
+    int   slot_ctx;       /* positions per slot in a full-attention layer (g_kv_nctx, :65, :5482) */
+    int   n_slots;        /* KV partitions (serving slots, bruce.cu:90-94)                        */
+    int   q_dtype;        /* BATTN_F32 (as the reference) or BATTN_F16                            */
+    int   out_dtype;      /* BATTN_F32 (as the reference) or BATTN_F16                            */
+    float softmax_scale;  /* 0 => 1/sqrt(head_dim) (0.0625 in the reference, bruce.cu:756)        */
+} battn_geom;
+
+typedef struct battn_handle battn_handle;
+
+/* One-time set-up: replaces the lazy cudaFuncSetAttribute calls (bruce.cu:3948-3955, 4161-4168)
+ * and the g_kv_nctx symbol upload (bruce.cu:5482).  Makes `device` current, allocates one small
+ * device status word, sets every kernel attribute.  Call outside stream capture. */
+int battn_init(const battn_geom* geom, int device, battn_handle** out_handle);
+int battn_destroy(battn_handle* h);
+
+/* Bytes of ONE layer's K (or V) buffer for all slots: the sizes alloc_buffers computes at
+ * bruce.cu:5476-5481 (n_slots * pstride * n_kv * record_bytes). */
+int battn_kv_layer_bytes(const battn_handle* h, int is_swa, size_t* out_bytes);
+
+/* Bytes of the split-K scratch (`part` in the reference, bruce.cu:1058-1070, 5564) needed for a
+ * call with up to n_seq sequences of up to rows_per_seq query rows each. */
+int battn_workspace_bytes(const battn_handle* h, int n_seq, int rows_per_seq, size_t* out_bytes);
+
+/* Bytes of scratch battn_attend_exact needs for an explicit split count (the reference sizes
+ * `part` as rows * nsplit records, bruce.cu:1060-1066). */
+int battn_exact_workspace_bytes(const battn_handle* h, int n_seq, int rows_per_seq, int nsplit,
+                                size_t* out_bytes);
+
+/* KV append: the quantise-and-store half of k_qkv_prep (bruce.cu:690-710), k_qkv_prep_rows
+ * (:1713-1725), k_qkv_prep_fast (:1789-1812) and k_qkv_prep_fast_ms (:1888-1918).
+ *   k, v   fp32 [n_seq][rows_per_seq][n_kv][head_dim], already RoPE'd / normalised by the host
+ *   kslot == NULL : single-sequence call.  kvk/kvv are that sequence's SLOT base (M.kvk_ptr[b]),
+ *                   n_seq must be 1 and row r is stored at position pos[0] + r      (:1732, :7671)
+ *   kslot != NULL : multi-slot call.  kvk/kvv are the LAYER base (M.kvk_layer[b]); sequence i
+ *                   writes rows pos[i] .. pos[i]+rows_per_seq-1 of partition kslot[i]; sequences
+ *                   with act[i] == 0 write nothing                                  (:1835-1869)
+ * Per 32 values: d = amax/127.f, id = d ? 1.f/d : 0, q = lrintf(x*id), scale = fp16(d), no clamp.
+ * The bytes written are identical to the reference's. */
+int battn_kv_append(battn_handle* h, const float* k, const float* v, uint8_t* kvk, uint8_t* kvv,
+                    const int* pos, const int* kslot, const int* act,
+                    int n_seq, int rows_per_seq, int is_swa, void* stream);
+
+/* Decode attention, one query row per sequence, normalised output:
+ * launch_attn_m(rows = 1) + k_attn_combine_fast (bruce.cu:3942-3963, 928-990, call :7958-7969)
+ * when kslot == NULL, launch_attn_ms (bruce.cu:4158-4177, call :7720) when kslot != NULL.
+ *   q, out [n_seq][n_head][head_dim] in q_dtype / out_dtype; row i attends keys
+ *   [kstart, pos[i]] of its partition, kstart = is_swa ? max(0, pos[i]+1-window) : 0  (:724-729).
+ *   Rows with act[i] == 0 produce no output and touch no KV (:3398-3406). */
+int battn_decode(battn_handle* h, void* out, const void* q, const uint8_t* kvk, const uint8_t* kvv,
+                 const int* pos, const int* kslot, const int* act, void* ws,
+                 int n_seq, int is_swa, void* stream);
+
+/* Speculative-verify attention: `rows` (1..8) query rows at positions pos[i] .. pos[i]+rows-1 that
+ * share one sweep over sequence i's KV and are causal among themselves:
+ * launch_attn_m(rows 2..8) + k_attn_combine_rows (bruce.cu:3965-4019, 1999-2016; exact form
+ * k_attn_m<M> :2087-2143).  Row r sees keys [lo_r, pos[i]+r], lo_r = is_swa ?
+ * max(0, pos[i]+r-window+1) : 0 (:3686-3689, :2056).  `batch` sequences are processed in one call
+ * (kslot/act as in battn_decode; kslot == NULL requires batch == 1).
+ *   q, out [batch][rows][n_head][head_dim]. */
+int battn_verify(battn_handle* h, void* out, const void* q, const uint8_t* kvk, const uint8_t* kvv,
+                 const int* pos, const int* kslot, const int* act, void* ws,
+                 int rows, int batch, int is_swa, void* stream);
+
+/* Prompt-chunk attention: `rows` (1..512) query rows at pos[0] .. pos[0]+rows-1 against the cache
+ * AFTER the chunk's own K/V were appended: launch_attn_m(rows > 8) + the merge
+ * (bruce.cu:4021-4078, 2750-3131, call :7729-7732).  Causal plus optional window.
+ *   q, out [rows][n_head][head_dim].  kvk/kvv are the slot base. */
+int battn_prefill(battn_handle* h, void* out, const void* q, const uint8_t* kvk, const uint8_t* kvv,
+                  const int* pos, void* ws, int rows, int is_swa, void* stream);
+
+/* The exact fp32 path: per-key online softmax in fp32 with no tensor cores, the same arithmetic as
+ * k_attn / k_attn_rows / k_attn_m (bruce.cu:713-785, 1921-1997, 2087-2143) followed by
+ * k_attn_combine_rows (:1999-2016).  Any rows_per_seq >= 1.  `nsplit` (1..128) is the reference's
+ * split count (key range rule :724-729).  Same argument meaning as battn_verify. */
+int battn_attend_exact(battn_handle* h, void* out, const void* q, const uint8_t* kvk,
+                       const uint8_t* kvv, const int* pos, const int* kslot, const int* act,
+                       void* ws, int n_seq, int rows_per_seq, int nsplit, int is_swa, void* stream);
+
+/* Partial records for a sequence split across devices: like battn_verify, but instead of the
+ * normalised output each (sequence, row, head) yields the reference's split record
+ * (bruce.cu:781-783, 1058-1070): head_dim fp32 unnormalised o, then m (max score, natural-log
+ * units), then l (sum of exp(score - m)).
+ *   rec fp32 [batch][rows][n_head][head_dim + 2].  An empty key range gives (0, -1e30, 0). */
+int battn_partials(battn_handle* h, float* rec, const void* q, const uint8_t* kvk,
+                   const uint8_t* kvv, const int* pos, const int* kslot, const int* act, void* ws,
+                   int rows, int batch, int is_swa, void* stream);
+
+/* Log-sum-exp merge of n_parts records per (row, head): k_attn_combine (bruce.cu:992-1007).
+ *   parts fp32 [n_parts][n_rows][n_head][head_dim + 2]; out [n_rows][n_head][head_dim] out_dtype.
+ *   out = sum_s o_s e^(m_s-M) / sum_s l_s e^(m_s-M), M = max_s m_s; empty records contribute 0. */
+int battn_merge(battn_handle* h, void* out, const float* parts, int n_parts, int n_rows,
+                void* stream);
+
+/* Device status word (bits BATTN_DEV_*), read with a blocking copy; clears it when `clear` != 0.
+ * Not for use inside stream capture. */
+int battn_device_status(battn_handle* h, int* out_bits, int clear);
+
+/* Per-kernel timing, the counterpart of the reference's --probe CUDA-event phase timing
+ * (bruce.cu:8334-8397).  Between battn_profile_start and battn_profile_stop every attention call
+ * brackets its MAIN kernel (flash-decode / prefill; not the merge) with a pair of CUDA events on the
+ * caller's stream, up to max_launches pairs.  battn_profile_stop synchronises on the last event and
+ * returns the elapsed milliseconds of each bracketed launch in call order.  Not capturable. */
+int battn_profile_start(battn_handle* h, int max_launches);
+int battn_profile_stop(battn_handle* h, float* ms_out, int cap, int* n_out);
+
+/* cudaError_t of the last failing runtime call on this handle (0 if none). */
+int battn_last_cuda_error(const battn_handle* h);
+
+/* Number of kernels this library has launched through `h` since init (for launch accounting). */
+long long battn_launch_count(const battn_handle* h);
+
+int battn_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BATTN_H */

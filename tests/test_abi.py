@@ -1,0 +1,67 @@
+"""The C-ABI library builds, loads without a GPU, and exports exactly what include/battn.h
+declares.  No compute calls here."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+import bruce_engine_b200  # noqa: F401
+from bruce_engine_b200 import build, capi
+from bruce_engine_b200.layout import G_B, G_R
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared():
+    text = open(os.path.join(ROOT, "include", "battn.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(battn_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_builds_and_exports_every_declared_symbol():
+    path = build.build()
+    assert os.path.exists(path)
+    lib = C.CDLL(path)
+    names = _declared()
+    assert len(names) >= 15
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in battn.h but not exported"
+    assert set(names) == set(capi.SIGNATURES), "ctypes binding and header disagree"
+    assert capi.load().battn_version() == 1
+
+
+def test_argument_errors_without_a_device():
+    lib = capi.load()
+    h = C.c_void_p()
+    assert lib.battn_init(None, 0, C.byref(h)) == capi.ERR_ARG
+    bad = capi.CGeom(32, 8, 96, 4096, 8192, 1, 1, 1, 0.0)            # head_dim 96 unsupported
+    assert lib.battn_init(C.byref(bad), 0, C.byref(h)) == capi.ERR_ARG
+    bad = capi.CGeom(32, 8, 128, 1000, 8192, 1, 1, 1, 0.0)           # window not a power of two
+    assert lib.battn_init(C.byref(bad), 0, C.byref(h)) == capi.ERR_ARG
+    bad = capi.CGeom(32, 8, 128, 4096, 8191, 1, 1, 1, 0.0)           # odd slot_ctx
+    assert lib.battn_init(C.byref(bad), 0, C.byref(h)) == capi.ERR_ARG
+    bad = capi.CGeom(30, 8, 128, 4096, 8192, 1, 1, 1, 0.0)           # heads not divisible
+    assert lib.battn_init(C.byref(bad), 0, C.byref(h)) == capi.ERR_ARG
+    assert lib.battn_destroy(None) == capi.ERR_ARG
+    assert lib.battn_launch_count(None) == 0
+
+
+def test_engine_refuses_to_run_without_cuda():
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("CUDA present")
+    from bruce_engine_b200.engine import AttnEngine
+    with pytest.raises(RuntimeError):
+        AttnEngine(G_B)
+
+
+def test_layout_constants_match_reference():
+    # bruce.cu:56-61: 272 B per kv head per position, 1088 B per position (4 kv heads), K or V
+    assert G_R.rec == 272 and G_R.n_kv * G_R.rec == 1088
+    assert G_B.rec == 136
+    assert G_B.pos_bytes == G_R.pos_bytes == 2176
+    g = G_B.with_(slot_ctx=262144)
+    assert g.layer_bytes(False) == 262144 * 1088 and g.layer_bytes(True) == 8192 * 1088
+    g8 = G_R.with_(slot_ctx=4096, n_slots=8)
+    assert g8.slot_offset(3, False) == 3 * 4096 * 1088 and g8.slot_offset(3, True) == 3 * 2048 * 1088
