@@ -13,7 +13,9 @@ using namespace battn;
 
 namespace {
 
-constexpr size_t SMEM_MAX = 227 * 1024;     // opt-in dynamic shared memory per CTA on sm_100
+constexpr size_t SMEM_MAX = 226 * 1024;     // dynamic shared memory per CTA: the 227 KB opt-in limit of sm_100
+                                            // minus room for the kernels' static shared variables
+int g_init_cuda_error = 0;                  // cudaError_t of the last failing battn_init
 constexpr int FD_MAX_CTAS_PER_SM = 4;
 
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
@@ -208,6 +210,7 @@ int battn_init(const battn_geom* geom, int device, battn_handle** out_handle) {
     if (e == cudaSuccess) e = cudaMemset(h->d_status, 0, 16);
     if (e == cudaSuccess) e = g.HD == 128 ? fd_prepare_all<128>(h) : fd_prepare_all<256>(h);
     if (e != cudaSuccess) {
+        g_init_cuda_error = (int)e;
         if (h->d_status) cudaFree(h->d_status);
         delete h;
         return BATTN_ERR_CUDA;
@@ -255,6 +258,9 @@ int battn_kv_append(battn_handle* h, const float* k, const float* v, uint8_t* kv
     const int rc = check_seq_args(h, k, v, kvk, kvv, pos, kslot, n_seq, rows_per_seq, MAX_PREFILL);
     if (rc) return rc;
     const Geom& g = h->g;
+    // one call must not wrap the ring onto itself: two rows of the same launch would race for a slot
+    // (the reference appends at most 512 rows into a 2048-slot ring, bruce.cu:50-53, 1058)
+    if (is_swa && rows_per_seq > g.ring) return BATTN_ERR_CAPACITY;
     AppendParams P;
     P.k = k; P.v = v; P.kvk = kvk; P.kvv = kvv; P.pos = pos; P.kslot = kslot; P.act = act;
     P.n_seq = n_seq; P.rows = rows_per_seq; P.Hkv = g.Hkv;
@@ -366,7 +372,7 @@ int battn_profile_stop(battn_handle* h, float* ms_out, int cap, int* n_out) {
     return e == cudaSuccess ? BATTN_OK : cuda_fail(h, e);
 }
 
-int battn_last_cuda_error(const battn_handle* h) { return h ? h->last_cuda_error : 0; }
+int battn_last_cuda_error(const battn_handle* h) { return h ? h->last_cuda_error : g_init_cuda_error; }
 
 long long battn_launch_count(const battn_handle* h) { return h ? h->launches : 0; }
 

@@ -32,7 +32,9 @@ namespace fd {
 constexpr int NW = 4;                     // consumer warps
 constexpr int TILE = 64;                  // keys per stage
 constexpr int NTHREADS = (NW + 1) * 32;   // + one producer warp
-constexpr int STAGES = 3;
+// pipeline depth; the widest instantiation (head_dim 256, 8 rows) keeps two stages to fit shared memory
+template <int HD, int NT>
+__host__ __device__ constexpr int stages_of() { return (HD == 256 && NT == 4) ? 2 : 3; }
 
 struct Params {
     const void* q;
@@ -61,8 +63,8 @@ struct Cfg {
 // shared-memory bytes of one CTA
 template <int HD, int NT>
 __host__ __device__ constexpr size_t smem_bytes(int RG, int n_seq) {
-    return (size_t)STAGES * 2 * Cfg<HD>::TILE_BYTES + (size_t)NT * 8 * Cfg<HD>::QSTR * 2 +
-           (size_t)NW * RG * (HD + 2) * 4 + 2 * STAGES * 8 + (size_t)(n_seq + 2) * 4 + 16;
+    return (size_t)stages_of<HD, NT>() * 2 * Cfg<HD>::TILE_BYTES + (size_t)NT * 8 * Cfg<HD>::QSTR * 2 +
+           (size_t)NW * RG * (HD + 2) * 4 + 2 * stages_of<HD, NT>() * 8 + (size_t)(n_seq + 2) * 4 + 16;
 }
 
 __device__ __forceinline__ int perm16(int kappa) { return kappa ^ ((kappa >> 2) & 1); }
@@ -93,6 +95,7 @@ __global__ void __launch_bounds__(NTHREADS, (NT == 1 ? 3 : (NT == 2 ? 2 : 1)))
 k_flash_decode(const Params P) {
     using C = Cfg<HD>;
     constexpr int NBLK = C::NBLK, REC = C::REC, KSTEP = C::KSTEP, TILE_BYTES = C::TILE_BYTES, QSTR = C::QSTR;
+    constexpr int STAGES = stages_of<HD, NT>();
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ int s_abort;
     const int RG = P.RG;

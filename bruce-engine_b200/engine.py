@@ -37,7 +37,7 @@ class AttnEngine:
         h = C.c_void_p()
         rc = self.lib.battn_init(C.byref(cg), device, C.byref(h))
         if rc:
-            raise capi.BattnError("battn_init", rc)
+            raise capi.BattnError("battn_init", rc, self.lib.battn_last_cuda_error(None))
         self.h = h
         self.q_torch = torch.float16 if geom.q_dtype == F16 else torch.float32
         self.out_torch = torch.float16 if geom.out_dtype == F16 else torch.float32

@@ -98,6 +98,8 @@ int battn_exact_workspace_bytes(const battn_handle* h, int n_seq, int rows_per_s
  *   kslot != NULL : multi-slot call.  kvk/kvv are the LAYER base (M.kvk_layer[b]); sequence i
  *                   writes rows pos[i] .. pos[i]+rows_per_seq-1 of partition kslot[i]; sequences
  *                   with act[i] == 0 write nothing                                  (:1835-1869)
+ * On a sliding-window layer one call may append at most 2*window rows per sequence (more would
+ * alias ring slots inside one launch).
  * Per 32 values: d = amax/127.f, id = d ? 1.f/d : 0, q = lrintf(x*id), scale = fp16(d), no clamp.
  * The bytes written are identical to the reference's. */
 int battn_kv_append(battn_handle* h, const float* k, const float* v, uint8_t* kvk, uint8_t* kvv,
@@ -167,7 +169,8 @@ int battn_device_status(battn_handle* h, int* out_bits, int clear);
 int battn_profile_start(battn_handle* h, int max_launches);
 int battn_profile_stop(battn_handle* h, float* ms_out, int cap, int* n_out);
 
-/* cudaError_t of the last failing runtime call on this handle (0 if none). */
+/* cudaError_t of the last failing runtime call on this handle (0 if none); with h == NULL, of the
+ * last failing battn_init. */
 int battn_last_cuda_error(const battn_handle* h);
 
 /* Number of kernels this library has launched through `h` since init (for launch accounting). */

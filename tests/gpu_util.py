@@ -22,6 +22,8 @@ def gpu_fill(eng: AttnEngine, k: np.ndarray, v: np.ndarray, kvk, kvv, is_swa: bo
     rows per call.  slot=None uses the single-sequence form with the slot-base pointer."""
     g = eng.geom
     n = k.shape[0]
+    if is_swa:
+        chunk = min(chunk, 2 * g.window)        # one call must not wrap the ring onto itself
     kd = torch.from_numpy(np.ascontiguousarray(k)).to(eng.device)
     vd = torch.from_numpy(np.ascontiguousarray(v)).to(eng.device)
     for a in range(0, n, chunk):

@@ -82,3 +82,16 @@ def test_append_out_of_range_position_is_reported_not_written():
     assert eng.device_status() & capi.DEV_BAD_POSITION
     assert (kvk == 0x11).all() and (kvv == 0x11).all()
     assert eng.device_status() == 0                                              # cleared by the read
+
+
+def test_append_rejects_a_call_that_wraps_the_ring():
+    from bruce_engine_b200 import capi
+    from bruce_engine_b200.layout import G_B
+    g = G_B.with_(slot_ctx=1024, window=64)
+    eng = _engine(g)
+    kvk, kvv = eng.alloc_kv_layer(True, fill=0)
+    k = torch.zeros((1, 129, g.n_kv, g.head_dim), device="cuda")
+    with pytest.raises(capi.BattnError) as ei:
+        eng.qkv_prep_store(k, k, kvk, kvv, dev_i32([0], eng.device), rows=129, is_swa=True)
+    assert ei.value.code == capi.ERR_CAPACITY
+    eng.qkv_prep_store(k[:, :128], k[:, :128], kvk, kvv, dev_i32([0], eng.device), rows=128, is_swa=True)
