@@ -8,6 +8,7 @@
 #include "exact.cuh"
 #include "flash_decode.cuh"
 #include "kv_append.cuh"
+#include "prefill.cuh"
 
 using namespace battn;
 
@@ -44,6 +45,9 @@ cudaError_t fd_prepare(battn_handle* h, int idx) {
 template <int HD>
 cudaError_t fd_prepare_all(battn_handle* h) {
     cudaError_t e;
+    if (HD == 128) e = cudaFuncSetAttribute((const void*)pf::k_prefill<128, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, pf::Cfg<128, 128>::TOTAL);
+    else           e = cudaFuncSetAttribute((const void*)pf::k_prefill<256, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, pf::Cfg<256, 64>::TOTAL);
+    if (e != cudaSuccess) return e;
     if ((e = fd_prepare<HD, 1>(h, 0)) != cudaSuccess) return e;
     if ((e = fd_prepare<HD, 2>(h, 1)) != cudaSuccess) return e;
     if ((e = fd_prepare<HD, 4>(h, 2)) != cudaSuccess) return e;
@@ -169,6 +173,29 @@ int launch_flash(battn_handle* h, void* out, float* rec_out, const void* q, cons
     else             k_merge<256><<<n_seq * rows * g.Hq, 128, 0, st>>>(M);
     h->launches += 2;
     e = cudaGetLastError();
+    return e == cudaSuccess ? BATTN_OK : cuda_fail(h, e);
+}
+
+// prompt chunk on the tcgen05 kernel: one CTA per (128-row M tile, kv head), normalised output
+int launch_prefill(battn_handle* h, void* out, const void* q, const uint8_t* kvk, const uint8_t* kvv, const int* pos,
+                   int rows, int is_swa, cudaStream_t st) {
+    const Geom& g = h->g;
+    if (128 % g.G) return BATTN_ERR_ARG;
+    pf::Params P;
+    P.q = q; P.out = out; P.kvk = kvk; P.kvv = kvv; P.pos = pos;
+    P.rows = rows; P.Hq = g.Hq; P.Hkv = g.Hkv; P.G = g.G;
+    P.W = g.W; P.pstride = is_swa ? g.ring : g.slot_ctx; P.ring_mask = is_swa ? g.ring - 1 : -1;
+    P.slot_ctx = g.slot_ctx; P.is_swa = is_swa; P.q_f16 = g.q_f16; P.out_f16 = g.out_f16;
+    P.scale_log2 = g.scale * LOG2E; P.status = h->d_status;
+    const int MR = 128 / g.G;
+    const dim3 grid((rows + MR - 1) / MR, g.Hkv);
+    {
+        ProfScope prof(h, st);
+        if (g.HD == 128) pf::k_prefill<128, 128><<<grid, pf::NTHREADS, pf::Cfg<128, 128>::TOTAL, st>>>(P);
+        else             pf::k_prefill<256, 64><<<grid, pf::NTHREADS, pf::Cfg<256, 64>::TOTAL, st>>>(P);
+    }
+    h->launches += 1;
+    const cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? BATTN_OK : cuda_fail(h, e);
 }
 
@@ -306,8 +333,12 @@ int battn_prefill(battn_handle* h, void* out, const void* q, const uint8_t* kvk,
     const int rc = check_seq_args(h, out, q, kvk, kvv, pos, nullptr, 1, rows, MAX_PREFILL);
     if (rc) return rc;
     if (!ws) return BATTN_ERR_ARG;
-    return launch_exact(h, out, nullptr, q, kvk, kvv, pos, nullptr, nullptr, ws, 1, rows, exact_default_splits(rows),
-                        is_swa, (cudaStream_t)stream);
+    // the ring must hold the whole chunk plus the oldest row's window (bruce.cu:50-53)
+    if (is_swa && rows > h->g.W) return BATTN_ERR_CAPACITY;
+    if (h->g.W < 64) return BATTN_ERR_ARG;               // key tiles of 64 / 128 must not wrap the ring
+    if (rows * h->g.G <= 32)
+        return launch_flash(h, out, nullptr, q, kvk, kvv, pos, nullptr, nullptr, ws, 1, rows, is_swa, (cudaStream_t)stream);
+    return launch_prefill(h, out, q, kvk, kvv, pos, rows, is_swa, (cudaStream_t)stream);
 }
 
 int battn_attend_exact(battn_handle* h, void* out, const void* q, const uint8_t* kvk, const uint8_t* kvv,

@@ -333,11 +333,17 @@ k_flash_decode(const Params P) {
                         any_rescale |= (mn != m[nt][e]);
                         alpha[nt][e] = al;
                         m[nt][e] = mn;
-                        l[nt][e] = fmaf(l[nt][e], al, p0 + p1);
                         pe[e] = p0; pe[2 + e] = p1;
                     }
-                    pb0[nt] = movmatrix_trans(pack_h2(pe[0], pe[1]));     // keys kappa = 2t4, 2t4+1
-                    pb1[nt] = movmatrix_trans(pack_h2(pe[2], pe[3]));     // keys kappa = 2t4+8, 2t4+9
+                    const uint32_t h01 = pack_h2(pe[0], pe[1]), h23 = pack_h2(pe[2], pe[3]);
+                    // the denominator sums the fp16-rounded weights the MMA will use, so that
+                    // out = sum(p v) / sum(p) stays a convex combination of the V rows
+                    const float2 f01 = __half22float2(*reinterpret_cast<const __half2*>(&h01));
+                    const float2 f23 = __half22float2(*reinterpret_cast<const __half2*>(&h23));
+                    l[nt][0] = fmaf(l[nt][0], alpha[nt][0], f01.x + f23.x);
+                    l[nt][1] = fmaf(l[nt][1], alpha[nt][1], f01.y + f23.y);
+                    pb0[nt] = movmatrix_trans(h01);     // keys kappa = 2t4, 2t4+1
+                    pb1[nt] = movmatrix_trans(h23);     // keys kappa = 2t4+8, 2t4+9
                 }
                 if (__any_sync(0xffffffffu, any_rescale)) {
 #pragma unroll

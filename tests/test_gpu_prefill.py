@@ -1,0 +1,98 @@
+"""Parity of the tcgen05 prompt-chunk kernel with the CPU oracle (same tolerance as the other
+attention paths).  A prompt is processed the way the reference does it (bruce.cu:7665-7737): for
+each chunk, append the chunk's K/V rows, then attend the chunk's query rows against the cache."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as O
+from tests.gpu_util import dev_i32, dev_q, gpu_fill, new_out, to_np
+from tests.util import assert_close, draw_qkv, oracle_fill, oracle_geom
+
+pytestmark = pytest.mark.gpu
+
+
+def _geom(name, **kw):
+    from bruce_engine_b200.layout import G_B, G_R
+    return (G_B if name == "B" else G_R).with_(**kw)
+
+
+def _run_prompt(name, n_prompt, chunk, is_swa, window, seed, check_chunks=None):
+    from bruce_engine_b200.engine import AttnEngine
+    g = _geom(name, slot_ctx=max(n_prompt, 64), window=window)
+    eng, og = AttnEngine(g), oracle_geom(g)
+    rng = np.random.default_rng(seed)
+    q = rng.standard_normal((n_prompt, g.n_head, g.head_dim), dtype=np.float32)
+    if g.q_dtype == 1:
+        q = q.astype(np.float16).astype(np.float32)
+    k = rng.standard_normal((n_prompt, g.n_kv, g.head_dim), dtype=np.float32)
+    v = rng.standard_normal((n_prompt, g.n_kv, g.head_dim), dtype=np.float32)
+    kvk, kvv = eng.alloc_kv_layer(is_swa, fill=0xFF)       # 0xFF..: NaN scales in never-written slots
+    okvk, okvv = O.new_cache(og, is_swa, fill=0xFF), O.new_cache(og, is_swa, fill=0xFF)
+    part = eng.alloc_part(1, chunk)
+    worst = (0.0, 0.0)
+    for ci, a in enumerate(range(0, n_prompt, chunk)):
+        rows = min(chunk, n_prompt - a)
+        gpu_fill(eng, k[a:a + rows], v[a:a + rows], kvk, kvv, is_swa, start=a)
+        oracle_fill(og, k[a:a + rows], v[a:a + rows], is_swa, kvk=okvk, kvv=okvv, start=a)
+        out = new_out(eng, 1, rows, g.n_head, g.head_dim)
+        eng.launch_attn_m(out, dev_q(eng, q[None, a:a + rows]), kvk, kvv, dev_i32([a], eng.device), part, rows, is_swa)
+        torch.cuda.synchronize()
+        if check_chunks is not None and ci not in check_chunks:
+            continue
+        want = O.attend(og, q[None, a:a + rows], okvk, okvv, [a], rows=rows, is_swa=is_swa)
+        mabs, rel = assert_close(to_np(out), want, f"{name} swa={is_swa} chunk {ci} rows {rows}")
+        worst = (max(worst[0], mabs), max(worst[1], rel))
+    assert (kvk.cpu().numpy() == okvk).all() and (kvv.cpu().numpy() == okvv).all()
+    assert eng.device_status() == 0
+    return worst
+
+
+@pytest.mark.parametrize("name", ["B", "R"])
+@pytest.mark.parametrize("is_swa", [False, True])
+def test_chunked_prompt_small(name, is_swa):
+    """Ragged sizes: prompt not a multiple of the chunk, chunk not a multiple of the M tile."""
+    _run_prompt(name, n_prompt=700, chunk=200, is_swa=is_swa, window=256, seed=21)
+
+
+@pytest.mark.parametrize("name", ["B", "R"])
+def test_single_small_chunks(name):
+    """Chunks of 9..40 rows (one partial M tile) at position 0 and deeper."""
+    for rows, n0 in ((9, 0), (33, 0), (40, 300), (31, 129)):
+        _run_prompt(name, n_prompt=n0 + rows, chunk=max(n0, rows) if n0 else rows, is_swa=False, window=64, seed=22)
+
+
+@pytest.mark.parametrize("is_swa", [False, True])
+def test_prompt_4k_in_512_row_chunks(is_swa):
+    """BASELINE config 2 at reduced length: 512-row chunks against a growing cache, window 1024 so
+    that later chunks exercise the sliding window; all rows of chunks 0, 3 and 7 are checked."""
+    _run_prompt("B", n_prompt=4096, chunk=512, is_swa=is_swa, window=1024, seed=0, check_chunks={0, 3, 7})
+
+
+def test_prefill_matches_exact_device_path_at_depth():
+    """A 512-row chunk at depth 32K (window 4096 and full): compared with the exact fp32 device path
+    (itself oracle-checked) because the CPU oracle would need minutes."""
+    from bruce_engine_b200.engine import AttnEngine
+    g = _geom("B", slot_ctx=33280, window=4096)
+    eng = AttnEngine(g)
+    gen = torch.Generator(device="cuda"); gen.manual_seed(5)
+    n, rows = 33280, 512
+    for is_swa in (False, True):
+        kvk, kvv = eng.alloc_kv_layer(is_swa)
+        start = n - 8192 if is_swa else 0
+        pos = torch.zeros(1, dtype=torch.int32, device="cuda")
+        for a in range(start, n, 512):
+            kk = torch.randn((1, 512, g.n_kv, g.head_dim), generator=gen, device="cuda")
+            vv = torch.randn((1, 512, g.n_kv, g.head_dim), generator=gen, device="cuda")
+            pos.fill_(a)
+            eng.qkv_prep_store(kk, vv, kvk, kvv, pos, rows=512, is_swa=is_swa)
+        q = torch.randn((1, rows, g.n_head, g.head_dim), generator=gen, device="cuda").half()
+        pos.fill_(n - rows)
+        out = new_out(eng, 1, rows, g.n_head, g.head_dim)
+        eng.launch_attn_m(out, q, kvk, kvv, pos, eng.alloc_part(1, rows), rows, is_swa)
+        ref = torch.empty_like(out)
+        ws = torch.empty(eng.exact_workspace_bytes(1, rows, 4), dtype=torch.uint8, device="cuda")
+        eng.attn_exact(ref, q, kvk, kvv, pos, ws, 1, rows, 4, is_swa)
+        torch.cuda.synchronize()
+        assert_close(to_np(out), to_np(ref), f"prefill at depth swa={is_swa}")
+    assert eng.device_status() == 0
