@@ -1,0 +1,86 @@
+/*
+ * battn_bruce_shim.h -- drop-in shim for the reference engine's attention call sites.
+ *
+ * The reference (engine/src/bruce.cu) launches its attention kernels through a handful of `static`
+ * functions.  Including this header after `#include "battn.h"` gives the host code functions with the
+ * reference's own names, argument order and meaning, implemented by the C ABI, so the call sites at
+ * bruce.cu:7665-7761 (batched) and :7936-7980 (single row) change by a rename at most.
+ *
+ * What differs from the reference, by design:
+ *   - k and v arrive already RoPE'd / normalised: the model-specific prologue of k_qkv_prep* (L2 norm,
+ *     NeoX RoPE, sqk scale; bruce.cu:657-687, 1742-1780) stays in a host kernel; `kv_append_*` below
+ *     replaces only the quantise-and-store half (:690-710).
+ *   - launch_attn_m / launch_attn_ms write the NORMALISED output and ignore `ns`: the host then takes its
+ *     existing ns == 1 branch (k_gate_norm_vec4 on `out`, bruce.cu:7745-7751) and never launches
+ *     k_attn_combine* / k_combine_gate_norm_rows_opt.
+ *   - a non-zero status is reported through battn_shim_fail() (default: print and exit(1), the
+ *     reference's CK() behaviour, bruce.cu:70-71); hosts that want to recover install their own.
+ */
+#ifndef BATTN_BRUCE_SHIM_H
+#define BATTN_BRUCE_SHIM_H
+
+#include <cstdio>
+#include <cstdlib>
+#include <cuda_runtime.h>
+
+#include "battn.h"
+
+static battn_handle* g_battn = nullptr;   /* set once by battn_shim_init() from alloc_buffers() */
+
+static inline void battn_shim_fail(const char* what, int rc) {
+    std::fprintf(stderr, "battn: %s failed with status %d (cudaError %d)\n", what, rc,
+                 battn_last_cuda_error(g_battn));
+    std::exit(1);
+}
+#define BATTN_CK(call) do { int rc_ = (call); if (rc_) battn_shim_fail(#call, rc_); } while (0)
+
+/* alloc_buffers() (bruce.cu:5460-5507): geometry from the engine's #defines / model fields.
+ * Replaces the g_kv_nctx upload (:5482) and the lazy cudaFuncSetAttribute calls (:3948-3955). */
+static inline void battn_shim_init(int n_head, int n_kv, int hd, int swa, int slot_ctx, int n_slots) {
+    battn_geom g = {n_head, n_kv, hd, swa, slot_ctx, n_slots, BATTN_F32, BATTN_F32, 0.f};
+    BATTN_CK(battn_init(&g, 0, &g_battn));
+}
+/* size of M.part (bruce.cu:5564): rows = MBUF for the prompt path */
+static inline size_t battn_shim_part_bytes(int max_slots, int max_rows) {
+    size_t a = 0, b = 0;
+    BATTN_CK(battn_workspace_bytes(g_battn, max_slots, 8, &a));
+    BATTN_CK(battn_workspace_bytes(g_battn, 1, max_rows, &b));
+    return a > b ? a : b;
+}
+
+/* store half of k_qkv_prep / k_qkv_prep_fast (bruce.cu:644, 1732; calls :7671, :7941):
+ * rows of ONE sequence at *pos .. *pos+rows-1, kvk/kvv = slot base (M.kvk_ptr[b]) */
+static inline void kv_append_rows(const float* k, const float* v, uint8_t* kvk, uint8_t* kvv, const int* pos,
+                                  int rows, int is_swa, cudaStream_t st) {
+    BATTN_CK(battn_kv_append(g_battn, k, v, kvk, kvv, pos, nullptr, nullptr, 1, rows, is_swa, st));
+}
+/* store half of k_qkv_prep_fast_ms (bruce.cu:1835; call :7667): one row per slot, layer base pointers */
+static inline void kv_append_ms(const float* k, const float* v, uint8_t* kvk_layer, uint8_t* kvv_layer,
+                                const int* pos, const int* kslot, const int* act, int rows, int is_swa,
+                                cudaStream_t st) {
+    BATTN_CK(battn_kv_append(g_battn, k, v, kvk_layer, kvv_layer, pos, kslot, act, rows, 1, is_swa, st));
+}
+
+/* launch_attn_m (bruce.cu:3942; calls :7729, :7732, :7958) with the merge folded in */
+static inline void launch_attn_m(float* out, const float* q, const uint8_t* kvk, const uint8_t* kvv,
+                                 const int* pos, float* part, int rows, int /*ns*/, int is_swa, cudaStream_t st) {
+    if (rows == 1)      BATTN_CK(battn_decode(g_battn, out, q, kvk, kvv, pos, nullptr, nullptr, part, 1, is_swa, st));
+    else if (rows <= 8) BATTN_CK(battn_verify(g_battn, out, q, kvk, kvv, pos, nullptr, nullptr, part, rows, 1, is_swa, st));
+    else                BATTN_CK(battn_prefill(g_battn, out, q, kvk, kvv, pos, part, rows, is_swa, st));
+}
+
+/* launch_attn_ms (bruce.cu:4158; call :7720) with the merge folded in */
+static inline void launch_attn_ms(float* out, const float* q, const uint8_t* kvk, const uint8_t* kvv,
+                                  const int* pos, const int* kslot, const int* act, float* part, int rows,
+                                  int /*ns*/, int is_swa, cudaStream_t st) {
+    BATTN_CK(battn_decode(g_battn, out, q, kvk, kvv, pos, kslot, act, part, rows, is_swa, st));
+}
+
+/* --prefill-tc 0 / BRUCE_ATTN_M1PATH=0: the exact fp32 path, k_attn_rows + k_attn_combine_rows
+ * (bruce.cu:7735, 7753) */
+static inline void launch_attn_exact(float* out, const float* q, const uint8_t* kvk, const uint8_t* kvv,
+                                     const int* pos, float* part, int rows, int ns, int is_swa, cudaStream_t st) {
+    BATTN_CK(battn_attend_exact(g_battn, out, q, kvk, kvv, pos, nullptr, nullptr, part, 1, rows, ns, is_swa, st));
+}
+
+#endif /* BATTN_BRUCE_SHIM_H */

@@ -65,3 +65,22 @@ def test_layout_constants_match_reference():
     assert g.layer_bytes(False) == 262144 * 1088 and g.layer_bytes(True) == 8192 * 1088
     g8 = G_R.with_(slot_ctx=4096, n_slots=8)
     assert g8.slot_offset(3, False) == 3 * 4096 * 1088 and g8.slot_offset(3, True) == 3 * 2048 * 1088
+
+
+def test_reference_shim_header_compiles():
+    """include/battn_bruce_shim.h re-creates the reference's call surface over the C ABI."""
+    import shutil
+    import subprocess
+    import tempfile
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    with tempfile.TemporaryDirectory() as d:
+        src = os.path.join(d, "shim_check.cu")
+        with open(src, "w") as f:
+            f.write('#include "battn_bruce_shim.h"\n'
+                    "void use(float* o, const float* q, const uint8_t* k, const uint8_t* v, const int* p, float* part,\n"
+                    "         cudaStream_t st) { launch_attn_m(o, q, k, v, p, part, 1, 56, 0, st);\n"
+                    "  launch_attn_ms(o, q, k, v, p, p, p, part, 8, 7, 1, st); launch_attn_exact(o, q, k, v, p, part, 4, 8, 0, st); }\n")
+        r = subprocess.run([nvcc, "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-I",
+                            os.path.join(ROOT, "include"), "-c", src, "-o", os.path.join(d, "shim_check.o")],
+                           capture_output=True, text=True)
+        assert r.returncode == 0, r.stderr
