@@ -38,6 +38,7 @@ SIGNATURES = {
     "battn_exact_workspace_bytes": (_I, [_P, _I, _I, _I, _SZP]),
     "battn_kv_append": (_I, [_P] * 8 + [_I, _I, _I, _P]),
     "battn_decode": (_I, [_P] * 9 + [_I, _I, _P]),
+    "battn_decode_noalloc": (_I, [_P] * 8 + [_I, _I, _P]),
     "battn_verify": (_I, [_P] * 9 + [_I, _I, _I, _P]),
     "battn_prefill": (_I, [_P] * 7 + [_I, _I, _P]),
     "battn_attend_exact": (_I, [_P] * 9 + [_I, _I, _I, _I, _P]),

@@ -19,6 +19,10 @@ constexpr size_t SMEM_MAX = 226 * 1024;     // dynamic shared memory per CTA: th
 int g_init_cuda_error = 0;                  // cudaError_t of the last failing battn_init
 constexpr int FD_MAX_CTAS_PER_SM = 4;
 
+// Built-in split-K scratch of battn_decode_noalloc: part of the library image, one copy per device that
+// loads it.  In host code this name is only a handle for cudaGetSymbolAddress, never a device pointer.
+__device__ __align__(256) unsigned char g_noalloc_scratch[BATTN_NOALLOC_SCRATCH_BYTES];
+
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 inline int cuda_fail(battn_handle* h, cudaError_t e) {
@@ -236,6 +240,9 @@ int battn_init(const battn_geom* geom, int device, battn_handle** out_handle) {
     if (e == cudaSuccess) { h->num_sms = prop.multiProcessorCount; e = cudaMalloc(&h->d_status, 16); }
     if (e == cudaSuccess) e = cudaMemset(h->d_status, 0, 16);
     if (e == cudaSuccess) e = g.HD == 128 ? fd_prepare_all<128>(h) : fd_prepare_all<256>(h);
+    // device address of the built-in scratch on THIS device (it is current here)
+    h->noalloc_ws = nullptr;
+    if (e == cudaSuccess) e = cudaGetSymbolAddress(&h->noalloc_ws, g_noalloc_scratch);
     if (e != cudaSuccess) {
         g_init_cuda_error = (int)e;
         if (h->d_status) cudaFree(h->d_status);
@@ -309,6 +316,17 @@ int battn_decode(battn_handle* h, void* out, const void* q, const uint8_t* kvk, 
     if (rc) return rc;
     if (!ws) return BATTN_ERR_ARG;
     return launch_flash(h, out, nullptr, q, kvk, kvv, pos, kslot, act, ws, n_seq, 1, is_swa, (cudaStream_t)stream);
+}
+
+int battn_decode_noalloc(battn_handle* h, void* out, const void* q, const uint8_t* kvk, const uint8_t* kvv,
+                         const int* pos, const int* kslot, const int* act, int n_seq, int is_swa, void* stream) {
+    const int rc = check_seq_args(h, out, q, kvk, kvv, pos, kslot, n_seq, 1, 1);
+    if (rc) return rc;
+    if (!h->noalloc_ws) return BATTN_ERR_ARG;
+    // the built-in array is all the scratch there is: larger requests are refused, never truncated
+    if (fd_workspace(h, n_seq, 1).total > (size_t)BATTN_NOALLOC_SCRATCH_BYTES) return BATTN_ERR_CAPACITY;
+    return launch_flash(h, out, nullptr, q, kvk, kvv, pos, kslot, act, h->noalloc_ws, n_seq, 1, is_swa,
+                        (cudaStream_t)stream);
 }
 
 int battn_verify(battn_handle* h, void* out, const void* q, const uint8_t* kvk, const uint8_t* kvv, const int* pos,

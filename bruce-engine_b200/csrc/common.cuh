@@ -36,6 +36,7 @@ struct battn_handle {
     long long launches;
     cudaEvent_t* prof_ev;    // 2 * prof_cap events while profiling, else null
     int prof_cap, prof_n;
+    void* noalloc_ws;        // device address of the library's built-in scratch array on this device
     int fd_ctas_per_sm[3];   // resident CTAs per SM of the flash-decode kernel, per NT in {1,2,4}
     int fd_smem[3];
 };

@@ -129,6 +129,13 @@ class AttnEngine:
                                        _ptr(act), _ptr(part), rows_per_seq, rows, int(is_swa), st)
             self._check("battn_verify", rc)
 
+    def decode_noalloc(self, out, q, kvk, kvv, pos, kslot=None, act=None, is_swa: bool = False):
+        """Decode attention without a caller-provided `part` buffer: the scratch is a fixed array
+        inside the library (for hosts that cannot allocate device memory while serving)."""
+        rc = self.lib.battn_decode_noalloc(self.h, _ptr(out), _ptr(q), _ptr(kvk), _ptr(kvv), _ptr(pos),
+                                           _ptr(kslot), _ptr(act), pos.numel(), int(is_swa), self._stream())
+        self._check("battn_decode_noalloc", rc)
+
     def attn_exact(self, out, q, kvk, kvv, pos, part, n_seq: int, rows: int, nsplit: int, is_swa: bool = False,
                    kslot=None, act=None):
         """The exact fp32 path (k_attn / k_attn_rows / k_attn_m + k_attn_combine_rows)."""

@@ -116,6 +116,31 @@ int battn_decode(battn_handle* h, void* out, const void* q, const uint8_t* kvk, 
                  const int* pos, const int* kslot, const int* act, void* ws,
                  int n_seq, int is_swa, void* stream);
 
+/* Decode attention for callers that cannot hand the library a scratch buffer.  (This entry point has
+ * no counterpart in the reference, whose host always owns a `part` allocation.)
+ *
+ * Some hosts cannot call cudaMalloc once they are running: an inference server that gave every byte of
+ * HBM to its KV pool at start-up has nothing left to allocate from, and a latency-critical decode loop
+ * cannot afford the implicit device-wide synchronisation an allocation may cause.  For them this variant
+ * of battn_decode takes no `ws`: its split-K scratch is a fixed array of BATTN_NOALLOC_SCRATCH_BYTES that
+ * lives inside the library image, so every GPU that loads the library holds that much memory until the
+ * process exits.  The call itself allocates nothing, on the host or on the device.
+ *
+ *   - Same arguments, results and status codes as battn_decode, minus `ws`.
+ *   - battn_init() resolves the array's device address once for the handle's device (with that device
+ *     current), so there is no first-call set-up cost here; call battn_init outside stream capture.
+ *   - A call whose scratch need exceeds the array (about 175 sequences at 8 KV heads / head_dim 128,
+ *     about 100 at 4 KV heads / head_dim 256) is rejected with BATTN_ERR_CAPACITY before anything is
+ *     launched.
+ *   - All calls on a device share the one array and it keeps the previous call's contents.  The kernels
+ *     overwrite every word they later read, so nothing needs clearing between calls, but two calls that
+ *     overlap on the GPU (different streams, or different handles on the same device) race on it:
+ *     issue them on one stream or serialise them yourself. */
+#define BATTN_NOALLOC_SCRATCH_BYTES (4u << 20)
+int battn_decode_noalloc(battn_handle* h, void* out, const void* q, const uint8_t* kvk,
+                         const uint8_t* kvv, const int* pos, const int* kslot, const int* act,
+                         int n_seq, int is_swa, void* stream);
+
 /* Speculative-verify attention: `rows` (1..8) query rows at positions pos[i] .. pos[i]+rows-1 that
  * share one sweep over sequence i's KV and are causal among themselves:
  * launch_attn_m(rows 2..8) + k_attn_combine_rows (bruce.cu:3965-4019, 1999-2016; exact form
