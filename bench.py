@@ -47,7 +47,7 @@ POS_BYTES = 2176                      # K+V bytes per cached position per layer
 METRIC = "decode-attn HBM TB/s (ctx sweep 8K-256K, full + window-4096 layer per ctx)"
 # DRAM bytes (read + write) of one flash-decode launch at 256K from the ncu capture summarised in
 # profiles/; None until a capture exists
-NCU_TRAFFIC_256K = None
+NCU_TRAFFIC_256K = 570504448 + 4723968   # dram__bytes_read.sum + dram__bytes_write.sum, profiles/flash_decode_256k_ncu.md
 
 
 def visible(ctx: int, is_swa: bool) -> int:
@@ -255,10 +255,182 @@ class Layer:
         return h2d, self.h_out.numel() * 2
 
 
+PREFILL_PROMPT, PREFILL_CHUNK = 16384, 512
+
+
+def prefill_pairs(n_prompt: int, window: int | None) -> int:
+    """Unmasked (query, key) pairs of a causal (optionally windowed) prompt."""
+    if window is None or window >= n_prompt:
+        return n_prompt * (n_prompt + 1) // 2
+    return window * (window + 1) // 2 + (n_prompt - window) * window
+
+
+def bench_prefill(torch, AttnEngine, G_B, device, reps: int):
+    """BASELINE config 2: a 16,384-token prompt in 512-row chunks against a growing q8_0 cache, one
+    full-causal layer and one window-4096 layer; each chunk = append 512 K/V rows, then attend."""
+    g = G_B.with_(slot_ctx=PREFILL_PROMPT, window=WINDOW)
+    eng = AttnEngine(g, device)
+    dev = eng.device
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(7)
+    n_chunks = PREFILL_PROMPT // PREFILL_CHUNK
+    q = torch.randn((n_chunks, PREFILL_CHUNK, g.n_head, g.head_dim), generator=gen, device=dev).half()
+    k = torch.randn((n_chunks, PREFILL_CHUNK, g.n_kv, g.head_dim), generator=gen, device=dev)
+    v = torch.randn((n_chunks, PREFILL_CHUNK, g.n_kv, g.head_dim), generator=gen, device=dev)
+    out = torch.zeros((1, PREFILL_CHUNK, g.n_head, g.head_dim), dtype=torch.float16, device=dev)
+    part = eng.alloc_part(1, PREFILL_CHUNK)
+    pos = [torch.full((1,), c * PREFILL_CHUNK, dtype=torch.int32, device=dev) for c in range(n_chunks)]
+    flop_per_pair = 4 * g.head_dim * g.n_head
+    res = {}
+    for is_swa in (False, True):
+        kvk, kvv = eng.alloc_kv_layer(is_swa)
+
+        def prompt():
+            for c in range(n_chunks):
+                eng.qkv_prep_store(k[c:c + 1], v[c:c + 1], kvk, kvv, pos[c], rows=PREFILL_CHUNK, is_swa=is_swa)
+                eng.launch_attn_m(out, q[c:c + 1], kvk, kvv, pos[c], part, PREFILL_CHUNK, is_swa)
+
+        prompt()                                   # warm-up (also fills the cache)
+        torch.cuda.synchronize()
+        eng.profile_start(n_chunks * reps)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            prompt()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / reps
+        kms = eng.profile_stop()
+        pairs = prefill_pairs(PREFILL_PROMPT, WINDOW if is_swa else None)
+        flops = pairs * flop_per_pair
+        last = [kms[r * n_chunks + n_chunks - 1] for r in range(reps)]
+        c_last = n_chunks - 1
+        if is_swa:
+            pairs_last = PREFILL_CHUNK * WINDOW
+        else:
+            pairs_last = PREFILL_CHUNK * c_last * PREFILL_CHUNK + PREFILL_CHUNK * (PREFILL_CHUNK + 1) // 2
+        t_last = statistics.mean(last) * 1e-3
+        res["swa" if is_swa else "full"] = {
+            "prompt_ms": ms, "tflop": flops / 1e12, "TFLOPS": flops / (ms * 1e-3) / 1e12,
+            "prefill_tok_per_s": PREFILL_PROMPT / (ms * 1e-3),
+            "last_chunk_kernel_us": t_last * 1e6, "last_chunk_TFLOPS": pairs_last * flop_per_pair / t_last / 1e12}
+        del kvk, kvv
+    assert eng.device_status() == 0
+    return res
+
+
+def bench_serving_mix(torch, dist, AttnEngine, G_B, bd, local, rank, world, reps: int):
+    """BASELINE config 4a: 64 decode slots with context lengths uniform in [1K, 128K] (seed 0), slots dealt
+    to the ranks by length (no collective); one multi-slot decode call per rank per step."""
+    n_slots_total = 64
+    ctx = np.random.default_rng(0).integers(1024, 131073, size=n_slots_total)
+    mine = bd.balance_slots(ctx, world)[rank]
+    cap = 131072
+    g = G_B.with_(slot_ctx=cap, window=WINDOW, n_slots=max(1, len(mine)))
+    eng = AttnEngine(g, local)
+    dev = eng.device
+    kvk, kvv = eng.alloc_kv_layer(False)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(1000 + rank)
+    kb = torch.randn((1, 512, g.n_kv, g.head_dim), generator=gen, device=dev)
+    vb = torch.randn((1, 512, g.n_kv, g.head_dim), generator=gen, device=dev)
+    pos1 = torch.zeros(1, dtype=torch.int32, device=dev)
+    ks1 = torch.zeros(1, dtype=torch.int32, device=dev)
+    for j, s in enumerate(mine):                    # the same random 512-row block fills every chunk
+        ks1.fill_(j)
+        for a in range(0, int(ctx[s]), 512):
+            n = min(512, int(ctx[s]) - a)
+            pos1.fill_(a)
+            eng.qkv_prep_store(kb[:, :n], vb[:, :n], kvk, kvv, pos1, kslot=ks1, rows=n)
+    n = len(mine)
+    pos = torch.tensor([int(ctx[s]) - 1 for s in mine], dtype=torch.int32, device=dev)
+    kslot = torch.arange(n, dtype=torch.int32, device=dev)
+    q = torch.randn((n, 1, g.n_head, g.head_dim), generator=gen, device=dev).half()
+    out = torch.zeros_like(q)
+    part = eng.alloc_part(max(1, n), 1)
+
+    def step():
+        if n:
+            eng.launch_attn_ms(out, q, kvk, kvv, pos, kslot, None, part, n, False)
+
+    for _ in range(3):
+        step()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / reps
+    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_max = float(t.item())
+    total_bytes = int(ctx.sum()) * POS_BYTES
+    assert eng.device_status() == 0
+    return {"slots": n_slots_total, "ctx_sum": int(ctx.sum()), "bytes": total_bytes, "ms_per_step": ms_max,
+            "TBps": total_bytes / (ms_max * 1e-3) / 1e12, "tok_per_s": n_slots_total / (ms_max * 1e-3),
+            "rank0_ms": ms, "rank0_slots": n, "rank0_bytes": int(sum(int(ctx[s]) for s in mine)) * POS_BYTES,
+            "scaling": "strong (64 slots dealt over the ranks by context length)"}
+
+
+def bench_seq_split(torch, dist, AttnEngine, G_B, bd, local, rank, world, reps: int):
+    """BASELINE config 4b: one 1,048,576-token sequence, KV split evenly by position range over the
+    ranks; decode = local partials + all-gather of (o, m, l) records + merge."""
+    n_total = 1 << 20
+    sh = bd.shard_of(n_total, rank, world)
+    g = G_B.with_(slot_ctx=sh.capacity, window=WINDOW)
+    eng = AttnEngine(g, local)
+    dev = eng.device
+    kvk, kvv = eng.alloc_kv_layer(False)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(2000 + rank)
+    kb = torch.randn((1, 512, g.n_kv, g.head_dim), generator=gen, device=dev)
+    vb = torch.randn((1, 512, g.n_kv, g.head_dim), generator=gen, device=dev)
+    pos1 = torch.zeros(1, dtype=torch.int32, device=dev)
+    for a in range(0, sh.capacity, 512):
+        pos1.fill_(a)
+        eng.qkv_prep_store(kb, vb, kvk, kvv, pos1, rows=min(512, sh.capacity - a))
+    q = torch.randn((1, g.n_head, g.head_dim), generator=gen, device=dev).half()
+    if world > 1:
+        dist.broadcast(q, 0)
+    out = torch.zeros_like(q)
+    if world > 1:
+        dec = bd.SeqSplitDecoder(eng, n_total)
+        step = lambda: dec.decode(out, q, kvk, kvv, n_total - 1, 1)          # noqa: E731
+    else:
+        part = eng.alloc_part(1, 1)
+        pos = torch.tensor([n_total - 1], dtype=torch.int32, device=dev)
+        step = lambda: eng.launch_attn_m(out, q, kvk, kvv, pos, part, 1, False)  # noqa: E731
+    for _ in range(3):
+        step()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / reps], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    assert eng.device_status() == 0
+    return {"tokens": n_total, "bytes": n_total * POS_BYTES, "ms_per_step": ms,
+            "TBps": n_total * POS_BYTES / (ms * 1e-3) / 1e12, "exchange_bytes_per_rank": g.n_head * (g.head_dim + 2) * 4,
+            "scaling": "strong (position range split evenly, NCCL all-gather of the split records)"}
+
+
 def run_gpu(args):
     import torch
     import torch.distributed as dist
 
+    from bruce_engine_b200 import dist as bd
     from bruce_engine_b200.engine import AttnEngine
     from bruce_engine_b200.layout import G_B
 
@@ -273,7 +445,11 @@ def run_gpu(args):
 
     gen = torch.Generator(device=f"cuda:{local}")
     gen.manual_seed(1000 + rank)                   # every rank serves its own sequence
-    layers = [Layer(c, s, gen, torch, AttnEngine, G_B, local) for c in CTXS for s in (False, True)]
+    ctxs = [args.only_ctx] if args.only_ctx else CTXS
+    if args.case == "prefill":                      # light run for profiling the prompt-chunk kernel
+        print(json.dumps({"prefill": bench_prefill(torch, AttnEngine, G_B, local, max(1, args.steps))}))
+        return 0
+    layers = [Layer(c, s, gen, torch, AttnEngine, G_B, local) for c in ctxs for s in (False, True)]
     torch.cuda.synchronize()
 
     def step():
@@ -312,7 +488,13 @@ def run_gpu(args):
     l0 = sum(L.eng.launch_count() for L in layers)
     step()
     launches_per_step = sum(L.eng.launch_count() for L in layers) - l0
-    graph = capture(step)
+
+    class _Eager:                                   # --light: no graph, the step is launched eagerly
+        @staticmethod
+        def replay():
+            step()
+
+    graph = _Eager if args.light else capture(step)
 
     # ---- device-resident timed region: K graph replays of the step ------------------------------------
     for _ in range(W):
@@ -338,6 +520,14 @@ def run_gpu(args):
         step()
     barrier()
     kernel_ms = {(L.ctx, L.is_swa): L.eng.profile_stop() for L in layers}
+
+    if args.light:                                  # profiling run: kernel timings only
+        if rank == 0:
+            print(json.dumps({"light": True, "ms_per_step": ms / K, "kernel_us": {
+                f"{c}{'_swa' if w else ''}": statistics.mean(v) * 1e3 for (c, w), v in kernel_ms.items()}}))
+        if world > 1:
+            dist.destroy_process_group()
+        return 0
 
     # ---- end-to-end timed region: host buffers, copies inside, one graph replay + host sync per step ------
     def e2e_enqueue():
@@ -366,7 +556,7 @@ def run_gpu(args):
     ms_e2e = max_over_ranks(e0.elapsed_time(e1))
 
     status = sum(L.eng.device_status() for L in layers)
-    sb = step_bytes(CTXS)
+    sb = step_bytes(ctxs)
     value = world * K * sb / (ms * 1e-3) / 1e12
     e2e_value = world * K * sb / (ms_e2e * 1e-3) / 1e12
     h2d = sum(L.e2e_bytes()[0] for L in layers)
@@ -374,14 +564,14 @@ def run_gpu(args):
 
     peak, peak_kind = measured_peak()
     sweep = []
-    for c in CTXS:
+    for c in ctxs:
         tf = statistics.mean(kernel_ms[(c, False)]) * 1e-3
         ts = statistics.mean(kernel_ms[(c, True)]) * 1e-3
         sweep.append({"ctx": c, "full_us": tf * 1e6, "full_TBps": c * POS_BYTES / tf / 1e12,
                       "full_frac_of_peak": c * POS_BYTES / tf / 1e9 / peak,
                       "swa_us": ts * 1e6, "swa_TBps": visible(c, True) * POS_BYTES / ts / 1e12,
                       "attn_tok_per_s_layer_pair": 1.0 / (tf + ts)})
-    top = CTXS[-1]
+    top = ctxs[-1]
     t_top = statistics.mean(kernel_ms[(top, False)]) * 1e-3
     alg_bytes = top * POS_BYTES + 2 * 32 * 128 * 2
     achieved = alg_bytes / t_top / 1e9
@@ -391,6 +581,23 @@ def run_gpu(args):
                 "frac_of_nominal_8TBps": achieved / 8000.0, "launch_us": t_top * 1e6,
                 "algorithmic_bytes_per_launch": alg_bytes, "traffic": NCU_TRAFFIC_256K}
 
+    del layers, graph, graph_e2e
+    torch.cuda.empty_cache()
+    serving = bench_serving_mix(torch, dist, AttnEngine, G_B, bd, local, rank, world, 20)
+    torch.cuda.empty_cache()
+    seqsplit = bench_seq_split(torch, dist, AttnEngine, G_B, bd, local, rank, world, 20)
+    torch.cuda.empty_cache()
+    prefill = bench_prefill(torch, AttnEngine, G_B, local, 2) if rank == 0 else None
+    if prefill is not None:
+        bf16_peak = None
+        try:
+            with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+                bf16_peak = float(json.load(f)["bf16_tflops_sustained"])
+        except Exception:
+            bf16_peak = 1400.0
+        for kind in prefill.values():
+            kind["frac_of_measured_dense_bf16_sustained"] = kind["TFLOPS"] / bf16_peak
+            kind["frac_of_nominal_dense_fp16_2250"] = kind["TFLOPS"] / 2250.0
     if rank == 0:
         cpu = cpu_baseline() if world == 1 else None
         line = {
@@ -405,7 +612,8 @@ def run_gpu(args):
                        "launch": "one CUDA graph per step (12 decode calls through the C ABI), replayed K times"},
             "e2e": {"value": e2e_value, "unit": "TB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": ms_e2e / K},
-            "gpu_launches": launches, "roofline": roofline, "sweep": sweep, "clocks": clocks,
+            "gpu_launches": launches, "roofline": roofline, "sweep": sweep, "prefill": prefill, "serving_mix_64_slots": serving, "seq_split_1m": seqsplit,
+            "clocks": clocks,
             "device_status": status,
         }
         if cpu is not None:
@@ -422,6 +630,9 @@ def main():
     ap.add_argument("--steps", type=int, default=500)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--light", action="store_true", help="profiling run: eager launches, kernel timings only")
+    ap.add_argument("--only-ctx", type=int, default=0, help="restrict the decode sweep to one context")
+    ap.add_argument("--case", default="decode", choices=["decode", "prefill"], help="light run of one kernel family")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)

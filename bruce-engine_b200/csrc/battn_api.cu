@@ -121,8 +121,8 @@ int launch_exact(battn_handle* h, void* out, float* rec_out, const void* q, cons
     M.count = nsplit; M.log2_domain = 0; M.out_f16 = g.out_f16;
     M.pos = pos; M.kslot = kslot; M.act = act; M.is_swa = is_swa; M.W = g.W; M.slot_ctx = g.slot_ctx;
     M.n_slots = g.n_slots; M.status = h->d_status; M.hdr = nullptr;
-    if (g.HD == 128) k_merge<128><<<n_seq * rows * g.Hq, 64, 0, st>>>(M);
-    else             k_merge<256><<<n_seq * rows * g.Hq, 128, 0, st>>>(M);
+    if (g.HD == 128) k_merge<128><<<n_seq * rows * g.Hq, MERGE_THREADS, 0, st>>>(M);
+    else             k_merge<256><<<n_seq * rows * g.Hq, MERGE_THREADS, 0, st>>>(M);
     h->launches += 2;
     const cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? BATTN_OK : cuda_fail(h, e);
@@ -173,8 +173,8 @@ int launch_flash(battn_handle* h, void* out, float* rec_out, const void* q, cons
     M.mode = MERGE_BALANCED; M.part = P.part; M.out = out; M.rec_out = rec_out;
     M.n_rows = n_seq * rows; M.rows = rows; M.Hq = g.Hq; M.Hkv = g.Hkv; M.G = g.G;
     M.count = 0; M.log2_domain = 1; M.out_f16 = g.out_f16; M.hdr = P.hdr; M.status = h->d_status;
-    if (g.HD == 128) k_merge<128><<<n_seq * rows * g.Hq, 64, 0, st>>>(M);
-    else             k_merge<256><<<n_seq * rows * g.Hq, 128, 0, st>>>(M);
+    if (g.HD == 128) k_merge<128><<<n_seq * rows * g.Hq, MERGE_THREADS, 0, st>>>(M);
+    else             k_merge<256><<<n_seq * rows * g.Hq, MERGE_THREADS, 0, st>>>(M);
     h->launches += 2;
     e = cudaGetLastError();
     return e == cudaSuccess ? BATTN_OK : cuda_fail(h, e);
@@ -371,14 +371,15 @@ int battn_attend_exact(battn_handle* h, void* out, const void* q, const uint8_t*
 
 int battn_merge(battn_handle* h, void* out, const float* parts, int n_parts, int n_rows, void* stream) {
     if (!h || !out || !parts || n_parts < 1 || n_rows < 1) return BATTN_ERR_ARG;
+    if (n_parts > MERGE_MAX_COUNT) return BATTN_ERR_CAPACITY;
     const Geom& g = h->g;
     MergeParams M{};
     M.mode = MERGE_GATHERED; M.part = parts; M.out = out; M.rec_out = nullptr;
     M.n_rows = n_rows; M.rows = 1; M.Hq = g.Hq; M.Hkv = g.Hkv; M.G = g.G;
     M.count = n_parts; M.log2_domain = 0; M.out_f16 = g.out_f16; M.status = h->d_status;
     cudaStream_t st = (cudaStream_t)stream;
-    if (g.HD == 128) k_merge<128><<<n_rows * g.Hq, 64, 0, st>>>(M);
-    else             k_merge<256><<<n_rows * g.Hq, 128, 0, st>>>(M);
+    if (g.HD == 128) k_merge<128><<<n_rows * g.Hq, MERGE_THREADS, 0, st>>>(M);
+    else             k_merge<256><<<n_rows * g.Hq, MERGE_THREADS, 0, st>>>(M);
     h->launches += 1;
     const cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? BATTN_OK : cuda_fail(h, e);

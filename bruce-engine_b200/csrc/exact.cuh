@@ -126,12 +126,22 @@ struct MergeParams {
     const int* hdr;
 };
 
+constexpr int MERGE_THREADS = 256;
+constexpr int MERGE_MAX_COUNT = 1024;     // records merged per (row, head)
+
+// One block per (row, head).  The records are read in three block-wide phases (max, weights and
+// denominator, weighted sum) with every load independent of the others, so the latency of the record
+// reads is paid a few times per block instead of once per split.
 template <int HD>
-__global__ void __launch_bounds__(HD / 2) k_merge(const MergeParams P) {
+__global__ void __launch_bounds__(MERGE_THREADS) k_merge(const MergeParams P) {
+    __shared__ float s_m[MERGE_MAX_COUNT];       // m_s, then the weight w_s
+    __shared__ float s_l[MERGE_MAX_COUNT];
+    __shared__ float s_red[MERGE_THREADS / 32];
+    __shared__ float2 s_acc[MERGE_THREADS];
     const int hq = blockIdx.x % P.Hq, rowidx = blockIdx.x / P.Hq;
     const int i = rowidx / P.rows, r = rowidx % P.rows;
     const int kvh = hq / P.G, h = hq % P.G;
-    const int d2 = threadIdx.x * 2;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const float* base;
     size_t stride;
     int count;
@@ -158,17 +168,54 @@ __global__ void __launch_bounds__(HD / 2) k_merge(const MergeParams P) {
         base = P.part + ((size_t)(clo + item) * RG + r * P.G + h) * (size_t)(HD + 2);
         stride = (size_t)RG * (HD + 2);
     }
-    float M = NEG_BIG;
-    for (int s = 0; s < count; ++s) M = fmaxf(M, base[s * stride + HD]);
-    float L = 0.f, a0 = 0.f, a1 = 0.f;
-    for (int s = 0; s < count; ++s) {
-        const float* b = base + s * stride;
-        const float w = P.log2_domain ? fast_exp2(b[HD] - M) : __expf(b[HD] - M);   // bruce.cu:1000
-        L = fmaf(b[HD + 1], w, L);
-        const float2 o = *reinterpret_cast<const float2*>(b + d2);
+    count = min(count, MERGE_MAX_COUNT);
+
+    // phase 1: (m, l) of every record, block max of m
+    float mx = NEG_BIG;
+    for (int s = tid; s < count; s += MERGE_THREADS) {
+        const float2 ml = *reinterpret_cast<const float2*>(base + s * stride + HD);
+        s_m[s] = ml.x; s_l[s] = ml.y;
+        mx = fmaxf(mx, ml.x);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if (lane == 0) s_red[warp] = mx;
+    __syncthreads();
+    float M = s_red[0];
+#pragma unroll
+    for (int w = 1; w < MERGE_THREADS / 32; ++w) M = fmaxf(M, s_red[w]);
+    __syncthreads();
+    // phase 2: weights w_s = e^(m_s - M) and the denominator sum w_s l_s   (bruce.cu:1000-1001)
+    float ls = 0.f;
+    for (int s = tid; s < count; s += MERGE_THREADS) {
+        const float w = P.log2_domain ? fast_exp2(s_m[s] - M) : __expf(s_m[s] - M);
+        s_m[s] = w;
+        ls = fmaf(s_l[s], w, ls);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ls += __shfl_xor_sync(0xffffffffu, ls, o);
+    if (lane == 0) s_red[warp] = ls;
+    __syncthreads();
+    float L = 0.f;
+#pragma unroll
+    for (int w = 0; w < MERGE_THREADS / 32; ++w) L += s_red[w];
+    // phase 3: weighted sum of o; HD/2 dim pairs x NG interleaved groups of records
+    constexpr int NDP = HD / 2, NG = MERGE_THREADS / NDP;
+    const int dp = tid % NDP, grp = tid / NDP;
+    float a0 = 0.f, a1 = 0.f;
+#pragma unroll 4
+    for (int s = grp; s < count; s += NG) {
+        const float2 o = *reinterpret_cast<const float2*>(base + s * stride + 2 * dp);
+        const float w = s_m[s];
         a0 = fmaf(o.x, w, a0);
         a1 = fmaf(o.y, w, a1);
     }
+    s_acc[tid] = make_float2(a0, a1);
+    __syncthreads();
+    if (grp != 0) return;
+#pragma unroll
+    for (int g2 = 1; g2 < NG; ++g2) { a0 += s_acc[g2 * NDP + dp].x; a1 += s_acc[g2 * NDP + dp].y; }
+    const int d2 = 2 * dp;
     if (P.out) {
         const float il = L > 0.f ? 1.f / L : 0.f;
         const size_t oi = ((size_t)rowidx * P.Hq + hq) * HD + d2;
@@ -178,7 +225,7 @@ __global__ void __launch_bounds__(HD / 2) k_merge(const MergeParams P) {
     if (P.rec_out) {
         float* ro = P.rec_out + ((size_t)rowidx * P.Hq + hq) * (size_t)(HD + 2);
         *reinterpret_cast<float2*>(ro + d2) = make_float2(a0, a1);
-        if (threadIdx.x == 0) {
+        if (dp == 0) {
             ro[HD] = (P.log2_domain && M > -1e29f) ? M * LN2 : M;
             ro[HD + 1] = L;
         }

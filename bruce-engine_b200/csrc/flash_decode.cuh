@@ -109,33 +109,43 @@ k_flash_decode(const Params P) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
     // ---- every CTA derives the same work cut from the device-resident positions -------------------
-    for (int i = tid; i < P.n_seq; i += NTHREADS) {
-        const SeqRange sr = seq_range(P.pos, P.kslot, P.act, i, P.rows, P.is_swa, P.W, P.slot_ctx, P.n_slots, P.status);
-        cum[i + 1] = sr.active ? ((sr.hi + TILE - 1) / TILE - sr.lo / TILE) : 0;
-    }
     if (tid == 0) {
-        cum[0] = 0;
         s_abort = 0;
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], NW); }
         mbar_fence_init();
     }
-    __syncthreads();
-    if (warp == 0) {
-        int carry = 0;
-        for (int base = 0; base < P.n_seq; base += 32) {
-            const int idx = base + lane;
-            int v = idx < P.n_seq ? cum[idx + 1] : 0;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const int t = __shfl_up_sync(0xffffffffu, v, o);
-                if (lane >= o) v += t;
-            }
-            v += carry;
-            if (idx < P.n_seq) cum[idx + 1] = v;
-            carry = __shfl_sync(0xffffffffu, v, 31);
+    if (P.n_seq == 1) {
+        // one sequence (decode / verify of a single stream): no prefix sum, one barrier
+        if (tid == 0) {
+            const SeqRange sr = seq_range(P.pos, P.kslot, P.act, 0, P.rows, P.is_swa, P.W, P.slot_ctx, P.n_slots, P.status);
+            cum[0] = 0;
+            cum[1] = sr.active ? ((sr.hi + TILE - 1) / TILE - sr.lo / TILE) : 0;
         }
+        __syncthreads();
+    } else {
+        for (int i = tid; i < P.n_seq; i += NTHREADS) {
+            const SeqRange sr = seq_range(P.pos, P.kslot, P.act, i, P.rows, P.is_swa, P.W, P.slot_ctx, P.n_slots, P.status);
+            cum[i + 1] = sr.active ? ((sr.hi + TILE - 1) / TILE - sr.lo / TILE) : 0;
+        }
+        if (tid == 0) cum[0] = 0;
+        __syncthreads();
+        if (warp == 0) {
+            int carry = 0;
+            for (int base = 0; base < P.n_seq; base += 32) {
+                const int idx = base + lane;
+                int v = idx < P.n_seq ? cum[idx + 1] : 0;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int t = __shfl_up_sync(0xffffffffu, v, o);
+                    if (lane >= o) v += t;
+                }
+                v += carry;
+                if (idx < P.n_seq) cum[idx + 1] = v;
+                carry = __shfl_sync(0xffffffffu, v, 31);
+            }
+        }
+        __syncthreads();
     }
-    __syncthreads();
     const int total = P.Hkv * cum[P.n_seq];
     const int per = max(1, (total + (int)gridDim.x - 1) / (int)gridDim.x);
     if (blockIdx.x == 0) {
