@@ -124,6 +124,17 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
         if (mbar_try_wait(bar, parity)) return true;
     return false;
 }
+// Bounded wait with back-off: idle roles sleep between polls instead of flooding the issue slots and the
+// shared-memory pipe that the working warps need.
+__device__ __forceinline__ bool mbar_wait_backoff(uint64_t* bar, uint32_t parity, uint32_t sleep_ns = 100,
+                                                  uint32_t limit = (1u << 22)) {
+    if (mbar_try_wait(bar, parity)) return true;
+    for (uint32_t i = 0; i < limit; ++i) {
+        __nanosleep(sleep_ns);
+        if (mbar_try_wait(bar, parity)) return true;
+    }
+    return false;
+}
 // global -> shared bulk copy; dst, src 16-byte aligned, bytes a multiple of 16
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
     asm volatile(

@@ -4,21 +4,26 @@
 // Behaviour replaced: k_attn_tc_rs_opt<NW,...> for rows > 8 and its dispatch
 // (engine/src/bruce.cu:2750-3131, 4021-4078); masks as bruce.cu:2799-2805, 3012-3029.
 //
-// Design (sm_100a), one CTA per (128-row M tile, kv head):
+// Design (sm_100a), one CTA per (128-row M tile, kv head), 17 warps (8 softmax, 4 K-dequant, 4 V-dequant, 1 control):
 //   * M tile = 128/G consecutive query positions x the G query heads of one kv head (row m = position
 //     m / G, head m % G, the reference's pair packing, bruce.cu:2288-2296): every dequantised K/V tile
 //     serves all G heads, and the causal diagonal of a tile spans only 128/G positions.
 //   * One control thread streams raw K and V tiles (BN records each, one contiguous run per tile because
 //     the cache is head-major) with cp.async.bulk into a double buffer and issues every tcgen05.mma.
-//   * Four dequant warps turn raw q8_0 records into fp16 operands in 128-byte-swizzled K-major shared
+//   * Two groups of four dequant warps (one for K, one for V, running in parallel) turn raw q8_0 records into fp16 operands in 128-byte-swizzled K-major shared
 //     memory: K as [key][dim], V transposed to [dim][key] with byte-permute interleaves, scale folded in.
 //   * S = Q K^T (M 128, N BN, K head_dim) and O += P V (M 128, N head_dim, K BN) run as tcgen05.mma with
 //     fp32 accumulators in tensor memory: O plus two S buffers, so S of tile j+1 is computed while the
 //     softmax warps work on tile j.
-//   * Four softmax warps own one accumulator row per thread (TMEM lane = row): row max and row sum need
-//     no shuffles.  P goes to shared memory as the fp16 A operand of the second MMA.  O is rescaled in
-//     TMEM only when a row maximum grows by more than 2^8 (the reference value is kept otherwise, the
-//     final normalisation uses the same reference, so the result is unchanged).
+//   * Eight softmax warps: TMEM lane = accumulator row, two threads per row (one per half of the S
+//     columns), so the row max needs one exchange through shared memory and no shuffles.  P never
+//     leaves tensor memory: each thread overwrites the S columns it has just read with its fp16 P
+//     values, and the second MMA takes its A operand from there (S is double-buffered, so P is too and
+//     the softmax warps can run a tile ahead of the P.V MMA).  The softmax denominator is not summed by
+//     the warps at all: a block of ones appended to the V operand makes the tensor core accumulate
+//     sum(P) in fp32 next to O, from exactly the fp16-rounded P it multiplies with V.  O (and that sum)
+//     are rescaled in TMEM only when a row maximum grows by more than 2^8 (the reference value is kept
+//     otherwise and the final normalisation uses the same reference, so the result is unchanged).
 //   * Row n of the K operand / column n of S holds key kappa(n), a fixed permutation inside each 64-key
 //     span chosen so that every shared-memory access of the dequant warps is bank-conflict free.
 //   * Every mbarrier wait is bounded; a wait that runs out sets the device status word, the remaining
@@ -29,7 +34,8 @@
 namespace battn {
 namespace pf {
 
-constexpr int NTHREADS = 288;     // warps 0-3 softmax, 4-7 dequant, warp 8 control
+constexpr int NSOFT = 256, NDEQ = 128;              // NDEQ threads dequantise K, another NDEQ dequantise V
+constexpr int NTHREADS = NSOFT + 2 * NDEQ + 32;     // warps 0-7 softmax, 8-11 K dequant, 12-15 V dequant, 16 control
 constexpr int TMEM_COLS = 512;
 constexpr float RESCALE_THRESHOLD = 8.0f;   // log2 units
 
@@ -52,21 +58,23 @@ struct Cfg {
     static constexpr int Q_BYTES = 128 * HD * 2;
     static constexpr int K_BYTES = BN * HD * 2;
     static constexpr int V_BYTES = HD * BN * 2;
-    static constexpr int P_BYTES = 128 * BN * 2;
     static constexpr int RAW_BYTES = BN * REC;              // one raw K (or V) tile
     static constexpr int OFF_Q = 0;
     static constexpr int OFF_K = OFF_Q + Q_BYTES;
     static constexpr int OFF_V = OFF_K + K_BYTES;
-    static constexpr int OFF_P = OFF_V + V_BYTES;
-    static constexpr int OFF_RAW = OFF_P + P_BYTES;          // [2 buffers][K | V]
+    static constexpr int ONES_BYTES = 16 * BN * 2;           // 16 operand rows of ones: the denominator MMA
+    static constexpr int OFF_ONES = OFF_V + V_BYTES;
+    static constexpr int OFF_RAW = OFF_ONES + ONES_BYTES;    // [2 buffers][K | V]
     static constexpr int OFF_BAR = OFF_RAW + 4 * RAW_BYTES;
     static constexpr int N_BARS = 12;
     static constexpr int OFF_MISC = OFF_BAR + N_BARS * 8;    // tmem base, abort flag
-    static constexpr int TOTAL = OFF_MISC + 16 + 1024;       // + slack to align the base to 1024
+    static constexpr int OFF_RMAX = OFF_MISC + 16;           // [tile parity][2 halves][128 rows] row maxima
+    static constexpr int TOTAL = OFF_RMAX + 2 * 2 * 128 * 4 + 1024;   // + slack to align the base to 1024
     static constexpr int T_O = 0;                            // TMEM columns
-    static constexpr int T_S0 = HD;
-    static constexpr int T_S1 = HD + BN;
-    static_assert(HD + 2 * BN <= TMEM_COLS, "tensor memory budget");
+    static constexpr int T_L = HD;                           // 16 columns, each = sum of P
+    static constexpr int T_S0 = HD + 32;
+    static constexpr int T_S1 = HD + 32 + BN;
+    static_assert(HD + 32 + 2 * BN <= TMEM_COLS, "tensor memory budget");
     static_assert(RAW_BYTES % 16 == 0, "bulk copy size");
     static_assert((HD == 128 && BN == 128) || (HD == 256 && BN == 64), "supported tile shapes");
 };
@@ -102,6 +110,14 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t adesc, uint64
         ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
         : "memory");
 }
+// same, with the A operand in tensor memory (fp16 pairs packed in 32-bit columns, lane = row)
+__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(acc)
+        : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                  : "memory");
@@ -132,21 +148,54 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
           "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]), "r"(taddr)
         : "memory");
 }
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%16], {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15};"
+        ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+          "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(taddr)
+        : "memory");
+}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// single-column TMEM access (the denominator column)
+__device__ __forceinline__ uint32_t tmem_ld1(uint32_t taddr) {
+    uint32_t r;
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(r) : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    return r;
+}
+__device__ __forceinline__ void tmem_st1(uint32_t taddr, uint32_t r) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(taddr), "r"(r) : "memory");
+}
+// 32 columns without the wait, so several loads can be in flight
+__device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 template <int HD, int BN>
 __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const Params P) {
     using C = Cfg<HD, BN>;
     constexpr int NBLK = C::NBLK, REC = C::REC;
+    constexpr int HC = BN / 2;                               // S columns per softmax thread
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);      // 1024-byte aligned
     uint8_t* Qsm = smem + C::OFF_Q;
     uint8_t* Ksm = smem + C::OFF_K;
     uint8_t* Vsm = smem + C::OFF_V;
-    uint8_t* Psm = smem + C::OFF_P;
+    uint8_t* ONES = smem + C::OFF_ONES;
     uint8_t* RAW = smem + C::OFF_RAW;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
     volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(smem + C::OFF_MISC);   // [0] tmem base, [1] abort
+    volatile float* rmax = reinterpret_cast<volatile float*>(smem + C::OFF_RMAX);          // [2][2][128]
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = P.G, MR = 128 / G;                        // query positions per M tile
@@ -167,17 +216,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const Params P) {
     const int tile_first = lo_cta / BN;
     const int n_tiles = (hi_cta + BN - 1) / BN - tile_first;
 
-    // ---- set-up: barriers, tensor memory, the Q operand ---------------------------------------------
+    // ---- set-up: barriers, tensor memory, the Q operand, the block of ones ---------------------------
     if (tid == 0) {
         mbar_init(&bars[B_RAW_FULL0], 1); mbar_init(&bars[B_RAW_FULL1], 1);
-        mbar_init(&bars[B_RAW_FREE0], 4); mbar_init(&bars[B_RAW_FREE1], 4);
-        mbar_init(&bars[B_KF], 4); mbar_init(&bars[B_VF], 4);
+        mbar_init(&bars[B_RAW_FREE0], 2 * NDEQ / 32); mbar_init(&bars[B_RAW_FREE1], 2 * NDEQ / 32);
+        mbar_init(&bars[B_KF], NDEQ / 32); mbar_init(&bars[B_VF], NDEQ / 32);
         mbar_init(&bars[B_S0], 1); mbar_init(&bars[B_S1], 1);
-        mbar_init(&bars[B_P], 4); mbar_init(&bars[B_PV], 1);
+        mbar_init(&bars[B_P], NSOFT / 32); mbar_init(&bars[B_PV], 1);
         misc[1] = 0;
         mbar_fence_init();
     }
-    if (warp == 8) {
+    if (warp == NTHREADS / 32 - 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                          smem_u32(const_cast<uint32_t*>(&misc[0]))), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -199,6 +248,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const Params P) {
         }
         *reinterpret_cast<uint4*>(Qsm + (ch >> 3) * (128 * 128) + sw128(m, ch & 7)) = val;
     }
+    for (int idx = tid; idx < C::ONES_BYTES / 16; idx += NTHREADS)
+        reinterpret_cast<uint4*>(ONES)[idx] = make_uint4(0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u);
     proxy_fence();
     tc_fence_before();
     __syncthreads();
@@ -208,7 +259,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const Params P) {
     // bounded wait that degrades to "do not wait" once any wait has run out
     auto wait = [&](int b, uint32_t parity) {
         if (misc[1]) return;
-        if (!mbar_wait_bounded(&bars[b], parity)) {
+        if (!mbar_wait_backoff(&bars[b], parity)) {
             atomicOr(P.status, BATTN_DEV_WAIT_TIMEOUT);
             misc[1] = 1;
         }
@@ -216,7 +267,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const Params P) {
 
     const size_t hb = (size_t)kvh * P.pstride * (size_t)REC;
 
-    if (warp == 8) {
+    if (warp == NTHREADS / 32 - 1) {
         // ======================= control thread: bulk copies and every MMA ===========================
         if (lane == 0) {
             auto load_raw = [&](int j) {
@@ -232,8 +283,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const Params P) {
             load_raw(0);
             if (n_tiles > 1) load_raw(1);
 
-            const uint32_t idS = umma_idesc(128, BN), idO = umma_idesc(128, HD);
-            const uint32_t qa = smem_u32(Qsm), ka = smem_u32(Ksm), va = smem_u32(Vsm), pa = smem_u32(Psm);
+            const uint32_t idS = umma_idesc(128, BN), idO = umma_idesc(128, HD), idL = umma_idesc(128, 16);
+            const uint32_t qa = smem_u32(Qsm), ka = smem_u32(Ksm), va = smem_u32(Vsm);
+            const uint32_t oa = smem_u32(ONES);
             auto issue_S = [&](int j) {
                 const uint32_t d = tmem + ((j & 1) ? C::T_S1 : C::T_S0);
 #pragma unroll
@@ -256,11 +308,16 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const Params P) {
                 wait(B_P, j & 1);
                 wait(B_VF, j & 1);
                 tc_fence_after();
+                const uint32_t tP = tmem + ((j & 1) ? C::T_S1 : C::T_S0);     // P overwrote the S tile
 #pragma unroll
                 for (int ks = 0; ks < BN / 16; ++ks) {
-                    const uint64_t a = umma_desc(pa + (ks >> 2) * (128 * 128)) + 2 * (ks & 3);
+                    const uint32_t acc = (j > 0 || ks > 0) ? 1u : 0u;
+                    // keys of column half hf sit in 32-bit columns [hf*BN/2, hf*BN/2 + BN/4): 8 per k-step
+                    const uint32_t a = tP + (ks / (BN / 32)) * (BN / 2) + 8 * (ks % (BN / 32));
                     const uint64_t b = umma_desc(va + (ks >> 2) * (HD * 128)) + 2 * (ks & 3);
-                    umma_f16(tmem + C::T_O, a, b, idO, (j > 0 || ks > 0) ? 1u : 0u);
+                    const uint64_t o = umma_desc(oa + (ks >> 2) * (16 * 128)) + 2 * (ks & 3);
+                    umma_f16_ts(tmem + C::T_O, a, b, idO, acc);
+                    umma_f16_ts(tmem + C::T_L, a, o, idL, acc);             // every column = sum of P
                 }
                 umma_commit(&bars[B_PV]);
                 if (j + 2 < n_tiles) {
@@ -269,28 +326,79 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const Params P) {
                 }
             }
         }
-    } else if (warp >= 4) {
-        // ======================= dequant warps ========================================================
-        const int t = tid - 128, wq = t >> 5;
-        // K: one operand row per thread (BN == 128) or half a row (BN == 64)
-        const int krow = BN == 128 ? t : (t & 63);
-        const int kch0 = BN == 128 ? 0 : (t >> 6) * (HD / 16);
-        constexpr int KCH = BN == 128 ? HD / 8 : HD / 16;      // 16-byte output chunks per thread
-        const int kkey = kappa(krow);
-        // V^T: 4 micro-tiles of (4 dims x 8 keys) per thread
+    } else if (warp >= (NSOFT + NDEQ) / 32) {
+        // ======================= V dequant warps: V^T operand, [dim][key] ============================
+        const int t = tid - NSOFT - NDEQ, wq = t >> 5;
         constexpr int NWG = HD / 16;                            // groups of four dim-words
+        constexpr int UPT = (HD / 4) * (BN / 8) / NDEQ;         // micro-tiles (4 dims x 8 keys) per thread
         const int ccl = lane & 7, wl = lane >> 3;
-        const int cc = 8 * ((4 * wq) / NWG) + ccl;              // key chunk (8 keys), fixed per thread
+        const int cc = 8 * ((UPT * wq) / NWG) + ccl;            // key chunk (8 keys), fixed per thread
         int vkey[8];
 #pragma unroll
         for (int jj = 0; jj < 8; ++jj) vkey[jj] = kappa(8 * cc + jj);
-        const int sword = (HD == 128) ? (wq & 1) : wq;          // 32-bit word holding this thread's two V scales
 
         for (int j = 0; j < n_tiles; ++j) {
             const int b = j & 1;
             const int t0 = (tile_first + j) * BN;
+            const uint8_t* Vraw = RAW + b * 2 * C::RAW_BYTES + C::RAW_BYTES;
+            wait(B_RAW_FULL0 + b, (j >> 1) & 1);
+            if (j > 0) wait(B_PV, (j - 1) & 1);                              // P.V of the previous tile read V
+            {
+                // keys outside [lo, hi) were never written for this chunk's rows: their bytes are arbitrary,
+                // so their scale is forced to zero (their P is zero as well)
+                bool kok[8];
+#pragma unroll
+                for (int jj = 0; jj < 8; ++jj) kok[jj] = (t0 + vkey[jj] >= lo_cta) && (t0 + vkey[jj] < hi_cta);
+                uint32_t sp[4];
+#pragma unroll
+                for (int it = 0; it < UPT; ++it) {
+                    const int u = UPT * wq + it;
+                    const int w = 4 * (u % NWG) + wl;                       // dim word: dims 4w .. 4w+3
+                    if ((it & 1) == 0) {                                    // two consecutive micro-tiles share a block
+                        const int vblk = (u % NWG) >> 1;
+#pragma unroll
+                        for (int pr = 0; pr < 4; ++pr) {
+                            const uint32_t sa = kok[2 * pr] ? reinterpret_cast<const uint16_t*>(Vraw + vkey[2 * pr] * REC)[vblk] : 0u;
+                            const uint32_t sb = kok[2 * pr + 1] ? reinterpret_cast<const uint16_t*>(Vraw + vkey[2 * pr + 1] * REC)[vblk] : 0u;
+                            sp[pr] = sa | (sb << 16);
+                        }
+                    }
+                    uint32_t x[8];
+#pragma unroll
+                    for (int jj = 0; jj < 8; ++jj)
+                        x[jj] = *reinterpret_cast<const uint32_t*>(Vraw + vkey[jj] * REC + 2 * NBLK + 4 * w) ^ 0x80808080u;
+                    uint32_t chunk[4][4];
+#pragma unroll
+                    for (int pr = 0; pr < 4; ++pr) {
+                        const uint32_t lo = __byte_perm(x[2 * pr], x[2 * pr + 1], 0x5140);
+                        const uint32_t hi = __byte_perm(x[2 * pr], x[2 * pr + 1], 0x7362);
+                        chunk[0][pr] = hmul2_u32(sub1152(widen_lo(lo)), sp[pr]);
+                        chunk[1][pr] = hmul2_u32(sub1152(widen_hi(lo)), sp[pr]);
+                        chunk[2][pr] = hmul2_u32(sub1152(widen_lo(hi)), sp[pr]);
+                        chunk[3][pr] = hmul2_u32(sub1152(widen_hi(hi)), sp[pr]);
+                    }
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int d = 4 * w + i;
+                        *reinterpret_cast<uint4*>(Vsm + (cc >> 3) * (HD * 128) + sw128(d, cc & 7)) =
+                            make_uint4(chunk[i][0], chunk[i][1], chunk[i][2], chunk[i][3]);
+                    }
+                }
+            }
+            proxy_fence();
+            __syncwarp();
+            if (lane == 0) { mbar_arrive(&bars[B_VF]); mbar_arrive(&bars[B_RAW_FREE0 + b]); }
+        }
+    } else if (warp >= NSOFT / 32) {
+        // ======================= K dequant warps: K operand, [key][dim] ==============================
+        const int t = tid - NSOFT;
+        const int krow = t & (BN - 1);                          // each thread converts KCH chunks of one row
+        constexpr int KCH = (BN * HD / 8) / NDEQ;
+        const int kch0 = (t / BN) * KCH;
+        const int kkey = kappa(krow);
+        for (int j = 0; j < n_tiles; ++j) {
+            const int b = j & 1;
             const uint8_t* Kraw = RAW + b * 2 * C::RAW_BYTES;
-            const uint8_t* Vraw = Kraw + C::RAW_BYTES;
             wait(B_RAW_FULL0 + b, (j >> 1) & 1);
             if (j > 0) wait(B_S0 + ((j - 1) & 1), ((j - 1) >> 1) & 1);     // S of the previous tile read K
             {
@@ -313,146 +421,110 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const Params P) {
             }
             proxy_fence();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&bars[B_KF]);
-
-            if (j > 0) wait(B_PV, (j - 1) & 1);                              // P.V of the previous tile read V
-            {
-                // the two scale blocks this thread needs, per key; keys outside [lo, hi) were never written
-                // for this chunk's rows, so their scale is forced to zero (their P is zero as well)
-                uint32_t sw[8];
-#pragma unroll
-                for (int jj = 0; jj < 8; ++jj) {
-                    const int key = t0 + vkey[jj];
-                    const bool ok = key >= lo_cta && key < hi_cta;
-                    sw[jj] = ok ? reinterpret_cast<const uint32_t*>(Vraw + vkey[jj] * REC)[sword] : 0u;
-                }
-#pragma unroll
-                for (int it = 0; it < 4; ++it) {
-                    const int u = 4 * wq + it;
-                    const int w = 4 * (u % NWG) + wl;                       // dim word: dims 4w .. 4w+3
-                    const int hsel = (w >> 3) & 1;                          // which half of the scale word
-                    uint32_t x[8];
-#pragma unroll
-                    for (int jj = 0; jj < 8; ++jj)
-                        x[jj] = *reinterpret_cast<const uint32_t*>(Vraw + vkey[jj] * REC + 2 * NBLK + 4 * w) ^ 0x80808080u;
-                    uint32_t chunk[4][4];
-#pragma unroll
-                    for (int pr = 0; pr < 4; ++pr) {
-                        const uint32_t sp = hsel ? __byte_perm(sw[2 * pr], sw[2 * pr + 1], 0x7632)
-                                                 : __byte_perm(sw[2 * pr], sw[2 * pr + 1], 0x5410);
-                        const uint32_t lo = __byte_perm(x[2 * pr], x[2 * pr + 1], 0x5140);
-                        const uint32_t hi = __byte_perm(x[2 * pr], x[2 * pr + 1], 0x7362);
-                        chunk[0][pr] = hmul2_u32(sub1152(widen_lo(lo)), sp);
-                        chunk[1][pr] = hmul2_u32(sub1152(widen_hi(lo)), sp);
-                        chunk[2][pr] = hmul2_u32(sub1152(widen_lo(hi)), sp);
-                        chunk[3][pr] = hmul2_u32(sub1152(widen_hi(hi)), sp);
-                    }
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const int d = 4 * w + i;
-                        *reinterpret_cast<uint4*>(Vsm + (cc >> 3) * (HD * 128) + sw128(d, cc & 7)) =
-                            make_uint4(chunk[i][0], chunk[i][1], chunk[i][2], chunk[i][3]);
-                    }
-                }
-            }
-            proxy_fence();
-            __syncwarp();
-            if (lane == 0) { mbar_arrive(&bars[B_VF]); mbar_arrive(&bars[B_RAW_FREE0 + b]); }
+            if (lane == 0) { mbar_arrive(&bars[B_KF]); mbar_arrive(&bars[B_RAW_FREE0 + b]); }
         }
     } else {
-        // ======================= softmax warps: one accumulator row per thread ========================
-        const int m = tid;                                     // row = TMEM lane
-        const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+        // ======================= softmax warps: two threads per accumulator row ========================
+        const int m = tid & 127;                               // row = TMEM lane
+        const int half = tid >> 7;                             // which half of the S columns / O columns
+        const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
         const int r = m / G, h = m - r * G;
         const bool row_ok = r < rows_eff;
         const int prow = p_first + r;
         const int row_lo = P.is_swa ? max(0, prow + 1 - P.W) : 0;     // bruce.cu:3014
-        float m_ref = NEG_BIG, l = 0.f;
+        const float c2 = P.scale_log2;
+        const float thr = RESCALE_THRESHOLD / c2;              // threshold in raw-score units
+        float m_ref = NEG_BIG;                                 // reference maximum, raw-score units
 
         for (int j = 0; j < n_tiles; ++j) {
             const int t0 = (tile_first + j) * BN;
-            const uint32_t tS = tmem + lane_base + ((j & 1) ? C::T_S1 : C::T_S0);
+            const uint32_t tS = tmem + lane_base + ((j & 1) ? C::T_S1 : C::T_S0) + half * HC;
             // tiles every row of the CTA sees completely skip the mask code (bruce.cu:2927-2928)
             const bool masked = !(t0 >= full_lo && t0 + BN - 1 <= p_first) || rows_eff < MR;
             wait(B_S0 + (j & 1), (j >> 1) & 1);
             tc_fence_after();
             float mx = NEG_BIG;
 #pragma unroll
-            for (int c = 0; c < BN / 32; ++c) {
+            for (int c = 0; c < HC / 32; ++c) {
                 uint32_t v[32];
                 tmem_ld32(tS + c * 32, v);
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
-                    float s = __uint_as_float(v[i]) * P.scale_log2;
+                    float x = __uint_as_float(v[i]);
                     if (masked) {
-                        const int key = t0 + kappa(c * 32 + i);
-                        if (!row_ok || key > prow || key < row_lo) s = NEG_BIG;
+                        const int key = t0 + kappa(half * HC + c * 32 + i);
+                        if (!row_ok || key > prow || key < row_lo) x = NEG_BIG;
                     }
-                    mx = fmaxf(mx, s);
+                    mx = fmaxf(mx, x);
                 }
             }
+            // exchange with the thread that holds the other half of this row; the buffer alternates with
+            // the tile parity so that a fast thread's next write cannot overtake a slow partner's read
+            rmax[(j & 1) * 256 + half * 128 + m] = mx;
+            named_bar_sync(2, NSOFT);
+            mx = fmaxf(mx, rmax[(j & 1) * 256 + (half ^ 1) * 128 + m]);
             float m_new = fmaxf(m_ref, mx);
-            const bool need = m_new > m_ref + RESCALE_THRESHOLD;
+            const bool need = m_new > m_ref + thr;
             if (!need) m_new = m_ref;
             const bool warp_need = __any_sync(0xffffffffu, need);
-            if (j > 0) { wait(B_PV, (j - 1) & 1); tc_fence_after(); }      // O and the P buffer are free again
             if (warp_need) {
-                const float alpha = fast_exp2(m_ref - m_new);             // 1 for rows that keep their reference
-                l *= alpha;
                 if (j > 0) {
+                    wait(B_PV, (j - 1) & 1);                                // O must be complete before it is rescaled
+                    tc_fence_after();
+                    const float alpha = fast_exp2((m_ref - m_new) * c2);  // 1 for rows that keep their reference
 #pragma unroll
-                    for (int c = 0; c < HD / 32; ++c) {
-                        uint32_t v[32];
-                        tmem_ld32(tmem + lane_base + C::T_O + c * 32, v);
+                    for (int c = 0; c < HD / 64; ++c) {
+                        uint32_t o[32];
+                        const uint32_t ta = tmem + lane_base + C::T_O + half * (HD / 2) + c * 32;
+                        tmem_ld32(ta, o);
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-                        tmem_st32(tmem + lane_base + C::T_O + c * 32, v);
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        tmem_st32(ta, o);
+                    }
+                    if (half == 0) {
+                        const uint32_t tl = tmem + lane_base + C::T_L;
+                        tmem_st1(tl, __float_as_uint(__uint_as_float(tmem_ld1(tl)) * alpha));
                     }
                     tmem_st_wait();
                 }
                 m_ref = m_new;
             }
+            const float nb = -m_ref * c2;
+            uint32_t pk[HC / 2];
 #pragma unroll
-            for (int c = 0; c < BN / 32; ++c) {
+            for (int c = 0; c < HC / 32; ++c) {
                 uint32_t v[32];
-                tmem_ld32(tS + c * 32, v);
-                uint32_t pk[16];
+                tmem_ld32(tS + c * 32, v);                                  // second read: cheaper than 64 live registers
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                    float s0 = __uint_as_float(v[i]) * P.scale_log2, s1 = __uint_as_float(v[i + 1]) * P.scale_log2;
-                    float e0 = fast_exp2(s0 - m_ref), e1 = fast_exp2(s1 - m_ref);
+                    float e0 = fast_exp2(fmaf(__uint_as_float(v[i]), c2, nb));
+                    float e1 = fast_exp2(fmaf(__uint_as_float(v[i + 1]), c2, nb));
                     if (masked) {
-                        const int k0 = t0 + kappa(c * 32 + i), k1 = t0 + kappa(c * 32 + i + 1);
+                        const int k0 = t0 + kappa(half * HC + c * 32 + i), k1 = t0 + kappa(half * HC + c * 32 + i + 1);
                         if (!row_ok || k0 > prow || k0 < row_lo) e0 = 0.f;
                         if (!row_ok || k1 > prow || k1 < row_lo) e1 = 0.f;
                     }
-                    pk[i >> 1] = pack_h2(e0, e1);
-                    // the denominator sums the fp16-rounded weights the MMA will use, so that
-                    // out = sum(p v) / sum(p) stays a convex combination of the V rows
-                    const float2 pr = __half22float2(*reinterpret_cast<const __half2*>(&pk[i >> 1]));
-                    l += pr.x + pr.y;
-                }
-#pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    const int ch = c * 4 + q4;                              // 16-byte chunk = 8 keys
-                    *reinterpret_cast<uint4*>(Psm + (ch >> 3) * (128 * 128) + sw128(m, ch & 7)) =
-                        make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
+                    pk[c * 16 + (i >> 1)] = pack_h2(e0, e1);
                 }
             }
-            proxy_fence();
+            // P (fp16 pairs) overwrites the first half of the S columns this thread owns; nobody else reads or
+            // writes those columns, and the MMA that refills this S buffer is ordered after the P.V MMA
+            if constexpr (HC == 64) tmem_st32(tS, pk); else tmem_st16(tS, pk);
+            tmem_st_wait();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars[B_P]);
         }
-        // ---- epilogue: O / l -> global ----------------------------------------------------------------
+        // ---- epilogue: O / sum(P) -> global; each thread writes half of its row -----------------------
         wait(B_PV, (n_tiles - 1) & 1);
         tc_fence_after();
+        const float l = __uint_as_float(tmem_ld1(tmem + lane_base + C::T_L));
         const float il = l > 0.f ? 1.f / l : 0.f;
-        const size_t oi = (((size_t)(rbase + r)) * P.Hq + kvh * G + h) * HD;
+        const size_t oi = (((size_t)(rbase + r)) * P.Hq + kvh * G + h) * HD + half * (HD / 2);
 #pragma unroll
-        for (int c = 0; c < HD / 32; ++c) {
-            uint32_t v[32];
-            tmem_ld32(tmem + lane_base + C::T_O + c * 32, v);
+        for (int c = 0; c < HD / 64; ++c) {
+            uint32_t o[32];
+            tmem_ld32(tmem + lane_base + C::T_O + half * (HD / 2) + c * 32, o);
             if (row_ok) {
                 if (P.out_f16) {
                     uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__half*>(P.out) + oi + c * 32);
@@ -461,22 +533,22 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const Params P) {
                         uint32_t w[4];
 #pragma unroll
                         for (int e = 0; e < 4; ++e)
-                            w[e] = pack_h2(__uint_as_float(v[q4 * 8 + 2 * e]) * il, __uint_as_float(v[q4 * 8 + 2 * e + 1]) * il);
+                            w[e] = pack_h2(__uint_as_float(o[q4 * 8 + 2 * e]) * il, __uint_as_float(o[q4 * 8 + 2 * e + 1]) * il);
                         dst[q4] = make_uint4(w[0], w[1], w[2], w[3]);
                     }
                 } else {
                     float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(P.out) + oi + c * 32);
 #pragma unroll
                     for (int q4 = 0; q4 < 8; ++q4)
-                        dst[q4] = make_float4(__uint_as_float(v[4 * q4]) * il, __uint_as_float(v[4 * q4 + 1]) * il,
-                                              __uint_as_float(v[4 * q4 + 2]) * il, __uint_as_float(v[4 * q4 + 3]) * il);
+                        dst[q4] = make_float4(__uint_as_float(o[4 * q4]) * il, __uint_as_float(o[4 * q4 + 1]) * il,
+                                              __uint_as_float(o[4 * q4 + 2]) * il, __uint_as_float(o[4 * q4 + 3]) * il);
                 }
             }
         }
         tc_fence_before();
     }
     __syncthreads();
-    if (warp == 8) {
+    if (warp == NTHREADS / 32 - 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
     }
