@@ -350,7 +350,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const Params P) {
 #pragma unroll
                 for (int jj = 0; jj < 8; ++jj) kok[jj] = (t0 + vkey[jj] >= lo_cta) && (t0 + vkey[jj] < hi_cta);
                 uint32_t sp[4];
-#pragma unroll
+#pragma unroll 1
                 for (int it = 0; it < UPT; ++it) {
                     const int u = UPT * wq + it;
                     const int w = 4 * (u % NWG) + wl;                       // dim word: dims 4w .. 4w+3
@@ -403,7 +403,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const Params P) {
             if (j > 0) wait(B_S0 + ((j - 1) & 1), ((j - 1) >> 1) & 1);     // S of the previous tile read K
             {
                 const uint8_t* src = Kraw + kkey * REC;
-#pragma unroll
+#pragma unroll 2
                 for (int c = 0; c < KCH; ++c) {
                     const int ch = kch0 + c;
                     const __half sc = reinterpret_cast<const __half*>(src)[ch >> 2];
@@ -443,20 +443,40 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const Params P) {
             const bool masked = !(t0 >= full_lo && t0 + BN - 1 <= p_first) || rows_eff < MR;
             wait(B_S0 + (j & 1), (j >> 1) & 1);
             tc_fence_after();
-            float mx = NEG_BIG;
+            // Visibility of this thread's columns, one bit per column: all ones on tiles every row sees
+            // completely (bruce.cu:2927-2928), otherwise built by a small rolled loop.  One code path then
+            // serves both cases, which keeps the hot loop short enough for the instruction cache.
+            uint32_t vis[HC / 32];
 #pragma unroll
+            for (int c = 0; c < HC / 32; ++c) vis[c] = 0xffffffffu;
+            if (masked) {
+#pragma unroll
+                for (int c = 0; c < HC / 32; ++c) {
+                    uint32_t bits = 0u;
+#pragma unroll 1
+                    for (int i = 0; i < 32; ++i) {
+                        const int key = t0 + kappa(half * HC + c * 32 + i);
+                        const bool ok = row_ok && key <= prow && key >= row_lo;     // bruce.cu:3021-3028
+                        bits |= (ok ? 1u : 0u) << i;
+                    }
+                    vis[c] = bits;
+                }
+            }
+            float mx = NEG_BIG;
+#pragma unroll 1
             for (int c = 0; c < HC / 32; ++c) {
                 uint32_t v[32];
                 tmem_ld32(tS + c * 32, v);
+                const uint32_t vb = vis[c];
+                float m0 = NEG_BIG, m1 = NEG_BIG, m2 = NEG_BIG, m3 = NEG_BIG;
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    float x = __uint_as_float(v[i]);
-                    if (masked) {
-                        const int key = t0 + kappa(half * HC + c * 32 + i);
-                        if (!row_ok || key > prow || key < row_lo) x = NEG_BIG;
-                    }
-                    mx = fmaxf(mx, x);
+                for (int i = 0; i < 32; i += 4) {
+                    m0 = fmaxf(m0, (vb >> i) & 1u ? __uint_as_float(v[i]) : NEG_BIG);
+                    m1 = fmaxf(m1, (vb >> (i + 1)) & 1u ? __uint_as_float(v[i + 1]) : NEG_BIG);
+                    m2 = fmaxf(m2, (vb >> (i + 2)) & 1u ? __uint_as_float(v[i + 2]) : NEG_BIG);
+                    m3 = fmaxf(m3, (vb >> (i + 3)) & 1u ? __uint_as_float(v[i + 3]) : NEG_BIG);
                 }
+                mx = fmaxf(mx, fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)));
             }
             // exchange with the thread that holds the other half of this row; the buffer alternates with
             // the tile parity so that a fast thread's next write cannot overtake a slow partner's read
@@ -472,7 +492,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const Params P) {
                     wait(B_PV, (j - 1) & 1);                                // O must be complete before it is rescaled
                     tc_fence_after();
                     const float alpha = fast_exp2((m_ref - m_new) * c2);  // 1 for rows that keep their reference
-#pragma unroll
+#pragma unroll 1
                     for (int c = 0; c < HD / 64; ++c) {
                         uint32_t o[32];
                         const uint32_t ta = tmem + lane_base + C::T_O + half * (HD / 2) + c * 32;
@@ -490,26 +510,23 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const Params P) {
                 m_ref = m_new;
             }
             const float nb = -m_ref * c2;
-            uint32_t pk[HC / 2];
-#pragma unroll
+#pragma unroll 1
             for (int c = 0; c < HC / 32; ++c) {
                 uint32_t v[32];
                 tmem_ld32(tS + c * 32, v);                                  // second read: cheaper than 64 live registers
+                const uint32_t vb = vis[c];
+                uint32_t pk[16];
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                    float e0 = fast_exp2(fmaf(__uint_as_float(v[i]), c2, nb));
-                    float e1 = fast_exp2(fmaf(__uint_as_float(v[i + 1]), c2, nb));
-                    if (masked) {
-                        const int k0 = t0 + kappa(half * HC + c * 32 + i), k1 = t0 + kappa(half * HC + c * 32 + i + 1);
-                        if (!row_ok || k0 > prow || k0 < row_lo) e0 = 0.f;
-                        if (!row_ok || k1 > prow || k1 < row_lo) e1 = 0.f;
-                    }
-                    pk[c * 16 + (i >> 1)] = pack_h2(e0, e1);
+                    const float e0 = (vb >> i) & 1u ? fast_exp2(fmaf(__uint_as_float(v[i]), c2, nb)) : 0.f;
+                    const float e1 = (vb >> (i + 1)) & 1u ? fast_exp2(fmaf(__uint_as_float(v[i + 1]), c2, nb)) : 0.f;
+                    pk[i >> 1] = pack_h2(e0, e1);
                 }
+                // P (fp16 pairs) overwrites S columns this thread owns and has already read: chunk c of S
+                // (32 columns) becomes 16 columns of P at the start of the thread's region; nobody else reads
+                // or writes them, and the MMA that refills this S buffer is ordered after the P.V MMA
+                tmem_st16(tS + c * 16, pk);
             }
-            // P (fp16 pairs) overwrites the first half of the S columns this thread owns; nobody else reads or
-            // writes those columns, and the MMA that refills this S buffer is ordered after the P.V MMA
-            if constexpr (HC == 64) tmem_st32(tS, pk); else tmem_st16(tS, pk);
             tmem_st_wait();
             tc_fence_before();
             __syncwarp();
@@ -521,7 +538,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const Params P) {
         const float l = __uint_as_float(tmem_ld1(tmem + lane_base + C::T_L));
         const float il = l > 0.f ? 1.f / l : 0.f;
         const size_t oi = (((size_t)(rbase + r)) * P.Hq + kvh * G + h) * HD + half * (HD / 2);
-#pragma unroll
+#pragma unroll 1
         for (int c = 0; c < HD / 64; ++c) {
             uint32_t o[32];
             tmem_ld32(tmem + lane_base + C::T_O + half * (HD / 2) + c * 32, o);
