@@ -441,6 +441,8 @@ def run_gpu(args):
         raise SystemExit("bench.py needs a CUDA device: the attention path has no CPU implementation")
     torch.cuda.set_device(local)
     if world > 1:
+        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"        # the version banner goes to stdout, which carries the JSON line
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
     gen = torch.Generator(device=f"cuda:{local}")
