@@ -441,9 +441,19 @@ def run_gpu(args):
         raise SystemExit("bench.py needs a CUDA device: the attention path has no CPU implementation")
     torch.cuda.set_device(local)
     if world > 1:
-        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
-            os.environ["NCCL_DEBUG"] = "WARN"        # the version banner goes to stdout, which carries the JSON line
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        # NCCL may print a version banner on stdout when its communicator comes up; stdout carries the one
+        # JSON line, so it points at stderr while the process group and the first collective are set up
+        sys.stdout.flush()
+        saved = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+            dist.barrier()
+            torch.cuda.synchronize()
+        finally:
+            sys.stdout.flush()
+            os.dup2(saved, 1)
+            os.close(saved)
 
     gen = torch.Generator(device=f"cuda:{local}")
     gen.manual_seed(1000 + rank)                   # every rank serves its own sequence
