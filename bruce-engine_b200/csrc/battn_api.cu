@@ -68,7 +68,7 @@ inline FdWs fd_workspace(const battn_handle* h, int n_seq, int rows) {
     FdWs w;
     w.max_ctas = h->num_sms * FD_MAX_CTAS_PER_SM;
     w.hdr_bytes = align_up((size_t)(n_seq + 3) * sizeof(int), 256);
-    w.rec_bytes = (size_t)(w.max_ctas + (size_t)n_seq * g.Hkv) * rows * g.G * (g.HD + 2) * sizeof(float);
+    w.rec_bytes = (size_t)(w.max_ctas + (size_t)n_seq * g.Hkv) * rows * g.G * (g.HD + 4) * sizeof(float);
     w.total = w.hdr_bytes + w.rec_bytes;
     return w;
 }
@@ -173,8 +173,8 @@ int launch_flash(battn_handle* h, void* out, float* rec_out, const void* q, cons
     M.mode = MERGE_BALANCED; M.part = P.part; M.out = out; M.rec_out = rec_out;
     M.n_rows = n_seq * rows; M.rows = rows; M.Hq = g.Hq; M.Hkv = g.Hkv; M.G = g.G;
     M.count = 0; M.log2_domain = 1; M.out_f16 = g.out_f16; M.hdr = P.hdr; M.status = h->d_status;
-    if (g.HD == 128) k_merge<128><<<n_seq * rows * g.Hq, MERGE_THREADS, 0, st>>>(M);
-    else             k_merge<256><<<n_seq * rows * g.Hq, MERGE_THREADS, 0, st>>>(M);
+    if (g.HD == 128) k_merge_balanced<128><<<n_seq * rows * g.Hq, MERGE_B_THREADS, 0, st>>>(M);
+    else             k_merge_balanced<256><<<n_seq * rows * g.Hq, MERGE_B_THREADS, 0, st>>>(M);
     h->launches += 2;
     e = cudaGetLastError();
     return e == cudaSuccess ? BATTN_OK : cuda_fail(h, e);

@@ -232,4 +232,107 @@ __global__ void __launch_bounds__(MERGE_THREADS) k_merge(const MergeParams P) {
     }
 }
 
+// The merge behind the flash-decode kernel (MERGE_BALANCED records only).  Those records are padded to
+// HD + 4 floats so that every record is 16-byte aligned: 1024 threads = HD/4 float4 lanes x 32 (or 16)
+// record groups, so the ~74..592 records of a (row, head) are read in one or two rounds of independent
+// 16-byte loads instead of a long latency chain.
+constexpr int MERGE_B_THREADS = 1024;
+
+template <int HD>
+__global__ void __launch_bounds__(MERGE_B_THREADS) k_merge_balanced(const MergeParams P) {
+    constexpr int RS = HD + 4;                                   // floats per internal record
+    constexpr int NDQ = HD / 4, NG = MERGE_B_THREADS / NDQ;
+    __shared__ float s_m[MERGE_MAX_COUNT];
+    __shared__ float s_l[MERGE_MAX_COUNT];
+    __shared__ float s_red[MERGE_B_THREADS / 32];
+    __shared__ float4 s_acc[MERGE_B_THREADS];
+    const int hq = blockIdx.x % P.Hq, rowidx = blockIdx.x / P.Hq;
+    const int i = rowidx / P.rows, r = rowidx % P.rows;
+    const int kvh = hq / P.G, h = hq % P.G;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int per = P.hdr[0];
+    const int c0 = P.hdr[2 + i], c1 = P.hdr[3 + i];
+    const int nt = c1 - c0;
+    if (nt <= 0) return;                                         // inactive sequence: no output
+    const int item = i * P.Hkv + kvh;
+    const long long t0 = (long long)P.Hkv * c0 + (long long)kvh * nt, t1 = t0 + nt;
+    const int clo = (int)(t0 / per), chi = (int)((t1 - 1) / per);
+    const int RG = P.rows * P.G;
+    const int count = min(chi - clo + 1, MERGE_MAX_COUNT);
+    const float* base = P.part + ((size_t)(clo + item) * RG + r * P.G + h) * (size_t)RS;
+    const size_t stride = (size_t)RG * RS;
+
+    float mx = NEG_BIG;
+    for (int s = tid; s < count; s += MERGE_B_THREADS) {
+        const float2 ml = *reinterpret_cast<const float2*>(base + s * stride + HD);
+        s_m[s] = ml.x; s_l[s] = ml.y;
+        mx = fmaxf(mx, ml.x);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if (lane == 0) s_red[warp] = mx;
+    __syncthreads();
+    float M = s_red[lane];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+    __syncthreads();
+    float ls = 0.f;
+    for (int s = tid; s < count; s += MERGE_B_THREADS) {
+        const float w = fast_exp2(s_m[s] - M);                   // records carry m in log2 units
+        s_m[s] = w;
+        ls = fmaf(s_l[s], w, ls);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ls += __shfl_xor_sync(0xffffffffu, ls, o);
+    if (lane == 0) s_red[warp] = ls;
+    __syncthreads();
+    float L = s_red[lane];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
+
+    const int dq = tid % NDQ, grp = tid / NDQ;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+    for (int s = grp; s < count; s += NG) {
+        const float4 o = *reinterpret_cast<const float4*>(base + s * stride + 4 * dq);
+        const float w = s_m[s];
+        acc.x = fmaf(o.x, w, acc.x); acc.y = fmaf(o.y, w, acc.y);
+        acc.z = fmaf(o.z, w, acc.z); acc.w = fmaf(o.w, w, acc.w);
+    }
+    s_acc[tid] = acc;
+    __syncthreads();
+#pragma unroll
+    for (int st = NG / 2; st > 0; st >>= 1) {                    // fixed-order tree over the record groups
+        if (grp < st) {
+            const float4 o = s_acc[(grp + st) * NDQ + dq];
+            acc.x += o.x; acc.y += o.y; acc.z += o.z; acc.w += o.w;
+            s_acc[tid] = acc;
+        }
+        __syncthreads();
+    }
+    if (grp != 0) return;
+    const int d4 = 4 * dq;
+    if (P.out) {
+        const float il = L > 0.f ? 1.f / L : 0.f;
+        const size_t oi = ((size_t)rowidx * P.Hq + hq) * HD + d4;
+        if (P.out_f16) {
+            const __half2 a = __floats2half2_rn(acc.x * il, acc.y * il), b = __floats2half2_rn(acc.z * il, acc.w * il);
+            *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(P.out) + oi) =
+                make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
+        } else {
+            *reinterpret_cast<float4*>(reinterpret_cast<float*>(P.out) + oi) =
+                make_float4(acc.x * il, acc.y * il, acc.z * il, acc.w * il);
+        }
+    }
+    if (P.rec_out) {                                             // public record: HD + 2 floats, natural-log m
+        float* ro = P.rec_out + ((size_t)rowidx * P.Hq + hq) * (size_t)(HD + 2);
+        *reinterpret_cast<float2*>(ro + d4) = make_float2(acc.x, acc.y);
+        *reinterpret_cast<float2*>(ro + d4 + 2) = make_float2(acc.z, acc.w);
+        if (dq == 0) {
+            ro[HD] = M > -1e29f ? M * LN2 : M;
+            ro[HD + 1] = L;
+        }
+    }
+}
+
 }  // namespace battn

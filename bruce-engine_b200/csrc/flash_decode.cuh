@@ -44,7 +44,7 @@ struct Params {
     const int* kslot;
     const int* act;
     int* hdr;        // workspace header: {tiles_per_cta, total_tiles, cum[n_seq + 1]}
-    float* part;     // workspace records, slot stride RG * (HD + 2) floats
+    float* part;     // workspace records, slot stride RG * (HD + 4) floats
     int n_seq, rows, Hq, Hkv, G, RG;
     int W, pstride, ring_mask, slot_ctx, n_slots, is_swa, q_f16;
     float scale_log2;   // softmax scale * log2(e): scores are kept in log2 units
@@ -463,7 +463,8 @@ k_flash_decode(const Params P) {
                     }
                 }
             named_bar_sync(1, NW * 32);
-            float* dst = P.part + (size_t)(blockIdx.x + item) * RG * (HD + 2);
+            // records in the workspace are padded to HD + 4 floats (16-byte aligned for the merge kernel)
+            float* dst = P.part + (size_t)(blockIdx.x + item) * RG * (HD + 4);
             for (int idx = ctid; idx < RG * HD; idx += NW * 32) {
                 const int n = idx / HD, d = idx - n * HD;
                 float mw[NW], M = NEG_BIG;
@@ -479,8 +480,8 @@ k_flash_decode(const Params P) {
                     acc = fmaf(mbuf[((size_t)w * RG + n) * (HD + 2) + d], f, acc);
                     L = fmaf(mbuf[((size_t)w * RG + n) * (HD + 2) + HD + 1], f, L);
                 }
-                dst[(size_t)n * (HD + 2) + d] = acc;
-                if (d == 0) { dst[(size_t)n * (HD + 2) + HD] = M; dst[(size_t)n * (HD + 2) + HD + 1] = L; }
+                dst[(size_t)n * (HD + 4) + d] = acc;
+                if (d == 0) { dst[(size_t)n * (HD + 4) + HD] = M; dst[(size_t)n * (HD + 4) + HD + 1] = L; }
             }
             g += pc.n;
         }
