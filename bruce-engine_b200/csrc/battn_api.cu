@@ -89,6 +89,19 @@ int check_seq_args(const battn_handle* h, const void* a, const void* b, const vo
     return BATTN_OK;
 }
 
+// Launch with the programmatic-stream-serialisation attribute: the kernel may begin launching while the
+// previous kernel of the stream drains; it calls pdl_wait() before it touches global memory.
+template <typename Params>
+cudaError_t launch_pdl(void (*kernel)(const Params), dim3 grid, dim3 block, size_t smem, cudaStream_t st, const Params& p) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, p);
+}
+
 // event pair around the main kernel of a call while profiling is on
 struct ProfScope {
     battn_handle* h; cudaStream_t st; int idx;
@@ -130,8 +143,7 @@ int launch_exact(battn_handle* h, void* out, float* rec_out, const void* q, cons
 
 template <int HD, int NT>
 cudaError_t launch_fd_kernel(const fd::Params& P, int grid, size_t smem, cudaStream_t st) {
-    fd::k_flash_decode<HD, NT><<<grid, fd::NTHREADS, smem, st>>>(P);
-    return cudaGetLastError();
+    return launch_pdl(fd::k_flash_decode<HD, NT>, dim3(grid), dim3(fd::NTHREADS), smem, st, P);
 }
 
 // decode / verify / multi-slot decode through the flash-decode kernel and the balanced merge
@@ -173,10 +185,10 @@ int launch_flash(battn_handle* h, void* out, float* rec_out, const void* q, cons
     M.mode = MERGE_BALANCED; M.part = P.part; M.out = out; M.rec_out = rec_out;
     M.n_rows = n_seq * rows; M.rows = rows; M.Hq = g.Hq; M.Hkv = g.Hkv; M.G = g.G;
     M.count = 0; M.log2_domain = 1; M.out_f16 = g.out_f16; M.hdr = P.hdr; M.status = h->d_status;
-    if (g.HD == 128) k_merge_balanced<128><<<n_seq * rows * g.Hq, MERGE_B_THREADS, 0, st>>>(M);
-    else             k_merge_balanced<256><<<n_seq * rows * g.Hq, MERGE_B_THREADS, 0, st>>>(M);
+    if (g.HD == 128) e = launch_pdl(k_merge_balanced<128>, dim3(n_seq * rows * g.Hq), dim3(MERGE_B_THREADS), 0, st, M);
+    else             e = launch_pdl(k_merge_balanced<256>, dim3(n_seq * rows * g.Hq), dim3(MERGE_B_THREADS), 0, st, M);
     h->launches += 2;
-    e = cudaGetLastError();
+    if (e == cudaSuccess) e = cudaGetLastError();
     return e == cudaSuccess ? BATTN_OK : cuda_fail(h, e);
 }
 
@@ -303,10 +315,11 @@ int battn_kv_append(battn_handle* h, const float* k, const float* v, uint8_t* kv
     const long long warps = (long long)n_seq * rows_per_seq * g.Hkv * 2;
     const int blocks = (int)((warps + 7) / 8);
     cudaStream_t st = (cudaStream_t)stream;
-    if (g.HD == 128) k_kv_append<128><<<blocks, 256, 0, st>>>(P);
-    else             k_kv_append<256><<<blocks, 256, 0, st>>>(P);
+    cudaError_t e;
+    if (g.HD == 128) e = launch_pdl(k_kv_append<128>, dim3(blocks), dim3(256), 0, st, P);
+    else             e = launch_pdl(k_kv_append<256>, dim3(blocks), dim3(256), 0, st, P);
     h->launches += 1;
-    const cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) e = cudaGetLastError();
     return e == cudaSuccess ? BATTN_OK : cuda_fail(h, e);
 }
 

@@ -144,6 +144,13 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
         : "memory");
 }
 
+// Programmatic dependent launch: a kernel launched with the programmatic-serialisation attribute may start
+// while its predecessor in the stream is still draining.  pdl_wait() blocks until the predecessor has
+// completed and its writes are visible (a no-op for an ordinary launch); everything before it must not
+// touch global memory.  pdl_trigger() lets the successor begin its own launch.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }

@@ -250,6 +250,8 @@ __global__ void __launch_bounds__(MERGE_B_THREADS) k_merge_balanced(const MergeP
     const int i = rowidx / P.rows, r = rowidx % P.rows;
     const int kvh = hq / P.G, h = hq % P.G;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    pdl_wait();
+    pdl_trigger();
     const int per = P.hdr[0];
     const int c0 = P.hdr[2 + i], c1 = P.hdr[3 + i];
     const int nt = c1 - c0;

@@ -114,6 +114,8 @@ k_flash_decode(const Params P) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], NW); }
         mbar_fence_init();
     }
+    pdl_wait();          // nothing above reads or writes global memory
+    pdl_trigger();
     if (P.n_seq == 1) {
         // one sequence (decode / verify of a single stream): no prefix sum, one barrier
         if (tid == 0) {

@@ -26,6 +26,8 @@ template <int HD>
 __global__ void __launch_bounds__(256) k_kv_append(const AppendParams P) {
     constexpr int NBLK = HD / 32;
     constexpr int REC = HD + 2 * NBLK;
+    pdl_wait();
+    pdl_trigger();
     const int lane = threadIdx.x & 31;
     const long long wid = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const long long total = (long long)P.n_seq * P.rows * P.Hkv * 2;
