@@ -64,8 +64,9 @@ struct Cfg {
     static constexpr int OFF_V = OFF_K + K_BYTES;
     static constexpr int ONES_BYTES = 16 * BN * 2;           // 16 operand rows of ones: the denominator MMA
     static constexpr int OFF_ONES = OFF_V + V_BYTES;
-    static constexpr int OFF_RAW = OFF_ONES + ONES_BYTES;    // [2 buffers][K | V]
-    static constexpr int OFF_BAR = OFF_RAW + 4 * RAW_BYTES;
+    static constexpr int RAW_STAGES = HD == 128 ? 3 : 2;     // head_dim 256 has no shared memory left for a third
+    static constexpr int OFF_RAW = OFF_ONES + ONES_BYTES;    // [RAW_STAGES buffers][K | V]
+    static constexpr int OFF_BAR = OFF_RAW + RAW_STAGES * 2 * RAW_BYTES;
     static constexpr int N_BARS = 12;
     static constexpr int OFF_MISC = OFF_BAR + N_BARS * 8;    // tmem base, abort flag
     static constexpr int OFF_RMAX = OFF_MISC + 16;           // [tile parity][2 halves][128 rows] row maxima
@@ -80,7 +81,7 @@ struct Cfg {
 };
 
 // barrier indices
-enum { B_RAW_FULL0 = 0, B_RAW_FULL1, B_RAW_FREE0, B_RAW_FREE1, B_KF, B_VF, B_S0, B_S1, B_P, B_PV };
+enum { B_RAW_FULL0 = 0, B_RAW_FREE0 = 3, B_KF = 6, B_VF, B_S0, B_S1, B_P, B_PV };   // three raw stages
 
 // byte offset of 16-byte chunk `chunk` (0..7) of row `row` inside a [rows x 64 halves] sub-tile stored
 // K-major with the 128-byte swizzle (8-row atoms of 1024 B, chunk index XOR row-in-atom)
@@ -218,8 +219,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const Params P) {
 
     // ---- set-up: barriers, tensor memory, the Q operand, the block of ones ---------------------------
     if (tid == 0) {
-        mbar_init(&bars[B_RAW_FULL0], 1); mbar_init(&bars[B_RAW_FULL1], 1);
-        mbar_init(&bars[B_RAW_FREE0], 2 * NDEQ / 32); mbar_init(&bars[B_RAW_FREE1], 2 * NDEQ / 32);
+        for (int st = 0; st < C::RAW_STAGES; ++st) {
+            mbar_init(&bars[B_RAW_FULL0 + st], 1);
+            mbar_init(&bars[B_RAW_FREE0 + st], 2 * NDEQ / 32);
+        }
         mbar_init(&bars[B_KF], NDEQ / 32); mbar_init(&bars[B_VF], NDEQ / 32);
         mbar_init(&bars[B_S0], 1); mbar_init(&bars[B_S1], 1);
         mbar_init(&bars[B_P], NSOFT / 32); mbar_init(&bars[B_PV], 1);
@@ -271,7 +274,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const Params P) {
         // ======================= control thread: bulk copies and every MMA ===========================
         if (lane == 0) {
             auto load_raw = [&](int j) {
-                const int b = j & 1;
+                const int b = j % C::RAW_STAGES;
                 const int sp = ((tile_first + j) * BN) & P.ring_mask;
                 const int nk = min(BN, P.pstride - sp);
                 const uint32_t bytes = (uint32_t)nk * REC;
@@ -282,6 +285,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const Params P) {
             };
             load_raw(0);
             if (n_tiles > 1) load_raw(1);
+            if (C::RAW_STAGES > 2 && n_tiles > 2) load_raw(2);
 
             const uint32_t idS = umma_idesc(128, BN), idO = umma_idesc(128, HD), idL = umma_idesc(128, 16);
             const uint32_t qa = smem_u32(Qsm), ka = smem_u32(Ksm), va = smem_u32(Vsm);
@@ -320,9 +324,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const Params P) {
                     umma_f16_ts(tmem + C::T_L, a, o, idL, acc);             // every column = sum of P
                 }
                 umma_commit(&bars[B_PV]);
-                if (j + 2 < n_tiles) {
-                    wait(B_RAW_FREE0 + (j & 1), (j >> 1) & 1);
-                    load_raw(j + 2);
+                if (j + C::RAW_STAGES < n_tiles) {                       // refill the stage tile j just left
+                    wait(B_RAW_FREE0 + j % C::RAW_STAGES, (j / C::RAW_STAGES) & 1);
+                    load_raw(j + C::RAW_STAGES);
                 }
             }
         }
@@ -338,10 +342,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const Params P) {
         for (int jj = 0; jj < 8; ++jj) vkey[jj] = kappa(8 * cc + jj);
 
         for (int j = 0; j < n_tiles; ++j) {
-            const int b = j & 1;
+            const int b = j % C::RAW_STAGES;
             const int t0 = (tile_first + j) * BN;
             const uint8_t* Vraw = RAW + b * 2 * C::RAW_BYTES + C::RAW_BYTES;
-            wait(B_RAW_FULL0 + b, (j >> 1) & 1);
+            wait(B_RAW_FULL0 + b, (j / C::RAW_STAGES) & 1);
             if (j > 0) wait(B_PV, (j - 1) & 1);                              // P.V of the previous tile read V
             {
                 // keys outside [lo, hi) were never written for this chunk's rows: their bytes are arbitrary,
@@ -397,9 +401,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const Params P) {
         const int kch0 = (t / BN) * KCH;
         const int kkey = kappa(krow);
         for (int j = 0; j < n_tiles; ++j) {
-            const int b = j & 1;
+            const int b = j % C::RAW_STAGES;
             const uint8_t* Kraw = RAW + b * 2 * C::RAW_BYTES;
-            wait(B_RAW_FULL0 + b, (j >> 1) & 1);
+            wait(B_RAW_FULL0 + b, (j / C::RAW_STAGES) & 1);
             if (j > 0) wait(B_S0 + ((j - 1) & 1), ((j - 1) >> 1) & 1);     // S of the previous tile read K
             {
                 const uint8_t* src = Kraw + kkey * REC;
@@ -469,12 +473,22 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const Params P) {
                 tmem_ld32(tS + c * 32, v);
                 const uint32_t vb = vis[c];
                 float m0 = NEG_BIG, m1 = NEG_BIG, m2 = NEG_BIG, m3 = NEG_BIG;
+                if (vb == 0xffffffffu) {                                    // the common case: nothing masked
 #pragma unroll
-                for (int i = 0; i < 32; i += 4) {
-                    m0 = fmaxf(m0, (vb >> i) & 1u ? __uint_as_float(v[i]) : NEG_BIG);
-                    m1 = fmaxf(m1, (vb >> (i + 1)) & 1u ? __uint_as_float(v[i + 1]) : NEG_BIG);
-                    m2 = fmaxf(m2, (vb >> (i + 2)) & 1u ? __uint_as_float(v[i + 2]) : NEG_BIG);
-                    m3 = fmaxf(m3, (vb >> (i + 3)) & 1u ? __uint_as_float(v[i + 3]) : NEG_BIG);
+                    for (int i = 0; i < 32; i += 4) {
+                        m0 = fmaxf(m0, __uint_as_float(v[i]));
+                        m1 = fmaxf(m1, __uint_as_float(v[i + 1]));
+                        m2 = fmaxf(m2, __uint_as_float(v[i + 2]));
+                        m3 = fmaxf(m3, __uint_as_float(v[i + 3]));
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4) {
+                        m0 = fmaxf(m0, (vb >> i) & 1u ? __uint_as_float(v[i]) : NEG_BIG);
+                        m1 = fmaxf(m1, (vb >> (i + 1)) & 1u ? __uint_as_float(v[i + 1]) : NEG_BIG);
+                        m2 = fmaxf(m2, (vb >> (i + 2)) & 1u ? __uint_as_float(v[i + 2]) : NEG_BIG);
+                        m3 = fmaxf(m3, (vb >> (i + 3)) & 1u ? __uint_as_float(v[i + 3]) : NEG_BIG);
+                    }
                 }
                 mx = fmaxf(mx, fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)));
             }
@@ -516,11 +530,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const Params P) {
                 tmem_ld32(tS + c * 32, v);                                  // second read: cheaper than 64 live registers
                 const uint32_t vb = vis[c];
                 uint32_t pk[16];
+                if (vb == 0xffffffffu) {                                    // the common case: nothing masked
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    const float e0 = (vb >> i) & 1u ? fast_exp2(fmaf(__uint_as_float(v[i]), c2, nb)) : 0.f;
-                    const float e1 = (vb >> (i + 1)) & 1u ? fast_exp2(fmaf(__uint_as_float(v[i + 1]), c2, nb)) : 0.f;
-                    pk[i >> 1] = pack_h2(e0, e1);
+                    for (int i = 0; i < 32; i += 2)
+                        pk[i >> 1] = pack_h2(fast_exp2(fmaf(__uint_as_float(v[i]), c2, nb)),
+                                             fast_exp2(fmaf(__uint_as_float(v[i + 1]), c2, nb)));
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const float e0 = (vb >> i) & 1u ? fast_exp2(fmaf(__uint_as_float(v[i]), c2, nb)) : 0.f;
+                        const float e1 = (vb >> (i + 1)) & 1u ? fast_exp2(fmaf(__uint_as_float(v[i + 1]), c2, nb)) : 0.f;
+                        pk[i >> 1] = pack_h2(e0, e1);
+                    }
                 }
                 // P (fp16 pairs) overwrites S columns this thread owns and has already read: chunk c of S
                 // (32 columns) becomes 16 columns of P at the start of the thread's region; nobody else reads
