@@ -324,6 +324,49 @@ def bench_prefill(torch, AttnEngine, G_B, device, reps: int):
     return res
 
 
+def bench_verify(torch, AttnEngine, G_B, device, reps: int):
+    """BASELINE config 3: 8 query rows (1 accepted + 7 drafts, causal among themselves) against a 64K q8_0
+    context, batch 1 and batch 8 (independent slots); the KV is streamed once per sequence."""
+    ctx, rows = 65536, 8
+    res = {}
+    for batch in (1, 8):
+        g = G_B.with_(slot_ctx=ctx + 64, window=WINDOW, n_slots=batch)
+        eng = AttnEngine(g, device)
+        dev = eng.device
+        gen = torch.Generator(device=dev)
+        gen.manual_seed(batch)
+        kvk, kvv = eng.alloc_kv_layer(False)
+        kb = torch.randn((1, 512, g.n_kv, g.head_dim), generator=gen, device=dev)
+        vb = torch.randn((1, 512, g.n_kv, g.head_dim), generator=gen, device=dev)
+        pos1 = torch.zeros(1, dtype=torch.int32, device=dev)
+        ks1 = torch.zeros(1, dtype=torch.int32, device=dev)
+        for b in range(batch):
+            ks1.fill_(b)
+            for a in range(0, ctx + rows, 512):
+                pos1.fill_(a)
+                eng.qkv_prep_store(kb, vb, kvk, kvv, pos1, kslot=ks1, rows=min(512, ctx + rows - a))
+        q = torch.randn((batch, rows, g.n_head, g.head_dim), generator=gen, device=dev).half()
+        out = torch.zeros_like(q)
+        pos = torch.full((batch,), ctx, dtype=torch.int32, device=dev)
+        kslot = torch.arange(batch, dtype=torch.int32, device=dev)
+        part = eng.alloc_part(batch, rows)
+        step = lambda: eng.launch_attn_ms(out, q, kvk, kvv, pos, kslot, None, part, batch, False, rows_per_seq=rows)  # noqa: E731
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize()
+        eng.profile_start(reps)
+        for _ in range(reps):
+            step()
+        kms = eng.profile_stop()
+        t = statistics.mean(kms) * 1e-3
+        nbytes = batch * (ctx + rows) * POS_BYTES
+        res[f"batch{batch}"] = {"kernel_us": t * 1e6, "bytes": nbytes, "TBps": nbytes / t / 1e12,
+                                "verified_rows_per_s": batch * rows / t}
+        assert eng.device_status() == 0
+        del kvk, kvv
+    return res
+
+
 def bench_serving_mix(torch, dist, AttnEngine, G_B, bd, local, rank, world, reps: int):
     """BASELINE config 4a: 64 decode slots with context lengths uniform in [1K, 128K] (seed 0), slots dealt
     to the ranks by length (no collective); one multi-slot decode call per rank per step."""
@@ -463,6 +506,9 @@ def run_gpu(args):
     gen = torch.Generator(device=f"cuda:{local}")
     gen.manual_seed(1000 + rank)                   # every rank serves its own sequence
     ctxs = [args.only_ctx] if args.only_ctx else CTXS
+    if args.case == "verify":
+        print(json.dumps({"verify": bench_verify(torch, AttnEngine, G_B, local, max(1, args.steps))}))
+        return 0
     if args.case == "prefill":                      # light run for profiling the prompt-chunk kernel
         print(json.dumps({"prefill": bench_prefill(torch, AttnEngine, G_B, local, max(1, args.steps))}))
         return 0
@@ -620,6 +666,7 @@ def run_gpu(args):
     seqsplit = bench_seq_split(torch, dist, AttnEngine, G_B, bd, local, rank, world, 20)
     torch.cuda.empty_cache()
     prefill = bench_prefill(torch, AttnEngine, G_B, local, 2) if rank == 0 else None
+    verify = bench_verify(torch, AttnEngine, G_B, local, 20) if rank == 0 else None
     if prefill is not None:
         bf16_peak = None
         try:
@@ -644,7 +691,7 @@ def run_gpu(args):
                        "launch": "one CUDA graph per step (12 decode calls through the C ABI), replayed K times"},
             "e2e": {"value": e2e_value, "unit": "TB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": ms_e2e / K},
-            "gpu_launches": launches, "roofline": roofline, "sweep": sweep, "prefill": prefill, "serving_mix_64_slots": serving, "seq_split_1m": seqsplit,
+            "gpu_launches": launches, "roofline": roofline, "sweep": sweep, "prefill": prefill, "verify_8rows_64k": verify, "serving_mix_64_slots": serving, "seq_split_1m": seqsplit,
             "clocks": clocks,
             "device_status": status,
         }
@@ -664,7 +711,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--light", action="store_true", help="profiling run: eager launches, kernel timings only")
     ap.add_argument("--only-ctx", type=int, default=0, help="restrict the decode sweep to one context")
-    ap.add_argument("--case", default="decode", choices=["decode", "prefill"], help="light run of one kernel family")
+    ap.add_argument("--case", default="decode", choices=["decode", "prefill", "verify"], help="light run of one kernel family")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)

@@ -9,6 +9,7 @@
 #include "flash_decode.cuh"
 #include "kv_append.cuh"
 #include "prefill.cuh"
+#include "verify.cuh"
 
 using namespace battn;
 
@@ -47,14 +48,26 @@ cudaError_t fd_prepare(battn_handle* h, int idx) {
 }
 
 template <int HD>
+cudaError_t vw_prepare(battn_handle* h) {
+    auto kern = vw::k_verify_wide<HD>;
+    cudaError_t e = cudaFuncSetAttribute((const void*)kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX);
+    if (e != cudaSuccess) return e;
+    int nb = 0;
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, (const void*)kern, vw::NTHREADS, vw::smem_bytes<HD>(1));
+    if (e != cudaSuccess) return e;
+    h->vw_ctas_per_sm = nb < 1 ? 1 : (nb > FD_MAX_CTAS_PER_SM ? FD_MAX_CTAS_PER_SM : nb);
+    return cudaSuccess;
+}
+
+template <int HD>
 cudaError_t fd_prepare_all(battn_handle* h) {
     cudaError_t e;
+    if ((e = vw_prepare<HD>(h)) != cudaSuccess) return e;
     if (HD == 128) e = cudaFuncSetAttribute((const void*)pf::k_prefill<128, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, pf::Cfg<128, 128>::TOTAL);
     else           e = cudaFuncSetAttribute((const void*)pf::k_prefill<256, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, pf::Cfg<256, 64>::TOTAL);
     if (e != cudaSuccess) return e;
     if ((e = fd_prepare<HD, 1>(h, 0)) != cudaSuccess) return e;
     if ((e = fd_prepare<HD, 2>(h, 1)) != cudaSuccess) return e;
-    if ((e = fd_prepare<HD, 4>(h, 2)) != cudaSuccess) return e;
     return cudaSuccess;
 }
 
@@ -164,20 +177,30 @@ int launch_flash(battn_handle* h, void* out, float* rec_out, const void* q, cons
     P.slot_ctx = g.slot_ctx; P.n_slots = g.n_slots; P.is_swa = is_swa; P.q_f16 = g.q_f16;
     P.scale_log2 = g.scale * LOG2E; P.status = h->d_status;
 
-    size_t smem;
-    if (g.HD == 128) smem = idx == 0 ? fd::smem_bytes<128, 1>(RG, n_seq) : idx == 1 ? fd::smem_bytes<128, 2>(RG, n_seq) : fd::smem_bytes<128, 4>(RG, n_seq);
-    else             smem = idx == 0 ? fd::smem_bytes<256, 1>(RG, n_seq) : idx == 1 ? fd::smem_bytes<256, 2>(RG, n_seq) : fd::smem_bytes<256, 4>(RG, n_seq);
-    if (smem > SMEM_MAX) return BATTN_ERR_CAPACITY;
-    int per_sm = (int)(SMEM_MAX / (smem + 1024));
-    if (per_sm > h->fd_ctas_per_sm[idx]) per_sm = h->fd_ctas_per_sm[idx];
-    if (per_sm < 1) per_sm = 1;
-    const int grid = h->num_sms * per_sm;
-
     cudaError_t e;
-    {
-    ProfScope prof(h, st);
-    if (g.HD == 128) e = idx == 0 ? launch_fd_kernel<128, 1>(P, grid, smem, st) : idx == 1 ? launch_fd_kernel<128, 2>(P, grid, smem, st) : launch_fd_kernel<128, 4>(P, grid, smem, st);
-    else             e = idx == 0 ? launch_fd_kernel<256, 1>(P, grid, smem, st) : idx == 1 ? launch_fd_kernel<256, 2>(P, grid, smem, st) : launch_fd_kernel<256, 4>(P, grid, smem, st);
+    if (RG > 16) {
+        // 5..8 rows: the wide verify kernel (each warp owns 8 pairs over all keys of a tile)
+        const size_t smem = g.HD == 128 ? vw::smem_bytes<128>(n_seq) : vw::smem_bytes<256>(n_seq);
+        if (smem > SMEM_MAX) return BATTN_ERR_CAPACITY;
+        int per_sm = (int)(SMEM_MAX / (smem + 1024));
+        if (per_sm > h->vw_ctas_per_sm) per_sm = h->vw_ctas_per_sm;
+        if (per_sm < 1) per_sm = 1;
+        const int grid = h->num_sms * per_sm;
+        ProfScope prof(h, st);
+        e = g.HD == 128 ? launch_pdl(vw::k_verify_wide<128>, dim3(grid), dim3(vw::NTHREADS), smem, st, P)
+                        : launch_pdl(vw::k_verify_wide<256>, dim3(grid), dim3(vw::NTHREADS), smem, st, P);
+    } else {
+        size_t smem;
+        if (g.HD == 128) smem = idx == 0 ? fd::smem_bytes<128, 1>(RG, n_seq) : fd::smem_bytes<128, 2>(RG, n_seq);
+        else             smem = idx == 0 ? fd::smem_bytes<256, 1>(RG, n_seq) : fd::smem_bytes<256, 2>(RG, n_seq);
+        if (smem > SMEM_MAX) return BATTN_ERR_CAPACITY;
+        int per_sm = (int)(SMEM_MAX / (smem + 1024));
+        if (per_sm > h->fd_ctas_per_sm[idx]) per_sm = h->fd_ctas_per_sm[idx];
+        if (per_sm < 1) per_sm = 1;
+        const int grid = h->num_sms * per_sm;
+        ProfScope prof(h, st);
+        if (g.HD == 128) e = idx == 0 ? launch_fd_kernel<128, 1>(P, grid, smem, st) : launch_fd_kernel<128, 2>(P, grid, smem, st);
+        else             e = idx == 0 ? launch_fd_kernel<256, 1>(P, grid, smem, st) : launch_fd_kernel<256, 2>(P, grid, smem, st);
     }
     if (e != cudaSuccess) return cuda_fail(h, e);
 

@@ -37,7 +37,8 @@ struct battn_handle {
     cudaEvent_t* prof_ev;    // 2 * prof_cap events while profiling, else null
     int prof_cap, prof_n;
     void* noalloc_ws;        // device address of the library's built-in scratch array on this device
-    int fd_ctas_per_sm[3];   // resident CTAs per SM of the flash-decode kernel, per NT in {1,2,4}
+    int vw_ctas_per_sm;      // resident CTAs per SM of the wide verify kernel
+    int fd_ctas_per_sm[3];   // resident CTAs per SM of the flash-decode kernel, per NT in {1,2}
     int fd_smem[3];
 };
 

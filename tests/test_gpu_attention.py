@@ -290,3 +290,63 @@ def test_decode_256k_against_exact_device_path():
         torch.cuda.synchronize()
         assert_close(to_np(out), to_np(ref), f"decode 256K vs exact ns={ns}")
     assert eng.device_status() == 0
+
+
+def test_many_ragged_slots_in_one_call():
+    """257 sequences with ragged lengths (1 .. 700 keys, several at position 0) in one multi-slot decode:
+    exercises the prefix sum over sequences, CTAs that span many items and items split over CTAs."""
+    n_seq = 257
+    g = _geom("B", slot_ctx=704, window=64, n_slots=n_seq)
+    eng, og = _engine(g), oracle_geom(g)
+    rng = np.random.default_rng(77)
+    lens = rng.integers(1, 701, size=n_seq)
+    lens[[0, 5, 200]] = 1
+    lens[[1, 256]] = 700
+    kvk, kvv = eng.alloc_kv_layer(False, fill=0x7F)
+    okvk, okvv = O.new_cache(og, False, fill=0x7F), O.new_cache(og, False, fill=0x7F)
+    _, kall, vall = draw_qkv(g, 700, 1, seed=78)
+    for s in range(n_seq):                                   # every slot gets a different slice order
+        n = int(lens[s])
+        k = np.roll(kall, s, axis=0)[:n]
+        v = np.roll(vall, 3 * s, axis=0)[:n]
+        gpu_fill(eng, k, v, kvk, kvv, False, slot=s)
+        oracle_fill(og, k, v, False, slot=s, kvk=okvk, kvv=okvv)
+    act = np.ones(n_seq, dtype=np.int32)
+    act[[7, 100]] = 0
+    q = rng.standard_normal((n_seq, 1, g.n_head, g.head_dim), dtype=np.float32).astype(np.float16).astype(np.float32)
+    out = new_out(eng, n_seq, 1, g.n_head, g.head_dim)
+    part = eng.alloc_part(n_seq, 1)
+    kslot = np.arange(n_seq)
+    eng.launch_attn_ms(out, dev_q(eng, q), kvk, kvv, dev_i32(lens - 1, eng.device), dev_i32(kslot, eng.device),
+                       dev_i32(act, eng.device), part, n_seq, False)
+    torch.cuda.synchronize()
+    got = to_np(out)
+    want = O.attend(og, q, okvk, okvv, lens - 1, kslot=kslot, act=act, rows=1)
+    live = act.astype(bool)
+    assert np.isnan(got[~live]).all()
+    assert_close(got[live], want[live], "257 ragged slots")
+    assert eng.device_status() == 0
+
+
+def test_all_idle_batch_and_zero_sized_calls():
+    from bruce_engine_b200 import capi
+    import ctypes as C
+    g = _geom("B", slot_ctx=256, window=64, n_slots=4)
+    eng = _engine(g)
+    kvk, kvv = eng.alloc_kv_layer(False, fill=0)
+    q = torch.zeros((4, 1, g.n_head, g.head_dim), dtype=torch.float16, device="cuda")
+    out = new_out(eng, 4, 1, g.n_head, g.head_dim)
+    part = eng.alloc_part(4, 1)
+    # every row idle: nothing is read, nothing is written, no error
+    eng.launch_attn_ms(out, q, kvk, kvv, dev_i32([3, 9, 0, 255], "cuda"), dev_i32([0, 1, 2, 3], "cuda"),
+                       dev_i32([0, 0, 0, 0], "cuda"), part, 4, False)
+    torch.cuda.synchronize()
+    assert torch.isnan(out).all() and eng.device_status() == 0
+    # zero sequences / zero rows are argument errors, not launches
+    p = lambda t: C.c_void_p(t.data_ptr())
+    pos = dev_i32([0], "cuda")
+    assert eng.lib.battn_decode(eng.h, p(out), p(q), p(kvk), p(kvv), p(pos), p(pos), None, p(part), 0, 0, None) == capi.ERR_ARG
+    assert eng.lib.battn_verify(eng.h, p(out), p(q), p(kvk), p(kvv), p(pos), None, None, p(part), 0, 1, 0, None) == capi.ERR_ARG
+    assert eng.lib.battn_kv_append(eng.h, p(q), p(q), p(kvk), p(kvv), p(pos), None, None, 1, 0, 0, None) == capi.ERR_ARG
+    assert eng.lib.battn_prefill(eng.h, p(out), p(q), p(kvk), p(kvv), p(pos), p(part), 513, 0, None) == capi.ERR_CAPACITY
+    assert eng.launch_count() == 2                            # only the idle decode (flash + merge) was launched
