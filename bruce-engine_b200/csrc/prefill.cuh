@@ -4,7 +4,7 @@
 // Behaviour replaced: k_attn_tc_rs_opt<NW,...> for rows > 8 and its dispatch
 // (engine/src/bruce.cu:2750-3131, 4021-4078); masks as bruce.cu:2799-2805, 3012-3029.
 //
-// Design (sm_100a), one CTA per (128-row M tile, kv head), 17 warps (8 softmax, 4 K-dequant, 4 V-dequant, 1 control):
+// Design (sm_100a), one CTA per (128-row M tile, kv head), 18 warps (8 softmax, 4 K-dequant, 4 V-dequant, 1 MMA issuer, 1 loader):
 //   * M tile = 128/G consecutive query positions x the G query heads of one kv head (row m = position
 //     m / G, head m % G, the reference's pair packing, bruce.cu:2288-2296): every dequantised K/V tile
 //     serves all G heads, and the causal diagonal of a tile spans only 128/G positions.
@@ -35,7 +35,7 @@ namespace battn {
 namespace pf {
 
 constexpr int NSOFT = 256, NDEQ = 128;              // NDEQ threads dequantise K, another NDEQ dequantise V
-constexpr int NTHREADS = NSOFT + 2 * NDEQ + 32;     // warps 0-7 softmax, 8-11 K dequant, 12-15 V dequant, 16 control
+constexpr int NTHREADS = NSOFT + 2 * NDEQ + 64;     // warps 0-7 softmax, 8-11 K dequant, 12-15 V dequant, 16 MMA issue, 17 loader
 constexpr int TMEM_COLS = 512;
 constexpr float RESCALE_THRESHOLD = 8.0f;   // log2 units
 
@@ -55,19 +55,25 @@ template <int HD, int BN>
 struct Cfg {
     static constexpr int NBLK = HD / 32;
     static constexpr int REC = HD + 2 * NBLK;
-    static constexpr int Q_BYTES = 128 * HD * 2;
+    // head_dim 128: Q lives in tensor memory (the TMEM A operand of the S MMA) and the shared memory it would
+    // take double-buffers the fp16 K and V operands, so dequantising tile j+1 overlaps the MMAs of tile j.
+    // head_dim 256 has neither the tensor-memory columns nor the shared memory for that: Q in shared memory,
+    // single K/V buffers.
+    static constexpr bool Q_TMEM = HD == 128;
+    static constexpr int KV_BUFS = HD == 128 ? 2 : 1;
+    static constexpr int RAW_STAGES = 2;
+    static constexpr int Q_BYTES = Q_TMEM ? 0 : 128 * HD * 2;
     static constexpr int K_BYTES = BN * HD * 2;
     static constexpr int V_BYTES = HD * BN * 2;
     static constexpr int RAW_BYTES = BN * REC;              // one raw K (or V) tile
     static constexpr int OFF_Q = 0;
     static constexpr int OFF_K = OFF_Q + Q_BYTES;
-    static constexpr int OFF_V = OFF_K + K_BYTES;
+    static constexpr int OFF_V = OFF_K + KV_BUFS * K_BYTES;
     static constexpr int ONES_BYTES = 16 * BN * 2;           // 16 operand rows of ones: the denominator MMA
-    static constexpr int OFF_ONES = OFF_V + V_BYTES;
-    static constexpr int RAW_STAGES = HD == 128 ? 3 : 2;     // head_dim 256 has no shared memory left for a third
+    static constexpr int OFF_ONES = OFF_V + KV_BUFS * V_BYTES;
     static constexpr int OFF_RAW = OFF_ONES + ONES_BYTES;    // [RAW_STAGES buffers][K | V]
     static constexpr int OFF_BAR = OFF_RAW + RAW_STAGES * 2 * RAW_BYTES;
-    static constexpr int N_BARS = 12;
+    static constexpr int N_BARS = 16;
     static constexpr int OFF_MISC = OFF_BAR + N_BARS * 8;    // tmem base, abort flag
     static constexpr int OFF_RMAX = OFF_MISC + 16;           // [tile parity][2 halves][128 rows] row maxima
     static constexpr int TOTAL = OFF_RMAX + 2 * 2 * 128 * 4 + 1024;   // + slack to align the base to 1024
@@ -75,13 +81,17 @@ struct Cfg {
     static constexpr int T_L = HD;                           // 16 columns, each = sum of P
     static constexpr int T_S0 = HD + 32;
     static constexpr int T_S1 = HD + 32 + BN;
-    static_assert(HD + 32 + 2 * BN <= TMEM_COLS, "tensor memory budget");
+    static constexpr int T_Q = HD + 32 + 2 * BN;             // HD/2 columns of fp16 pairs (Q_TMEM only)
+    static_assert(HD + 32 + 2 * BN + (Q_TMEM ? HD / 2 : 0) <= TMEM_COLS, "tensor memory budget");
     static_assert(RAW_BYTES % 16 == 0, "bulk copy size");
     static_assert((HD == 128 && BN == 128) || (HD == 256 && BN == 64), "supported tile shapes");
+    static_assert(TOTAL <= 226 * 1024, "shared memory budget");
 };
 
 // barrier indices
-enum { B_RAW_FULL0 = 0, B_RAW_FREE0 = 3, B_KF = 6, B_VF, B_S0, B_S1, B_P, B_PV };   // three raw stages
+// every role-to-role barrier exists twice and alternates with the tile parity, so that no role can complete
+// two phases of a barrier before its waiter has observed the first
+enum { B_RAW_FULL0 = 0, B_RAW_FREE0 = 3, B_KF0 = 6, B_VF0 = 8, B_S0 = 10, B_P0 = 12, B_PV0 = 14 };
 
 // byte offset of 16-byte chunk `chunk` (0..7) of row `row` inside a [rows x 64 halves] sub-tile stored
 // K-major with the 128-byte swizzle (8-row atoms of 1024 B, chunk index XOR row-in-atom)
@@ -223,19 +233,21 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const Params P) {
             mbar_init(&bars[B_RAW_FULL0 + st], 1);
             mbar_init(&bars[B_RAW_FREE0 + st], 2 * NDEQ / 32);
         }
-        mbar_init(&bars[B_KF], NDEQ / 32); mbar_init(&bars[B_VF], NDEQ / 32);
-        mbar_init(&bars[B_S0], 1); mbar_init(&bars[B_S1], 1);
-        mbar_init(&bars[B_P], NSOFT / 32); mbar_init(&bars[B_PV], 1);
+        for (int par = 0; par < 2; ++par) {
+            mbar_init(&bars[B_KF0 + par], NDEQ / 32); mbar_init(&bars[B_VF0 + par], NDEQ / 32);
+            mbar_init(&bars[B_S0 + par], 1); mbar_init(&bars[B_PV0 + par], 1);
+            mbar_init(&bars[B_P0 + par], NSOFT / 32);
+        }
         misc[1] = 0;
         mbar_fence_init();
     }
-    if (warp == NTHREADS / 32 - 1) {
+    if (warp == (NSOFT + 2 * NDEQ) / 32) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                          smem_u32(const_cast<uint32_t*>(&misc[0]))), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    // Q: row m = (position m / G, head m % G), fp16, 64-dim sub-tiles, swizzled
-    for (int idx = tid; idx < 128 * (HD / 8); idx += NTHREADS) {
+    // Q: row m = (position m / G, head m % G), fp16, 64-dim sub-tiles, swizzled (shared-memory variant)
+    for (int idx = tid; idx < (C::Q_TMEM ? 0 : 128 * (HD / 8)); idx += NTHREADS) {
         const int m = idx / (HD / 8), ch = idx - m * (HD / 8);
         const int r = m / G, h = m - r * G;
         uint4 val = make_uint4(0u, 0u, 0u, 0u);
@@ -258,6 +270,39 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const Params P) {
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = misc[0];
+    if constexpr (C::Q_TMEM) {
+        // Q into tensor memory: lane = row m, 32-bit column c = dims (2c, 2c+1); two threads per row
+        if (tid < NSOFT) {
+            const int m = tid & 127, half = tid >> 7;
+            const int r = m / G, h = m - r * G;
+            uint32_t qv[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) qv[i] = 0u;
+            if (r < rows_eff) {
+                const size_t qi = (((size_t)(rbase + r)) * P.Hq + kvh * G + h) * HD + half * 64;
+                if (P.q_f16) {
+                    const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(P.q) + qi);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const uint4 w = src[i];
+                        qv[4 * i] = w.x; qv[4 * i + 1] = w.y; qv[4 * i + 2] = w.z; qv[4 * i + 3] = w.w;
+                    }
+                } else {
+                    const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(P.q) + qi);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const float4 w = src[i];
+                        qv[2 * i] = pack_h2(w.x, w.y); qv[2 * i + 1] = pack_h2(w.z, w.w);
+                    }
+                }
+            }
+            tmem_st32(tmem + ((uint32_t)((warp & 3) * 32) << 16) + C::T_Q + half * 32, qv);
+            tmem_st_wait();
+        }
+        tc_fence_before();
+        __syncthreads();
+        tc_fence_after();
+    }
 
     // bounded wait that degrades to "do not wait" once any wait has run out
     auto wait = [&](int b, uint32_t parity) {
@@ -270,11 +315,60 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const Params P) {
 
     const size_t hb = (size_t)kvh * P.pstride * (size_t)REC;
 
-    if (warp == NTHREADS / 32 - 1) {
+    if (warp == (NSOFT + 2 * NDEQ) / 32) {
         // ======================= control thread: bulk copies and every MMA ===========================
         if (lane == 0) {
-            auto load_raw = [&](int j) {
+            const uint32_t idS = umma_idesc(128, BN), idO = umma_idesc(128, HD), idL = umma_idesc(128, 16);
+            const uint32_t qa = smem_u32(Qsm), ka = smem_u32(Ksm), va = smem_u32(Vsm);
+            const uint32_t oa = smem_u32(ONES);
+            auto issue_S = [&](int j) {
+                const uint32_t d = tmem + ((j & 1) ? C::T_S1 : C::T_S0);
+                const uint32_t kb = ka + (j % C::KV_BUFS) * C::K_BYTES;
+#pragma unroll
+                for (int ks = 0; ks < HD / 16; ++ks) {
+                    const uint64_t b = umma_desc(kb + (ks >> 2) * (BN * 128)) + 2 * (ks & 3);
+                    if constexpr (C::Q_TMEM) {
+                        umma_f16_ts(d, tmem + C::T_Q + 8 * ks, b, idS, ks > 0);
+                    } else {
+                        const uint64_t a = umma_desc(qa + (ks >> 2) * (128 * 128)) + 2 * (ks & 3);
+                        umma_f16(d, a, b, idS, ks > 0);
+                    }
+                }
+                umma_commit(&bars[B_S0 + (j & 1)]);
+            };
+            wait(B_KF0, 0);
+            tc_fence_after();
+            issue_S(0);
+            for (int j = 0; j < n_tiles; ++j) {
+                if (j + 1 < n_tiles) {
+                    wait(B_KF0 + ((j + 1) & 1), ((j + 1) >> 1) & 1);
+                    tc_fence_after();
+                    issue_S(j + 1);
+                }
+                wait(B_P0 + (j & 1), (j >> 1) & 1);
+                wait(B_VF0 + (j & 1), (j >> 1) & 1);
+                tc_fence_after();
+                const uint32_t vb = va + (j % C::KV_BUFS) * C::V_BYTES;
+                const uint32_t tP = tmem + ((j & 1) ? C::T_S1 : C::T_S0);     // P overwrote the S tile
+#pragma unroll
+                for (int ks = 0; ks < BN / 16; ++ks) {
+                    const uint32_t acc = (j > 0 || ks > 0) ? 1u : 0u;
+                    // keys of column half hf sit in 32-bit columns [hf*BN/2, hf*BN/2 + BN/4): 8 per k-step
+                    const uint32_t a = tP + (ks / (BN / 32)) * (BN / 2) + 8 * (ks % (BN / 32));
+                    const uint64_t b = umma_desc(vb + (ks >> 2) * (HD * 128)) + 2 * (ks & 3);
+                    const uint64_t o = umma_desc(oa + (ks >> 2) * (16 * 128)) + 2 * (ks & 3);
+                    umma_f16_ts(tmem + C::T_O, a, b, idO, acc);
+                    umma_f16_ts(tmem + C::T_L, a, o, idL, acc);             // every column = sum of P
+                }
+                umma_commit(&bars[B_PV0 + (j & 1)]);
+            }
+        }
+    } else if (warp == (NSOFT + 2 * NDEQ) / 32 + 1) {
+        // ======================= loader: streams raw K and V tiles into the ring with bulk copies ========
+        if (lane == 0) {
+            for (int j = 0; j < n_tiles; ++j) {
                 const int b = j % C::RAW_STAGES;
+                if (j >= C::RAW_STAGES) wait(B_RAW_FREE0 + b, (j / C::RAW_STAGES - 1) & 1);   // both dequant groups left it
                 const int sp = ((tile_first + j) * BN) & P.ring_mask;
                 const int nk = min(BN, P.pstride - sp);
                 const uint32_t bytes = (uint32_t)nk * REC;
@@ -282,52 +376,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const Params P) {
                 mbar_expect_tx(&bars[B_RAW_FULL0 + b], 2 * bytes);
                 bulk_g2s(dst, P.kvk + hb + (size_t)sp * REC, bytes, &bars[B_RAW_FULL0 + b]);
                 bulk_g2s(dst + C::RAW_BYTES, P.kvv + hb + (size_t)sp * REC, bytes, &bars[B_RAW_FULL0 + b]);
-            };
-            load_raw(0);
-            if (n_tiles > 1) load_raw(1);
-            if (C::RAW_STAGES > 2 && n_tiles > 2) load_raw(2);
-
-            const uint32_t idS = umma_idesc(128, BN), idO = umma_idesc(128, HD), idL = umma_idesc(128, 16);
-            const uint32_t qa = smem_u32(Qsm), ka = smem_u32(Ksm), va = smem_u32(Vsm);
-            const uint32_t oa = smem_u32(ONES);
-            auto issue_S = [&](int j) {
-                const uint32_t d = tmem + ((j & 1) ? C::T_S1 : C::T_S0);
-#pragma unroll
-                for (int ks = 0; ks < HD / 16; ++ks) {
-                    const uint64_t a = umma_desc(qa + (ks >> 2) * (128 * 128)) + 2 * (ks & 3);
-                    const uint64_t b = umma_desc(ka + (ks >> 2) * (BN * 128)) + 2 * (ks & 3);
-                    umma_f16(d, a, b, idS, ks > 0);
-                }
-                umma_commit(&bars[B_S0 + (j & 1)]);
-            };
-            wait(B_KF, 0);
-            tc_fence_after();
-            issue_S(0);
-            for (int j = 0; j < n_tiles; ++j) {
-                if (j + 1 < n_tiles) {
-                    wait(B_KF, (j + 1) & 1);
-                    tc_fence_after();
-                    issue_S(j + 1);
-                }
-                wait(B_P, j & 1);
-                wait(B_VF, j & 1);
-                tc_fence_after();
-                const uint32_t tP = tmem + ((j & 1) ? C::T_S1 : C::T_S0);     // P overwrote the S tile
-#pragma unroll
-                for (int ks = 0; ks < BN / 16; ++ks) {
-                    const uint32_t acc = (j > 0 || ks > 0) ? 1u : 0u;
-                    // keys of column half hf sit in 32-bit columns [hf*BN/2, hf*BN/2 + BN/4): 8 per k-step
-                    const uint32_t a = tP + (ks / (BN / 32)) * (BN / 2) + 8 * (ks % (BN / 32));
-                    const uint64_t b = umma_desc(va + (ks >> 2) * (HD * 128)) + 2 * (ks & 3);
-                    const uint64_t o = umma_desc(oa + (ks >> 2) * (16 * 128)) + 2 * (ks & 3);
-                    umma_f16_ts(tmem + C::T_O, a, b, idO, acc);
-                    umma_f16_ts(tmem + C::T_L, a, o, idL, acc);             // every column = sum of P
-                }
-                umma_commit(&bars[B_PV]);
-                if (j + C::RAW_STAGES < n_tiles) {                       // refill the stage tile j just left
-                    wait(B_RAW_FREE0 + j % C::RAW_STAGES, (j / C::RAW_STAGES) & 1);
-                    load_raw(j + C::RAW_STAGES);
-                }
             }
         }
     } else if (warp >= (NSOFT + NDEQ) / 32) {
@@ -346,7 +394,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const Params P) {
             const int t0 = (tile_first + j) * BN;
             const uint8_t* Vraw = RAW + b * 2 * C::RAW_BYTES + C::RAW_BYTES;
             wait(B_RAW_FULL0 + b, (j / C::RAW_STAGES) & 1);
-            if (j > 0) wait(B_PV, (j - 1) & 1);                              // P.V of the previous tile read V
+            // the P.V MMA that last read this V buffer (tile j - KV_BUFS) must be complete
+            if (j >= C::KV_BUFS) wait(B_PV0 + ((j - C::KV_BUFS) & 1), ((j - C::KV_BUFS) >> 1) & 1);
+            uint8_t* Vdst = Vsm + (j % C::KV_BUFS) * C::V_BYTES;
             {
                 // keys outside [lo, hi) were never written for this chunk's rows: their bytes are arbitrary,
                 // so their scale is forced to zero (their P is zero as well)
@@ -384,14 +434,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const Params P) {
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                         const int d = 4 * w + i;
-                        *reinterpret_cast<uint4*>(Vsm + (cc >> 3) * (HD * 128) + sw128(d, cc & 7)) =
+                        *reinterpret_cast<uint4*>(Vdst + (cc >> 3) * (HD * 128) + sw128(d, cc & 7)) =
                             make_uint4(chunk[i][0], chunk[i][1], chunk[i][2], chunk[i][3]);
                     }
                 }
             }
             proxy_fence();
             __syncwarp();
-            if (lane == 0) { mbar_arrive(&bars[B_VF]); mbar_arrive(&bars[B_RAW_FREE0 + b]); }
+            if (lane == 0) { mbar_arrive(&bars[B_VF0 + (j & 1)]); mbar_arrive(&bars[B_RAW_FREE0 + b]); }
         }
     } else if (warp >= NSOFT / 32) {
         // ======================= K dequant warps: K operand, [key][dim] ==============================
@@ -404,7 +454,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const Params P) {
             const int b = j % C::RAW_STAGES;
             const uint8_t* Kraw = RAW + b * 2 * C::RAW_BYTES;
             wait(B_RAW_FULL0 + b, (j / C::RAW_STAGES) & 1);
-            if (j > 0) wait(B_S0 + ((j - 1) & 1), ((j - 1) >> 1) & 1);     // S of the previous tile read K
+            // the S MMA that last read this K buffer (tile j - KV_BUFS) must be complete
+            if (j >= C::KV_BUFS) wait(B_S0 + ((j - C::KV_BUFS) & 1), ((j - C::KV_BUFS) >> 1) & 1);
+            uint8_t* Kdst = Ksm + (j % C::KV_BUFS) * C::K_BYTES;
             {
                 const uint8_t* src = Kraw + kkey * REC;
 #pragma unroll 2
@@ -420,12 +472,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const Params P) {
                     o.y = hmul2_u32(sub1152(widen_hi(x)), su);
                     o.z = hmul2_u32(sub1152(widen_lo(y)), su);
                     o.w = hmul2_u32(sub1152(widen_hi(y)), su);
-                    *reinterpret_cast<uint4*>(Ksm + (ch >> 3) * (BN * 128) + sw128(krow, ch & 7)) = o;
+                    *reinterpret_cast<uint4*>(Kdst + (ch >> 3) * (BN * 128) + sw128(krow, ch & 7)) = o;
                 }
             }
             proxy_fence();
             __syncwarp();
-            if (lane == 0) { mbar_arrive(&bars[B_KF]); mbar_arrive(&bars[B_RAW_FREE0 + b]); }
+            if (lane == 0) { mbar_arrive(&bars[B_KF0 + (j & 1)]); mbar_arrive(&bars[B_RAW_FREE0 + b]); }
         }
     } else {
         // ======================= softmax warps: two threads per accumulator row ========================
@@ -503,7 +555,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const Params P) {
             const bool warp_need = __any_sync(0xffffffffu, need);
             if (warp_need) {
                 if (j > 0) {
-                    wait(B_PV, (j - 1) & 1);                                // O must be complete before it is rescaled
+                    wait(B_PV0 + ((j - 1) & 1), ((j - 1) >> 1) & 1);        // O must be complete before it is rescaled
                     tc_fence_after();
                     const float alpha = fast_exp2((m_ref - m_new) * c2);  // 1 for rows that keep their reference
 #pragma unroll 1
@@ -551,10 +603,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const Params P) {
             tmem_st_wait();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&bars[B_P]);
+            if (lane == 0) mbar_arrive(&bars[B_P0 + (j & 1)]);
         }
         // ---- epilogue: O / sum(P) -> global; each thread writes half of its row -----------------------
-        wait(B_PV, (n_tiles - 1) & 1);
+        wait(B_PV0 + ((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1);
         tc_fence_after();
         const float l = __uint_as_float(tmem_ld1(tmem + lane_base + C::T_L));
         const float il = l > 0.f ? 1.f / l : 0.f;
@@ -586,7 +638,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const Params P) {
         tc_fence_before();
     }
     __syncthreads();
-    if (warp == NTHREADS / 32 - 1) {
+    if (warp == (NSOFT + 2 * NDEQ) / 32) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
     }
