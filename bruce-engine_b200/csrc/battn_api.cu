@@ -9,6 +9,7 @@
 #include "flash_decode.cuh"
 #include "kv_append.cuh"
 #include "prefill.cuh"
+#include "prefill_hd128.cuh"
 #include "verify.cuh"
 
 using namespace battn;
@@ -63,7 +64,7 @@ template <int HD>
 cudaError_t fd_prepare_all(battn_handle* h) {
     cudaError_t e;
     if ((e = vw_prepare<HD>(h)) != cudaSuccess) return e;
-    if (HD == 128) e = cudaFuncSetAttribute((const void*)pf::k_prefill<128, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, pf::Cfg<128, 128>::TOTAL);
+    if (HD == 128) e = cudaFuncSetAttribute((const void*)pf128::k_prefill_hd128, cudaFuncAttributeMaxDynamicSharedMemorySize, pf128::TOTAL);
     else           e = cudaFuncSetAttribute((const void*)pf::k_prefill<256, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, pf::Cfg<256, 64>::TOTAL);
     if (e != cudaSuccess) return e;
     if ((e = fd_prepare<HD, 1>(h, 0)) != cudaSuccess) return e;
@@ -230,7 +231,7 @@ int launch_prefill(battn_handle* h, void* out, const void* q, const uint8_t* kvk
     const dim3 grid((rows + MR - 1) / MR, g.Hkv);
     {
         ProfScope prof(h, st);
-        if (g.HD == 128) pf::k_prefill<128, 128><<<grid, pf::NTHREADS, pf::Cfg<128, 128>::TOTAL, st>>>(P);
+        if (g.HD == 128) pf128::k_prefill_hd128<<<grid, pf128::NTHREADS, pf128::TOTAL, st>>>(P);
         else             pf::k_prefill<256, 64><<<grid, pf::NTHREADS, pf::Cfg<256, 64>::TOTAL, st>>>(P);
     }
     h->launches += 1;

@@ -4,7 +4,7 @@
 // Behaviour replaced: k_attn_tc_rs_opt<NW,...> for rows > 8 and its dispatch
 // (engine/src/bruce.cu:2750-3131, 4021-4078); masks as bruce.cu:2799-2805, 3012-3029.
 //
-// Design (sm_100a), one CTA per (128-row M tile, kv head), 18 warps (8 softmax, 4 K-dequant, 4 V-dequant, 1 MMA issuer, 1 loader):
+// Design (sm_100a), one CTA per (128-row M tile, kv head), 20 warps (8 softmax, 4 K-dequant, 4 V-dequant, 1 MMA issuer, 1 loader, 2 idle):
 //   * M tile = 128/G consecutive query positions x the G query heads of one kv head (row m = position
 //     m / G, head m % G, the reference's pair packing, bruce.cu:2288-2296): every dequantised K/V tile
 //     serves all G heads, and the causal diagonal of a tile spans only 128/G positions.
@@ -35,7 +35,12 @@ namespace battn {
 namespace pf {
 
 constexpr int NSOFT = 256, NDEQ = 128;              // NDEQ threads dequantise K, another NDEQ dequantise V
-constexpr int NTHREADS = NSOFT + 2 * NDEQ + 64;     // warps 0-7 softmax, 8-11 K dequant, 12-15 V dequant, 16 MMA issue, 17 loader
+constexpr int NTHREADS = NSOFT + 2 * NDEQ + 128;    // warps 0-7 softmax, 8-11 K dequant, 12-15 V dequant, 16 MMA issue, 17 loader, 18-19 idle
+// Registers per thread: the kernel launches with REGS_LAUNCH everywhere (five warps share each quarter of the
+// register file); every warpgroup then resizes itself for its role with setmaxnreg, so the softmax warps can
+// hold a whole S row segment in registers.  Per quarter: 2*REGS_SOFT + 2*REGS_DEQ + REGS_CTL <= 5*REGS_LAUNCH.
+constexpr int REGS_LAUNCH = 96, REGS_SOFT = 144, REGS_DEQ = 72, REGS_CTL = 40;
+static_assert(2 * REGS_SOFT + 2 * REGS_DEQ + REGS_CTL <= 5 * REGS_LAUNCH, "register budget per scheduler");
 constexpr int TMEM_COLS = 512;
 constexpr float RESCALE_THRESHOLD = 8.0f;   // log2 units
 
@@ -190,13 +195,32 @@ __device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t (&r)[3
         : "r"(taddr)
         : "memory");
 }
+// three-input maximum and two-wide fp32 multiply-add: each halves the instruction count of its softmax pass
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t pack_f2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void ffma2(float& o0, float& o1, float x0, float x1, uint64_t mul, uint64_t add) {
+    asm("{\n\t.reg .b64 a, r;\n\tmov.b64 a, {%2, %3};\n\tfma.rn.f32x2 r, a, %4, %5;\n\tmov.b64 {%0, %1}, r;\n\t}"
+        : "=f"(o0), "=f"(o1)
+        : "f"(x0), "f"(x1), "l"(mul), "l"(add));
+}
+template <int N> __device__ __forceinline__ void regs_grow() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N> __device__ __forceinline__ void regs_shrink() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 template <int HD, int BN>
-__global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const Params P) {
+__global__ void __maxnreg__(REGS_LAUNCH) k_prefill(const Params P) {
     using C = Cfg<HD, BN>;
     constexpr int NBLK = C::NBLK, REC = C::REC;
     constexpr int HC = BN / 2;                               // S columns per softmax thread
+    constexpr int NCH = HC / 32;                             // ... in TMEM loads of 32 columns
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);      // 1024-byte aligned
     uint8_t* Qsm = smem + C::OFF_Q;
@@ -315,8 +339,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const Params P) {
 
     const size_t hb = (size_t)kvh * P.pstride * (size_t)REC;
 
+    if (warp >= (NSOFT + 2 * NDEQ) / 32) regs_shrink<REGS_CTL>();          // the whole last warpgroup
     if (warp == (NSOFT + 2 * NDEQ) / 32) {
-        // ======================= control thread: bulk copies and every MMA ===========================
+        // ======================= control thread: every MMA =============================================
         if (lane == 0) {
             const uint32_t idS = umma_idesc(128, BN), idO = umma_idesc(128, HD), idL = umma_idesc(128, 16);
             const uint32_t qa = smem_u32(Qsm), ka = smem_u32(Ksm), va = smem_u32(Vsm);
@@ -378,8 +403,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const Params P) {
                 bulk_g2s(dst + C::RAW_BYTES, P.kvv + hb + (size_t)sp * REC, bytes, &bars[B_RAW_FULL0 + b]);
             }
         }
+    } else if (warp > (NSOFT + 2 * NDEQ) / 32 + 1) {
+        // idle warps that complete the last warpgroup
     } else if (warp >= (NSOFT + NDEQ) / 32) {
         // ======================= V dequant warps: V^T operand, [dim][key] ============================
+        regs_shrink<REGS_DEQ>();
         const int t = tid - NSOFT - NDEQ, wq = t >> 5;
         constexpr int NWG = HD / 16;                            // groups of four dim-words
         constexpr int UPT = (HD / 4) * (BN / 8) / NDEQ;         // micro-tiles (4 dims x 8 keys) per thread
@@ -445,6 +473,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const Params P) {
         }
     } else if (warp >= NSOFT / 32) {
         // ======================= K dequant warps: K operand, [key][dim] ==============================
+        regs_shrink<REGS_DEQ>();
         const int t = tid - NSOFT;
         const int krow = t & (BN - 1);                          // each thread converts KCH chunks of one row
         constexpr int KCH = (BN * HD / 8) / NDEQ;
@@ -481,6 +510,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const Params P) {
         }
     } else {
         // ======================= softmax warps: two threads per accumulator row ========================
+        regs_grow<REGS_SOFT>();
         const int m = tid & 127;                               // row = TMEM lane
         const int half = tid >> 7;                             // which half of the S columns / O columns
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
@@ -499,55 +529,56 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const Params P) {
             const bool masked = !(t0 >= full_lo && t0 + BN - 1 <= p_first) || rows_eff < MR;
             wait(B_S0 + (j & 1), (j >> 1) & 1);
             tc_fence_after();
-            // Visibility of this thread's columns, one bit per column: all ones on tiles every row sees
-            // completely (bruce.cu:2927-2928), otherwise built by a small rolled loop.  One code path then
-            // serves both cases, which keeps the hot loop short enough for the instruction cache.
-            uint32_t vis[HC / 32];
+            // One read of this thread's S columns; they stay in registers for both the maximum and the
+            // exponentials.
+            uint32_t v[NCH][32];
 #pragma unroll
-            for (int c = 0; c < HC / 32; ++c) vis[c] = 0xffffffffu;
+            for (int c = 0; c < NCH; ++c) tmem_ld32_nowait(tS + c * 32, v[c]);
+            tmem_ld_wait();
             if (masked) {
+                // Tiles that some row of the CTA sees only partly (the causal diagonal, the window edge, a
+                // ragged last chunk): hidden columns are replaced by "minus infinity" (bruce.cu:3021-3028),
+                // after which the common code below needs no mask.  The visibility bits are built by a rolled
+                // loop to keep this rarely executed path small.
 #pragma unroll
-                for (int c = 0; c < HC / 32; ++c) {
+                for (int c = 0; c < NCH; ++c) {
                     uint32_t bits = 0u;
 #pragma unroll 1
                     for (int i = 0; i < 32; ++i) {
                         const int key = t0 + kappa(half * HC + c * 32 + i);
-                        const bool ok = row_ok && key <= prow && key >= row_lo;     // bruce.cu:3021-3028
+                        const bool ok = row_ok && key <= prow && key >= row_lo;
                         bits |= (ok ? 1u : 0u) << i;
                     }
-                    vis[c] = bits;
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (!((bits >> i) & 1u)) v[c][i] = __float_as_uint(NEG_BIG);
                 }
             }
-            float mx = NEG_BIG;
-#pragma unroll 1
-            for (int c = 0; c < HC / 32; ++c) {
-                uint32_t v[32];
-                tmem_ld32(tS + c * 32, v);
-                const uint32_t vb = vis[c];
-                float m0 = NEG_BIG, m1 = NEG_BIG, m2 = NEG_BIG, m3 = NEG_BIG;
-                if (vb == 0xffffffffu) {                                    // the common case: nothing masked
+            float mx;
+            {
+                float m0 = __uint_as_float(v[0][0]), m1 = __uint_as_float(v[0][1]);
+                float m2 = __uint_as_float(v[0][2]), m3 = __uint_as_float(v[0][3]);
 #pragma unroll
-                    for (int i = 0; i < 32; i += 4) {
-                        m0 = fmaxf(m0, __uint_as_float(v[i]));
-                        m1 = fmaxf(m1, __uint_as_float(v[i + 1]));
-                        m2 = fmaxf(m2, __uint_as_float(v[i + 2]));
-                        m3 = fmaxf(m3, __uint_as_float(v[i + 3]));
+                for (int c = 0; c < NCH; ++c) {
+#pragma unroll
+                    for (int i = (c == 0 ? 4 : 0); i + 8 <= 32; i += 8) {
+                        m0 = fmax3(m0, __uint_as_float(v[c][i]), __uint_as_float(v[c][i + 1]));
+                        m1 = fmax3(m1, __uint_as_float(v[c][i + 2]), __uint_as_float(v[c][i + 3]));
+                        m2 = fmax3(m2, __uint_as_float(v[c][i + 4]), __uint_as_float(v[c][i + 5]));
+                        m3 = fmax3(m3, __uint_as_float(v[c][i + 6]), __uint_as_float(v[c][i + 7]));
                     }
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 32; i += 4) {
-                        m0 = fmaxf(m0, (vb >> i) & 1u ? __uint_as_float(v[i]) : NEG_BIG);
-                        m1 = fmaxf(m1, (vb >> (i + 1)) & 1u ? __uint_as_float(v[i + 1]) : NEG_BIG);
-                        m2 = fmaxf(m2, (vb >> (i + 2)) & 1u ? __uint_as_float(v[i + 2]) : NEG_BIG);
-                        m3 = fmaxf(m3, (vb >> (i + 3)) & 1u ? __uint_as_float(v[i + 3]) : NEG_BIG);
+                    if (c == 0) {
+                        m0 = fmax3(m0, __uint_as_float(v[0][28]), __uint_as_float(v[0][29]));
+                        m1 = fmax3(m1, __uint_as_float(v[0][30]), __uint_as_float(v[0][31]));
                     }
                 }
-                mx = fmaxf(mx, fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)));
+                mx = fmax3(fmaxf(m0, m1), m2, m3);
             }
-            // exchange with the thread that holds the other half of this row; the buffer alternates with
-            // the tile parity so that a fast thread's next write cannot overtake a slow partner's read
+            // exchange with the thread that holds the other half of this row (same lane, warp +-4); the buffer
+            // alternates with the tile parity so that a fast thread's next write cannot overtake a slow
+            // partner's read
             rmax[(j & 1) * 256 + half * 128 + m] = mx;
-            named_bar_sync(2, NSOFT);
+            named_bar_sync(2 + (warp & 3), 64);
             mx = fmaxf(mx, rmax[(j & 1) * 256 + (half ^ 1) * 128 + m]);
             float m_new = fmaxf(m_ref, mx);
             const bool need = m_new > m_ref + thr;
@@ -575,29 +606,22 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const Params P) {
                 }
                 m_ref = m_new;
             }
-            const float nb = -m_ref * c2;
-#pragma unroll 1
-            for (int c = 0; c < HC / 32; ++c) {
-                uint32_t v[32];
-                tmem_ld32(tS + c * 32, v);                                  // second read: cheaper than 64 live registers
-                const uint32_t vb = vis[c];
+            // p = 2^(s*c2 - m_ref*c2); a row that has seen no key yet keeps the offset at zero, so its hidden
+            // columns ("minus infinity") still come out as exactly zero
+            const float nb = m_ref > 0.5f * NEG_BIG ? -m_ref * c2 : 0.f;
+            const uint64_t c2p = pack_f2(c2, c2), nbp = pack_f2(nb, nb);
+            // P (fp16 pairs) overwrites S columns this thread owns and has already read: chunk c of S
+            // (32 columns) becomes 16 columns of P at the start of the thread's region; nobody else reads
+            // or writes them, and the MMA that refills this S buffer is ordered after the P.V MMA
+#pragma unroll
+            for (int c = 0; c < NCH; ++c) {
                 uint32_t pk[16];
-                if (vb == 0xffffffffu) {                                    // the common case: nothing masked
 #pragma unroll
-                    for (int i = 0; i < 32; i += 2)
-                        pk[i >> 1] = pack_h2(fast_exp2(fmaf(__uint_as_float(v[i]), c2, nb)),
-                                             fast_exp2(fmaf(__uint_as_float(v[i + 1]), c2, nb)));
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        const float e0 = (vb >> i) & 1u ? fast_exp2(fmaf(__uint_as_float(v[i]), c2, nb)) : 0.f;
-                        const float e1 = (vb >> (i + 1)) & 1u ? fast_exp2(fmaf(__uint_as_float(v[i + 1]), c2, nb)) : 0.f;
-                        pk[i >> 1] = pack_h2(e0, e1);
-                    }
+                for (int i = 0; i < 32; i += 2) {
+                    float e0, e1;
+                    ffma2(e0, e1, __uint_as_float(v[c][i]), __uint_as_float(v[c][i + 1]), c2p, nbp);
+                    pk[i >> 1] = pack_h2(fast_exp2(e0), fast_exp2(e1));
                 }
-                // P (fp16 pairs) overwrites S columns this thread owns and has already read: chunk c of S
-                // (32 columns) becomes 16 columns of P at the start of the thread's region; nobody else reads
-                // or writes them, and the MMA that refills this S buffer is ordered after the P.V MMA
                 tmem_st16(tS + c * 16, pk);
             }
             tmem_st_wait();

@@ -1,5 +1,5 @@
-"""Parity of the tcgen05 prompt-chunk kernel with the CPU oracle (same tolerance as the other
-attention paths).  A prompt is processed the way the reference does it (bruce.cu:7665-7737): for
+"""Parity of the tcgen05 prompt-chunk kernel with the CPU oracle (tolerances: tests/util.py; this path
+has its own per-(row, head) bound, explained there).  A prompt is processed the way the reference does it (bruce.cu:7665-7737): for
 each chunk, append the chunk's K/V rows, then attend the chunk's query rows against the cache."""
 import numpy as np
 import pytest
@@ -7,7 +7,7 @@ import torch
 
 from oracle import oracle as O
 from tests.gpu_util import dev_i32, dev_q, gpu_fill, new_out, to_np
-from tests.util import assert_close, draw_qkv, oracle_fill, oracle_geom
+from tests.util import PROMPT_HEAD_REL_TOL, assert_close, draw_qkv, oracle_fill, oracle_geom
 
 pytestmark = pytest.mark.gpu
 
@@ -41,7 +41,8 @@ def _run_prompt(name, n_prompt, chunk, is_swa, window, seed, check_chunks=None):
         if check_chunks is not None and ci not in check_chunks:
             continue
         want = O.attend(og, q[None, a:a + rows], okvk, okvv, [a], rows=rows, is_swa=is_swa)
-        mabs, rel = assert_close(to_np(out), want, f"{name} swa={is_swa} chunk {ci} rows {rows}")
+        mabs, rel = assert_close(to_np(out), want, f"{name} swa={is_swa} chunk {ci} rows {rows}",
+                                 head_tol=PROMPT_HEAD_REL_TOL)
         worst = (max(worst[0], mabs), max(worst[1], rel))
     assert (kvk.cpu().numpy() == okvk).all() and (kvv.cpu().numpy() == okvv).all()
     assert eng.device_status() == 0
@@ -94,5 +95,5 @@ def test_prefill_matches_exact_device_path_at_depth():
         ws = torch.empty(eng.exact_workspace_bytes(1, rows, 4), dtype=torch.uint8, device="cuda")
         eng.attn_exact(ref, q, kvk, kvv, pos, ws, 1, rows, 4, is_swa)
         torch.cuda.synchronize()
-        assert_close(to_np(out), to_np(ref), f"prefill at depth swa={is_swa}")
+        assert_close(to_np(out), to_np(ref), f"prefill at depth swa={is_swa}", head_tol=PROMPT_HEAD_REL_TOL)
     assert eng.device_status() == 0
