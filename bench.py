@@ -270,9 +270,11 @@ def prefill_pairs(n_prompt: int, window: int | None) -> int:
     return window * (window + 1) // 2 + (n_prompt - window) * window
 
 
-def bench_prefill(torch, AttnEngine, G_B, device, reps: int):
+def bench_prefill(torch, AttnEngine, G_B, device, reps: int, window: int = WINDOW):
     """BASELINE config 2: a 16,384-token prompt in 512-row chunks against a growing q8_0 cache, one
-    full-causal layer and one window-4096 layer; each chunk = append 512 K/V rows, then attend."""
+    full-causal layer and one sliding-window layer (window 4096 on the bench geometry); each chunk =
+    append 512 K/V rows, then attend."""
+    WINDOW = window
     g = G_B.with_(slot_ctx=PREFILL_PROMPT, window=WINDOW)
     eng = AttnEngine(g, device)
     dev = eng.device
@@ -510,7 +512,9 @@ def run_gpu(args):
         print(json.dumps({"verify": bench_verify(torch, AttnEngine, G_B, local, max(1, args.steps))}))
         return 0
     if args.case == "prefill":                      # light run for profiling the prompt-chunk kernel
-        print(json.dumps({"prefill": bench_prefill(torch, AttnEngine, G_B, local, max(1, args.steps))}))
+        from bruce_engine_b200.layout import G_R
+        print(json.dumps({"prefill": bench_prefill(torch, AttnEngine, G_B, local, max(1, args.steps)),
+                          "prefill_hd256_w1024": bench_prefill(torch, AttnEngine, G_R, local, max(1, args.steps), window=1024)}))
         return 0
     layers = [Layer(c, s, gen, torch, AttnEngine, G_B, local) for c in ctxs for s in (False, True)]
     torch.cuda.synchronize()

@@ -330,6 +330,7 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill(const Params P) {
 
     // bounded wait that degrades to "do not wait" once any wait has run out
     auto wait = [&](int b, uint32_t parity) {
+        if (mbar_try_wait(&bars[b], parity)) return;               // the common case costs one poll
         if (misc[1]) return;
         if (!mbar_wait_backoff(&bars[b], parity)) {
             atomicOr(P.status, BATTN_DEV_WAIT_TIMEOUT);

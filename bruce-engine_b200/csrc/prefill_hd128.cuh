@@ -216,7 +216,7 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill_hd128(const Params P) {
             uint8_t* ring = smem + (isv ? OFF_RAWV : OFF_RAWK);
             const int full = isv ? B_VRAW_FULL : B_KRAW_FULL, free_ = isv ? B_VRAW_FREE : B_KRAW_FREE;
             for (int j = 0; j < n_tiles; ++j) {
-                if (j >= NB) wait(free_ + slot(j), phase(j - NB), 20);          // the dequant group left it
+                if (j >= NB) wait(free_ + slot(j), phase(j - NB), 200);         // the dequant group left it (no hurry: the ring is four deep)
                 const int sp = ((tile_first + j) * BN) & P.ring_mask;
                 const int nk = min(BN, P.pstride - sp);
                 const uint32_t bytes = (uint32_t)nk * REC;
