@@ -326,6 +326,59 @@ def bench_prefill(torch, AttnEngine, G_B, device, reps: int, window: int = WINDO
     return res
 
 
+def bench_qkv_prep(torch, AttnEngine, G_B, device, reps: int):
+    """The fused QKV prologue + append (L2 scale, RoPE, sqk, q8_0 store, fp16 q for the attention kernels) on a
+    512-row prompt chunk and on a 64-slot decode batch: microseconds per call and algorithmic HBM bytes per second
+    (q in and out, k, v, the row's tables, the records written)."""
+    res = {}
+    for name, n_seq, rows in (("prompt_chunk_512_rows", 1, 512), ("decode_64_slots", 64, 1)):
+        g = G_B.with_(slot_ctx=4096, window=WINDOW, n_slots=n_seq)
+        eng = AttnEngine(g, device)
+        dev = eng.device
+        gen = torch.Generator(device=dev)
+        gen.manual_seed(11)
+        m = n_seq * rows
+        q = torch.randn((m, g.n_head, g.head_dim), generator=gen, device=dev)
+        k = torch.randn((m, g.n_kv, g.head_dim), generator=gen, device=dev)
+        v = torch.randn((m, g.n_kv, g.head_dim), generator=gen, device=dev)
+        sqk = torch.ones((g.n_head, g.head_dim), device=dev)
+        q16 = torch.empty((m, g.n_head, g.head_dim), dtype=torch.float16, device=dev)
+        cs = torch.zeros((m, g.head_dim), device=dev)
+        sn = torch.zeros((m, g.head_dim), device=dev)
+        pos = torch.full((n_seq,), 1000, dtype=torch.int32, device=dev)
+        kslot = torch.arange(n_seq, dtype=torch.int32, device=dev) if n_seq > 1 else None
+        kvk, kvv = eng.alloc_kv_layer(False)
+        eng.rope_tables(cs, sn, pos, rows=rows)
+
+        def call():
+            eng.qkv_prep(q16, q, k, v, sqk, cs, sn, kvk, kvv, pos, kslot=kslot, rows=rows)
+
+        for _ in range(5):
+            call()
+        torch.cuda.synchronize()
+        # 20 calls per graph, so that the figure is device time and not the host's launch rate
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(20):
+                call()
+        graph.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / (reps * 20)
+        del graph
+        per_row = g.n_head * g.head_dim * (4 + 2) + 2 * g.n_kv * g.head_dim * 4 + 2 * (g.head_dim // 2) * 4 + \
+            2 * g.n_kv * (g.head_dim + g.head_dim // 16)
+        res[name] = {"us_per_call": us, "bytes": m * per_row, "GBps": m * per_row / (us * 1e-6) / 1e9,
+                     "rows_per_s": m / (us * 1e-6)}
+        assert eng.device_status() == 0
+    return res
+
+
 def bench_verify(torch, AttnEngine, G_B, device, reps: int):
     """BASELINE config 3: 8 query rows (1 accepted + 7 drafts, causal among themselves) against a 64K q8_0
     context, batch 1 and batch 8 (independent slots); the KV is streamed once per sequence."""
@@ -509,7 +562,8 @@ def run_gpu(args):
     gen.manual_seed(1000 + rank)                   # every rank serves its own sequence
     ctxs = [args.only_ctx] if args.only_ctx else CTXS
     if args.case == "verify":
-        print(json.dumps({"verify": bench_verify(torch, AttnEngine, G_B, local, max(1, args.steps))}))
+        print(json.dumps({"verify": bench_verify(torch, AttnEngine, G_B, local, max(1, args.steps)),
+                          "qkv_prep": bench_qkv_prep(torch, AttnEngine, G_B, local, 50)}))
         return 0
     if args.case == "prefill":                      # light run for profiling the prompt-chunk kernel
         from bruce_engine_b200.layout import G_R
@@ -671,6 +725,7 @@ def run_gpu(args):
     torch.cuda.empty_cache()
     prefill = bench_prefill(torch, AttnEngine, G_B, local, 2) if rank == 0 else None
     verify = bench_verify(torch, AttnEngine, G_B, local, 20) if rank == 0 else None
+    qkv_prep = bench_qkv_prep(torch, AttnEngine, G_B, local, 50) if rank == 0 else None
     if prefill is not None:
         bf16_peak = None
         try:
@@ -695,7 +750,7 @@ def run_gpu(args):
                        "launch": "one CUDA graph per step (12 decode calls through the C ABI), replayed K times"},
             "e2e": {"value": e2e_value, "unit": "TB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": ms_e2e / K},
-            "gpu_launches": launches, "roofline": roofline, "sweep": sweep, "prefill": prefill, "verify_8rows_64k": verify, "serving_mix_64_slots": serving, "seq_split_1m": seqsplit,
+            "gpu_launches": launches, "roofline": roofline, "sweep": sweep, "prefill": prefill, "verify_8rows_64k": verify, "qkv_prep": qkv_prep, "serving_mix_64_slots": serving, "seq_split_1m": seqsplit,
             "clocks": clocks,
             "device_status": status,
         }

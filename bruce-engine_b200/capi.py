@@ -37,6 +37,8 @@ SIGNATURES = {
     "battn_workspace_bytes": (_I, [_P, _I, _I, _SZP]),
     "battn_exact_workspace_bytes": (_I, [_P, _I, _I, _I, _SZP]),
     "battn_kv_append": (_I, [_P] * 8 + [_I, _I, _I, _P]),
+    "battn_qkv_prep": (_I, [_P] * 8 + [_I] + [_P] * 5 + [_I, _I, _I, _P]),
+    "battn_rope_tables": (_I, [_P] * 4 + [_I, _I, _P]),
     "battn_decode": (_I, [_P] * 9 + [_I, _I, _P]),
     "battn_decode_noalloc": (_I, [_P] * 8 + [_I, _I, _P]),
     "battn_verify": (_I, [_P] * 9 + [_I, _I, _I, _P]),

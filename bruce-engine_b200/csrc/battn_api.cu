@@ -8,6 +8,7 @@
 #include "exact.cuh"
 #include "flash_decode.cuh"
 #include "kv_append.cuh"
+#include "qkv_prep.cuh"
 #include "prefill.cuh"
 #include "prefill_hd128.cuh"
 #include "verify.cuh"
@@ -342,6 +343,44 @@ int battn_kv_append(battn_handle* h, const float* k, const float* v, uint8_t* kv
     cudaError_t e;
     if (g.HD == 128) e = launch_pdl(k_kv_append<128>, dim3(blocks), dim3(256), 0, st, P);
     else             e = launch_pdl(k_kv_append<256>, dim3(blocks), dim3(256), 0, st, P);
+    h->launches += 1;
+    if (e == cudaSuccess) e = cudaGetLastError();
+    return e == cudaSuccess ? BATTN_OK : cuda_fail(h, e);
+}
+
+int battn_qkv_prep(battn_handle* h, void* q_out, const float* q, const float* k, const float* v, const float* sqk,
+                   const float* cs, const float* sn, int theta_sel, uint8_t* kvk, uint8_t* kvv, const int* pos,
+                   const int* kslot, const int* act, int n_seq, int rows_per_seq, int is_swa, void* stream) {
+    const int rc = check_seq_args(h, k, v, kvk, kvv, pos, kslot, n_seq, rows_per_seq, MAX_PREFILL);
+    if (rc) return rc;
+    if (!q_out || !q || !sqk || !cs || !sn || (theta_sel != 1 && theta_sel != 2)) return BATTN_ERR_ARG;
+    if ((((uintptr_t)q_out | (uintptr_t)q | (uintptr_t)sqk | (uintptr_t)cs | (uintptr_t)sn) & 15) != 0) return BATTN_ERR_ARG;
+    const Geom& g = h->g;
+    if (is_swa && rows_per_seq > g.ring) return BATTN_ERR_CAPACITY;        // as battn_kv_append
+    PrepParams P;
+    P.q = q; P.q_out = q_out; P.k = k; P.v = v; P.sqk = sqk; P.cs = cs; P.sn = sn; P.kvk = kvk; P.kvv = kvv;
+    P.pos = pos; P.kslot = kslot; P.act = act; P.n_seq = n_seq; P.rows = rows_per_seq; P.Hq = g.Hq; P.Hkv = g.Hkv;
+    P.table_off = theta_sel == 2 ? g.HD / 2 : 0; P.q_out_f16 = g.q_f16;
+    P.pstride = is_swa ? g.ring : g.slot_ctx; P.ring_mask = is_swa ? g.ring - 1 : -1;
+    P.n_slots = g.n_slots; P.status = h->d_status;
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e;
+    if (g.HD == 128) e = launch_pdl(k_qkv_prep<128>, dim3(n_seq * rows_per_seq), dim3(256), 0, st, P);
+    else             e = launch_pdl(k_qkv_prep<256>, dim3(n_seq * rows_per_seq), dim3(256), 0, st, P);
+    h->launches += 1;
+    if (e == cudaSuccess) e = cudaGetLastError();
+    return e == cudaSuccess ? BATTN_OK : cuda_fail(h, e);
+}
+
+int battn_rope_tables(battn_handle* h, float* cs, float* sn, const int* pos, int n_seq, int rows_per_seq, void* stream) {
+    if (!h || !cs || !sn || !pos || n_seq < 1 || rows_per_seq < 1 || rows_per_seq > MAX_PREFILL) return BATTN_ERR_ARG;
+    const Geom& g = h->g;
+    TableParams P;
+    P.cs = cs; P.sn = sn; P.pos = pos; P.rows = rows_per_seq; P.n_rows = n_seq * rows_per_seq;
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e;
+    if (g.HD == 128) e = launch_pdl(k_rope_tables<128>, dim3(P.n_rows), dim3(64), 0, st, P);
+    else             e = launch_pdl(k_rope_tables<256>, dim3(P.n_rows), dim3(128), 0, st, P);
     h->launches += 1;
     if (e == cudaSuccess) e = cudaGetLastError();
     return e == cudaSuccess ? BATTN_OK : cuda_fail(h, e);

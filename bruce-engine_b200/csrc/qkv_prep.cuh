@@ -1,0 +1,188 @@
+// QKV prologue fused with the quantise-on-append: per head an L2 scale, NeoX rotate-half RoPE from
+// per-row cos/sin tables and (q only) the per-head sqk scale; k is then quantised into the q8_0 cache,
+// v is quantised raw.  Replaces k_qkv_prep / k_qkv_prep_rows / k_qkv_prep_fast / k_qkv_prep_fast_ms
+// (engine/src/bruce.cu:645-710, 1656-1725, 1732-1812, 1835-1918) and the table kernels
+// k_rope_tables / k_rope_tables_rows / k_rope_tables_rows_ms (:328-336, 1641-1654, 1821-1833).
+//
+// HBM-bound element-wise work: one CTA per row, one warp per head (the whole head lives in the warp's
+// registers, 16-byte loads and stores), no shared memory, no block barrier.  Every fp32 step is written
+// with explicit round-to-nearest intrinsics in the order nvcc generates for the reference source (which
+// fuses x0*c - x1*s into fma(x0, c, -(x1*s)) and the squares into a chain of fma), so q and the K/V
+// records are bit-identical to the reference kernel's and do not depend on this file's compiler flags.
+// q can be emitted as fp16 for the attention kernels in the same pass.
+#pragma once
+#include "common.cuh"
+
+namespace battn {
+
+struct PrepParams {
+    const float* q;       // [n_seq*rows][Hq][HD]
+    void* q_out;          // same shape, fp32 (may alias q) or fp16
+    const float* k;       // [n_seq*rows][Hkv][HD]
+    const float* v;
+    const float* sqk;     // [Hq][HD]
+    const float* cs;      // [n_seq*rows][HD]: two tables of HD/2 per row
+    const float* sn;
+    uint8_t* kvk;
+    uint8_t* kvv;
+    const int* pos;
+    const int* kslot;     // null: single sequence, caches point at the slot base
+    const int* act;       // null: every sequence active
+    int n_seq, rows, Hq, Hkv;
+    int table_off;        // 0 or HD/2 (second table)
+    int q_out_f16;
+    int pstride, ring_mask, n_slots;
+    int* status;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(256) k_qkv_prep(const PrepParams P) {
+    constexpr int VEC = HD / 64;                 // values per lane and half: 4 (float4) or 2 (float2)
+    constexpr int H2 = HD / 2;
+    constexpr int NBLK = HD / 32;
+    constexpr int REC = HD + 2 * NBLK;
+    constexpr int LPB = 32 / VEC;                // lanes per 32-value quantisation block
+    pdl_wait();
+    pdl_trigger();
+    const int m = blockIdx.x;                    // row of the launch: sequence m / rows, row m % rows
+    const int i = m / P.rows, r = m - i * P.rows;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    float c[VEC], s[VEC];
+    {
+        const float* cp = P.cs + (size_t)m * HD + P.table_off + VEC * lane;
+        const float* sp = P.sn + (size_t)m * HD + P.table_off + VEC * lane;
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) { c[j] = cp[j]; s[j] = sp[j]; }
+    }
+    // L2 scale of one head held as e (first half) and f (second half): bruce.cu:305-307, 1751-1755
+    auto l2_scale = [&](const float (&e)[VEC], const float (&f)[VEC]) {
+        float a = __fmaf_rn(e[0], e[0], __fmul_rn(e[1], e[1]));
+        float b = __fmaf_rn(f[0], f[0], __fmul_rn(f[1], f[1]));
+#pragma unroll
+        for (int j = 2; j < VEC; ++j) { a = __fmaf_rn(e[j], e[j], a); b = __fmaf_rn(f[j], f[j], b); }
+        float ss = __fadd_rn(a, b);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss = __fadd_rn(ss, __shfl_down_sync(0xffffffffu, ss, o));
+        ss = __shfl_sync(0xffffffffu, ss, 0);
+        const float arg = __fadd_rn(__fdiv_rn(ss, (float)HD), __fdiv_rn(1e-6f, (float)HD));
+        return __fmul_rn(__fdiv_rn(1.0f, __fsqrt_rn(arg)), __fdiv_rn(1.0f, __fsqrt_rn((float)HD)));
+    };
+    auto load = [&](const float* p, float (&o)[VEC]) {
+        if constexpr (VEC == 4) {
+            const float4 t = *reinterpret_cast<const float4*>(p);
+            o[0] = t.x; o[1] = t.y; o[2] = t.z; o[3] = t.w;
+        } else {
+            const float2 t = *reinterpret_cast<const float2*>(p);
+            o[0] = t.x; o[1] = t.y;
+        }
+    };
+
+    // ---- q heads: scale, rotate, sqk (bruce.cu:1742-1766) ----------------------------------------------
+    for (int h = warp; h < P.Hq; h += 8) {
+        const size_t base = ((size_t)m * P.Hq + h) * HD + VEC * lane;
+        float e[VEC], f[VEC], s0[VEC], s1[VEC];
+        load(P.q + base, e); load(P.q + base + H2, f);
+        load(P.sqk + (size_t)h * HD + VEC * lane, s0); load(P.sqk + (size_t)h * HD + H2 + VEC * lane, s1);
+        const float norm = l2_scale(e, f);
+        float lo[VEC], hi[VEC];
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) {
+            lo[j] = __fmul_rn(__fmul_rn(__fmaf_rn(e[j], c[j], -__fmul_rn(f[j], s[j])), norm), s0[j]);
+            hi[j] = __fmul_rn(__fmul_rn(__fmaf_rn(e[j], s[j], __fmul_rn(f[j], c[j])), norm), s1[j]);
+        }
+        if (P.q_out_f16) {
+            __half* o = reinterpret_cast<__half*>(P.q_out) + base;
+#pragma unroll
+            for (int j = 0; j < VEC; j += 2) {
+                *reinterpret_cast<__half2*>(o + j) = __floats2half2_rn(lo[j], lo[j + 1]);
+                *reinterpret_cast<__half2*>(o + H2 + j) = __floats2half2_rn(hi[j], hi[j + 1]);
+            }
+        } else {
+            float* o = reinterpret_cast<float*>(P.q_out) + base;
+            if constexpr (VEC == 4) {
+                *reinterpret_cast<float4*>(o) = make_float4(lo[0], lo[1], lo[2], lo[3]);
+                *reinterpret_cast<float4*>(o + H2) = make_float4(hi[0], hi[1], hi[2], hi[3]);
+            } else {
+                *reinterpret_cast<float2*>(o) = make_float2(lo[0], lo[1]);
+                *reinterpret_cast<float2*>(o + H2) = make_float2(hi[0], hi[1]);
+            }
+        }
+    }
+
+    // ---- kv heads: k scale + rotate, then quantise k and raw v (bruce.cu:1768-1812, 1866-1918) ---------
+    if (P.act && !P.act[i]) return;               // idle rows normalise q but never write KV (:1869)
+    const int slot = P.kslot ? P.kslot[i] : 0;
+    const int p = P.pos[i] + r;
+    const bool bad = p < 0 || (P.ring_mask < 0 && p >= P.pstride) || slot < 0 || (P.kslot && slot >= P.n_slots);
+    if (bad) {
+        if (threadIdx.x == 0) atomicOr(P.status, BATTN_DEV_BAD_POSITION);
+        return;
+    }
+    const int pp = p & P.ring_mask;               // ring slot (bruce.cu:1796); identity when the mask is -1
+    for (int h = warp; h < P.Hkv; h += 8) {
+        const size_t base = ((size_t)m * P.Hkv + h) * HD + VEC * lane;
+        float e[VEC], f[VEC], v0[VEC], v1[VEC];
+        load(P.k + base, e); load(P.k + base + H2, f);
+        load(P.v + base, v0); load(P.v + base + H2, v1);
+        const float norm = l2_scale(e, f);
+        float k0[VEC], k1[VEC];
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) {
+            k0[j] = __fmul_rn(__fmaf_rn(e[j], c[j], -__fmul_rn(f[j], s[j])), norm);
+            k1[j] = __fmul_rn(__fmaf_rn(e[j], s[j], __fmul_rn(f[j], c[j])), norm);
+        }
+        const size_t roff = (((size_t)slot * P.Hkv + h) * P.pstride + pp) * (size_t)REC;
+        // one 32-value block = LPB neighbouring lanes; this lane's first-half values sit in block lane / LPB,
+        // its second-half values NBLK/2 blocks later
+        auto quant = [&](uint8_t* rec, int blk, const float (&x)[VEC]) {
+            float amax = fmaxf(fabsf(x[0]), fabsf(x[1]));
+#pragma unroll
+            for (int j = 2; j < VEC; ++j) amax = fmaxf(amax, fabsf(x[j]));
+#pragma unroll
+            for (int o = LPB / 2; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            const float d = __fdiv_rn(amax, 127.f);                        // bruce.cu:1799
+            const float id = d != 0.f ? __fdiv_rn(1.f, d) : 0.f;           // :1800
+            if ((lane & (LPB - 1)) == 0) reinterpret_cast<__half*>(rec)[blk] = __float2half_rn(d);
+            uint32_t pk = 0;
+#pragma unroll
+            for (int j = 0; j < VEC; ++j)                                    // lrintf(x * id), no clamp (:1802)
+                pk |= (uint32_t)(uint8_t)(int8_t)__float2int_rn(__fmul_rn(x[j], id)) << (8 * j);
+            uint8_t* dst = rec + 2 * NBLK + blk * 32 + (lane & (LPB - 1)) * VEC;
+            if constexpr (VEC == 4) *reinterpret_cast<uint32_t*>(dst) = pk;
+            else                    *reinterpret_cast<uint16_t*>(dst) = (uint16_t)pk;
+        };
+        const int blk_lo = lane / LPB;
+        quant(P.kvk + roff, blk_lo, k0);
+        quant(P.kvk + roff, blk_lo + NBLK / 2, k1);
+        quant(P.kvv + roff, blk_lo, v0);
+        quant(P.kvv + roff, blk_lo + NBLK / 2, v1);
+    }
+}
+
+// RoPE tables of a launch's rows: [theta 1e7 | theta 1e4], HD/2 entries each (bruce.cu:1641-1654).  The
+// expressions are the reference's, so the device math library gives the reference's values.
+struct TableParams {
+    float* cs;
+    float* sn;
+    const int* pos;
+    int rows, n_rows;
+};
+
+template <int HD>
+__global__ void k_rope_tables(const TableParams P) {
+    pdl_wait();
+    pdl_trigger();
+    const int m = blockIdx.x;
+    if (m >= P.n_rows) return;
+    const int p = P.pos[m / P.rows] + m % P.rows;
+    const int i = threadIdx.x;                    // HD/2 threads
+    float* c = P.cs + (size_t)m * HD;
+    float* s = P.sn + (size_t)m * HD;
+    const float th = (float)p * powf(10000000.0f, -2.0f * (float)i / (float)HD);
+    c[i] = cosf(th); s[i] = sinf(th);
+    const float th2 = (float)p * powf(10000.0f, -2.0f * (float)i / (float)HD);
+    c[HD / 2 + i] = cosf(th2); s[HD / 2 + i] = sinf(th2);
+}
+
+}  // namespace battn

@@ -97,6 +97,20 @@ class AttnEngine:
             self.h, _ptr(k), _ptr(v), _ptr(kvk), _ptr(kvv), _ptr(pos), _ptr(kslot), _ptr(act),
             n_seq, rows, int(is_swa), self._stream()))
 
+    def qkv_prep(self, q_out, q, k, v, sqk, cs, sn, kvk, kvv, pos, kslot=None, act=None, rows: int = 1,
+                 is_swa: bool = False, theta_sel: int = 1):
+        """The whole k_qkv_prep_fast / k_qkv_prep_fast_ms step (bruce.cu:1732-1812, 1835-1918): L2 scale + RoPE
+        (+ sqk on q) and the quantised append, one launch.  q_out: the geometry's q dtype (fp32 may be q itself)."""
+        n_seq = pos.numel()
+        self._check("battn_qkv_prep", self.lib.battn_qkv_prep(
+            self.h, _ptr(q_out), _ptr(q), _ptr(k), _ptr(v), _ptr(sqk), _ptr(cs), _ptr(sn), int(theta_sel),
+            _ptr(kvk), _ptr(kvv), _ptr(pos), _ptr(kslot), _ptr(act), n_seq, rows, int(is_swa), self._stream()))
+
+    def rope_tables(self, cs, sn, pos, rows: int = 1):
+        """k_rope_tables_rows / _ms (bruce.cu:1641-1654, 1821-1833): cs, sn fp32 [n_seq*rows][head_dim]."""
+        self._check("battn_rope_tables", self.lib.battn_rope_tables(
+            self.h, _ptr(cs), _ptr(sn), _ptr(pos), pos.numel(), rows, self._stream()))
+
     # ---- attention ---------------------------------------------------------------------------------
     def launch_attn_m(self, out, q, kvk, kvv, pos, part, rows: int, is_swa: bool = False):
         """Single-sequence attention: rows == 1 decode, 2..8 speculative verify, > 8 prompt chunk

@@ -106,6 +106,34 @@ int battn_kv_append(battn_handle* h, const float* k, const float* v, uint8_t* kv
                     const int* pos, const int* kslot, const int* act,
                     int n_seq, int rows_per_seq, int is_swa, void* stream);
 
+/* QKV prologue fused with the append, one launch: everything k_qkv_prep (bruce.cu:645-710),
+ * k_qkv_prep_rows (:1656-1725), k_qkv_prep_fast (:1732-1812) and k_qkv_prep_fast_ms (:1835-1918) do.
+ * Per row m = i*rows_per_seq + r (sequence i, row r, position pos[i] + r) and per head:
+ *   scale = l2_scale(sum of squares, head_dim)                               (:305-307)
+ *   NeoX rotate-half RoPE with the row's cos/sin table                       (:1757-1764)
+ *   q additionally times sqk[head][dim]; k is then quantised into kvk, v is quantised RAW into kvv.
+ *   q      fp32 [n_seq*rows_per_seq][n_head][head_dim] (read)
+ *   q_out  same shape in the geometry's q_dtype: fp32 (may be q itself: the reference works in place) or
+ *          fp16 (the operand the attention calls take; must not overlap q)
+ *   k, v   fp32 [n_seq*rows_per_seq][n_kv][head_dim], sqk fp32 [n_head][head_dim]
+ *   cs, sn fp32 [n_seq*rows_per_seq][head_dim]: per row two tables of head_dim/2 entries, theta_sel 1 uses
+ *          the first, 2 the second (the reference's 256-float rows, :1739-1740); battn_rope_tables fills them
+ *   kvk, kvv, pos, kslot, act, is_swa: exactly as battn_kv_append; idle sequences (act[i] == 0) still get
+ *          their q prepared but write no KV (:1869)
+ * Every fp32 step is performed in the order of the reference kernel as compiled by nvcc (fused multiply-adds
+ * included): q_out (fp32) and the K/V bytes are bit-identical to the reference's. */
+int battn_qkv_prep(battn_handle* h, void* q_out, const float* q, const float* k, const float* v,
+                   const float* sqk, const float* cs, const float* sn, int theta_sel,
+                   uint8_t* kvk, uint8_t* kvv, const int* pos, const int* kslot, const int* act,
+                   int n_seq, int rows_per_seq, int is_swa, void* stream);
+
+/* RoPE tables for the rows of one launch: k_rope_tables (bruce.cu:328-336), k_rope_tables_rows (:1641-1654)
+ * and k_rope_tables_rows_ms (:1821-1833).  Row m = i*rows_per_seq + r gets, for position p = pos[i] + r and
+ * j < head_dim/2: cs[m][j] = cosf(p * powf(1e7, -2j/head_dim)), cs[m][head_dim/2 + j] the same with base 1e4,
+ * sn likewise with sinf.  cs, sn: fp32 [n_seq*rows_per_seq][head_dim]. */
+int battn_rope_tables(battn_handle* h, float* cs, float* sn, const int* pos, int n_seq, int rows_per_seq,
+                      void* stream);
+
 /* Decode attention, one query row per sequence, normalised output:
  * launch_attn_m(rows = 1) + k_attn_combine_fast (bruce.cu:3942-3963, 928-990, call :7958-7969)
  * when kslot == NULL, launch_attn_ms (bruce.cu:4158-4177, call :7720) when kslot != NULL.

@@ -61,6 +61,29 @@ static inline void kv_append_ms(const float* k, const float* v, uint8_t* kvk_lay
     BATTN_CK(battn_kv_append(g_battn, k, v, kvk_layer, kvv_layer, pos, kslot, act, rows, 1, is_swa, st));
 }
 
+/* k_qkv_prep / k_qkv_prep_rows / k_qkv_prep_fast as launched at bruce.cu:7671-7675, :7941: the whole prologue
+ * (L2 scale, RoPE, sqk) and the append for rows of ONE sequence; q is prepared in place like the reference's */
+static inline void qkv_prep_rows(float* q, const float* k, const float* v, const float* sqk, uint8_t* kvk,
+                                 uint8_t* kvv, const int* pos, int rows, int is_swa, int theta_sel,
+                                 const float* cs, const float* sn, cudaStream_t st) {
+    BATTN_CK(battn_qkv_prep(g_battn, q, q, k, v, sqk, cs, sn, theta_sel, kvk, kvv, pos, nullptr, nullptr, 1, rows,
+                            is_swa, st));
+}
+/* k_qkv_prep_fast_ms as launched at bruce.cu:7667: one row per slot, layer base pointers */
+static inline void qkv_prep_ms(float* q, const float* k, const float* v, const float* sqk, uint8_t* kvk_layer,
+                               uint8_t* kvv_layer, const int* pos, const int* kslot, const int* act, int rows,
+                               int is_swa, int theta_sel, const float* cs, const float* sn, cudaStream_t st) {
+    BATTN_CK(battn_qkv_prep(g_battn, q, q, k, v, sqk, cs, sn, theta_sel, kvk_layer, kvv_layer, pos, kslot, act, rows,
+                            1, is_swa, st));
+}
+/* k_rope_tables_rows (bruce.cu:7625) and k_rope_tables_rows_ms (:7623) */
+static inline void rope_tables_rows(float* cs, float* sn, const int* pos, int rows, cudaStream_t st) {
+    BATTN_CK(battn_rope_tables(g_battn, cs, sn, pos, 1, rows, st));
+}
+static inline void rope_tables_rows_ms(float* cs, float* sn, const int* row_pos, int rows, cudaStream_t st) {
+    BATTN_CK(battn_rope_tables(g_battn, cs, sn, row_pos, rows, 1, st));
+}
+
 /* launch_attn_m (bruce.cu:3942; calls :7729, :7732, :7958) with the merge folded in */
 static inline void launch_attn_m(float* out, const float* q, const uint8_t* kvk, const uint8_t* kvv,
                                  const int* pos, float* part, int rows, int /*ns*/, int is_swa, cudaStream_t st) {

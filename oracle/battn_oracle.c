@@ -5,11 +5,14 @@
  * (and the timed CPU baseline of the benchmark).  It is never linked into, loaded by, or called
  * from the product library; the product has no CPU path.
  *
- * PARITY STATUS: the reference ships no golden vectors, known-answer tests or fixtures for its
- * attention path or its KV bytes, and its kernels cannot execute without a GPU, so this
- * restatement is pinned by (a) hand-derived known-answer cases, (b) an independent numpy
- * restatement, (c) committed fixtures generated from it, and (d) where a GPU box is available,
- * the reference's own kernels compiled from their sources (see ref_harness.cu beside this file).
+ * PARITY STATUS: the reference ships no golden vectors, known-answer tests or fixtures for this path, and
+ * its kernels cannot execute without a GPU, so the pins were made here: (a) golden vectors produced by the
+ * reference's own kernels (k_rope_tables_rows, k_qkv_prep_fast, k_qkv_prep_fast_ms) on a B200 through the
+ * harness in ref_harness.cu, committed as tests/golden/qkv_prep_ref.npz with the script that made them --
+ * oracle_qkv_prep and the quantiser reproduce them bit for bit; (b) hand-derived known-answer cases, an
+ * independent numpy restatement and fixtures generated from this file for the attention functions, whose
+ * agreement with the reference's exact kernels (2e-5) is checked on a GPU box by
+ * tests/test_gpu_reference_kernels.py.
  *
  * Each function cites the reference lines (engine/src/bruce.cu) it follows.
  */
@@ -135,6 +138,91 @@ int oracle_kv_append(const oracle_geom* g, const float* k, const float* v, uint8
             }
         }
     }
+    return 0;
+}
+
+/* ---- QKV prologue + append (k_qkv_prep_fast, bruce.cu:1732-1812; multi-slot k_qkv_prep_fast_ms,
+ *      :1835-1918): per head an L2 scale (l2_scale, :305-307), NeoX rotate-half RoPE with per-row
+ *      cos/sin tables, the per-head sqk scale on q; k gets scale + RoPE and is quantised, v is quantised raw.
+ * The fp32 operation order below is the one nvcc generates for the reference source (fused
+ * multiply-adds included); it reproduces the reference kernel's q output and K/V records bit for bit
+ * (tests/golden/qkv_prep_ref.npz holds outputs of the reference kernel itself).
+ *   lane l of the warp that owns a head holds VEC = HD/64 consecutive values of each half:
+ *     e[0..VEC) = x[VEC*l ..], f[0..VEC) = x[HD/2 + VEC*l ..]
+ *     partial(e) = fma(e[VEC-1], e[VEC-1], ... fma(e[2], e[2], fma(e[0], e[0], rn(e[1]*e[1]))))
+ *     ss_lane = partial(e) + partial(f);  ss = shfl_down tree over 32 lanes (16, 8, 4, 2, 1), lane 0
+ *   norm = (1 / sqrt(ss/HD + 1e-6f/HD)) * (1 / sqrt(HD))                         (each step rounded)
+ *   lo = fma(x0, c, -rn(x1*s)),  hi = fma(x0, s, rn(x1*c));  then * norm, then (q only) * sqk
+ * Tables: row m = i*rows + r uses cs/sn + m*HD + (theta_sel == 2 ? HD/2 : 0), HD/2 entries. */
+static float prep_sumsq(const float* x, int HD) {
+    const int VEC = HD / 64;
+    float lane[32];
+    for (int l = 0; l < 32; ++l) {
+        float part[2];
+        for (int half = 0; half < 2; ++half) {
+            const float* e = x + half * (HD / 2) + VEC * l;
+            float t = fmaf(e[0], e[0], e[1] * e[1]);
+            for (int j = 2; j < VEC; ++j) t = fmaf(e[j], e[j], t);
+            part[half] = t;
+        }
+        lane[l] = part[0] + part[1];
+    }
+    for (int o = 16; o > 0; o >>= 1)
+        for (int l = 0; l + o < 32; ++l) lane[l] = lane[l] + lane[l + o];   /* lanes >= 32-o keep their value */
+    return lane[0];
+}
+
+static float prep_l2_scale(float ss, int n) {
+    const float a = ss / (float)n + 1e-6f / (float)n;
+    return (1.0f / sqrtf(a)) * (1.0f / sqrtf((float)n));
+}
+
+static void prep_rotate(const float* x, const float* c, const float* s, float norm, const float* extra,
+                        float* out, int HD) {
+    const int H2 = HD / 2;
+    for (int i = 0; i < H2; ++i) {
+        const float x0 = x[i], x1 = x[i + H2];
+        float lo = fmaf(x0, c[i], -(x1 * s[i]));
+        float hi = fmaf(x0, s[i], x1 * c[i]);
+        lo = lo * norm; hi = hi * norm;
+        if (extra) { lo = lo * extra[i]; hi = hi * extra[i + H2]; }
+        out[i] = lo; out[i + H2] = hi;
+    }
+}
+
+int oracle_qkv_prep(const oracle_geom* g, float* q, const float* k, const float* v, const float* sqk,
+                    const float* cs, const float* sn, int theta_sel, uint8_t* kvk, uint8_t* kvv,
+                    const int* pos, const int* kslot, const int* act, int n_seq, int rows, int is_swa) {
+    const int HD = g->head_dim;
+    if (!kslot && n_seq != 1) return 1;
+    float* tmp = (float*)malloc(sizeof(float) * (size_t)HD);
+    if (!tmp) return 3;
+    for (int i = 0; i < n_seq; ++i) {
+        const int slot = kslot ? kslot[i] : 0;
+        for (int r = 0; r < rows; ++r) {
+            const size_t m = (size_t)i * rows + r;
+            const float* c = cs + m * HD + (theta_sel == 2 ? HD / 2 : 0);
+            const float* s = sn + m * HD + (theta_sel == 2 ? HD / 2 : 0);
+            for (int h = 0; h < g->n_head; ++h) {
+                float* qh = q + (m * g->n_head + h) * HD;
+                const float norm = prep_l2_scale(prep_sumsq(qh, HD), HD);
+                prep_rotate(qh, c, s, norm, sqk + (size_t)h * HD, tmp, HD);
+                memcpy(qh, tmp, sizeof(float) * (size_t)HD);
+            }
+            if (act && !act[i]) continue;                      /* idle rows normalise q but never write KV (:1869) */
+            const int p = pos[i] + r;
+            if (p < 0 || (!is_swa && p >= g->slot_ctx)) { free(tmp); return 2; }
+            for (int h = 0; h < g->n_kv; ++h) {
+                const size_t src = (m * g->n_kv + h) * HD;
+                const size_t off = rec_offset(g, is_swa, slot, h, p);
+                const float norm = prep_l2_scale(prep_sumsq(k + src, HD), HD);
+                prep_rotate(k + src, c, s, norm, NULL, tmp, HD);
+                oracle_quant_record(g, tmp, kvk + off);
+                oracle_quant_record(g, v + src, kvv + off);
+            }
+        }
+    }
+    free(tmp);
     return 0;
 }
 

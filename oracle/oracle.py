@@ -84,6 +84,9 @@ def lib():
         L.oracle_quant_block32.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
         L.oracle_kv_append.restype = C.c_int
         L.oracle_kv_append.argtypes = [C.POINTER(_Geom)] + [C.c_void_p] * 7 + [C.c_int] * 3
+        L.oracle_qkv_prep.restype = C.c_int
+        L.oracle_qkv_prep.argtypes = ([C.POINTER(_Geom)] + [C.c_void_p] * 6 + [C.c_int] + [C.c_void_p] * 5 +
+                                      [C.c_int] * 3)
         L.oracle_attend.restype = C.c_int
         L.oracle_attend.argtypes = [C.POINTER(_Geom)] + [C.c_void_p] * 8 + [C.c_int] * 6
         L.oracle_attend_f32.restype = C.c_int
@@ -122,6 +125,42 @@ def kv_append(g: Geom, k, v, kvk, kvv, pos, kslot=None, act=None, rows=1, is_swa
                                 _p(act), n_seq, rows, int(is_swa))
     if rc:
         raise ValueError(f"oracle_kv_append failed: {rc}")
+
+
+def qkv_prep(g: Geom, q, k, v, sqk, cs, sn, kvk, kvv, pos, kslot=None, act=None, rows=1, is_swa=False,
+             theta_sel=1):
+    """The reference's QKV prologue + append (bruce.cu:1732-1812, 1835-1918).  q: float32
+    [n_seq][rows][n_head][head_dim], k, v: [n_seq][rows][n_kv][head_dim], sqk: [n_head][head_dim],
+    cs, sn: [n_seq*rows][head_dim] (two tables of head_dim/2).  Returns the prepared q; writes the caches."""
+    q = np.array(q, dtype=np.float32, order="C", copy=True)
+    k = np.ascontiguousarray(k, dtype=np.float32)
+    v = np.ascontiguousarray(v, dtype=np.float32)
+    sqk = np.ascontiguousarray(sqk, dtype=np.float32)
+    cs = np.ascontiguousarray(cs, dtype=np.float32)
+    sn = np.ascontiguousarray(sn, dtype=np.float32)
+    pos, kslot, act = _ints(pos), _ints(kslot), _ints(act)
+    n_seq = pos.size
+    assert cs.size == n_seq * rows * g.head_dim and sn.size == cs.size
+    gc = g.c()
+    rc = lib().oracle_qkv_prep(C.byref(gc), _p(q), _p(k), _p(v), _p(sqk), _p(cs), _p(sn), int(theta_sel),
+                               _p(kvk), _p(kvv), _p(pos), _p(kslot), _p(act), n_seq, rows, int(is_swa))
+    if rc:
+        raise ValueError(f"oracle_qkv_prep failed: {rc}")
+    return q
+
+
+def rope_tables(head_dim: int, positions) -> tuple:
+    """cos/sin tables in the reference's layout (bruce.cu:1641-1654): per row [theta 1e7 | theta 1e4], head_dim/2
+    entries each, computed in double and rounded once (the reference evaluates powf/cosf/sinf in fp32 on the
+    device, so its tables differ from these in the last bits and, at large positions, by the fp32 error of the
+    angle itself; the prologue takes the tables as an input for that reason)."""
+    p = np.asarray(positions, dtype=np.float64).reshape(-1, 1)
+    i = np.arange(head_dim // 2, dtype=np.float64)
+    th1 = p * (1e7 ** (-2.0 * i / head_dim))
+    th2 = p * (1e4 ** (-2.0 * i / head_dim))
+    cs = np.concatenate([np.cos(th1), np.cos(th2)], axis=1).astype(np.float32)
+    sn = np.concatenate([np.sin(th1), np.sin(th2)], axis=1).astype(np.float32)
+    return cs, sn
 
 
 def attend(g: Geom, q, kvk, kvv, pos, kslot=None, act=None, rows=1, is_swa=False,
@@ -228,3 +267,38 @@ def np_attend(g: Geom, q, kvk, kvv, pos, kslot=None, rows=1, is_swa=False) -> np
                 w = np.exp(sc - sc.max())
                 out[i, r, h] = (w / w.sum()) @ vs
     return out.astype(np.float32)
+
+
+def _np_fma(a, b, c):
+    """fp32 fused multiply-add through float64 (the product of two floats is exact in double)."""
+    return (a.astype(np.float64) * b.astype(np.float64) + c.astype(np.float64)).astype(np.float32)
+
+
+def np_qkv_prologue(x: np.ndarray, c: np.ndarray, s: np.ndarray, extra=None) -> np.ndarray:
+    """Independent numpy restatement of the prologue of one tensor of heads: x [..., HD] float32, c, s
+    broadcastable [..., HD/2].  Same fp32 operation order as oracle_qkv_prep (see battn_oracle.c)."""
+    f32 = np.float32
+    x = np.asarray(x, dtype=f32)
+    HD = x.shape[-1]
+    H2, VEC = HD // 2, HD // 64
+    def partial(y):                                   # y [..., 32, VEC]
+        t = _np_fma(y[..., 0], y[..., 0], (y[..., 1] * y[..., 1]).astype(f32))
+        for j in range(2, VEC):
+            t = _np_fma(y[..., j], y[..., j], t)
+        return t
+    lane = (partial(x[..., :H2].reshape(x.shape[:-1] + (32, VEC))) +
+            partial(x[..., H2:].reshape(x.shape[:-1] + (32, VEC)))).astype(f32)
+    for o in (16, 8, 4, 2, 1):
+        nxt = lane.copy()
+        nxt[..., :32 - o] = (lane[..., :32 - o] + lane[..., o:]).astype(f32)
+        lane = nxt
+    ss = lane[..., 0]
+    a = ((ss / f32(HD)).astype(f32) + f32(f32(1e-6) / f32(HD))).astype(f32)
+    norm = ((f32(1.0) / np.sqrt(a).astype(f32)).astype(f32) * f32(f32(1.0) / np.sqrt(f32(HD)))).astype(f32)[..., None]
+    x0, x1 = x[..., :H2], x[..., H2:]
+    lo = (_np_fma(x0, c, -(x1 * s).astype(f32)) * norm).astype(f32)
+    hi = (_np_fma(x0, s, (x1 * c).astype(f32)) * norm).astype(f32)
+    if extra is not None:
+        lo = (lo * extra[..., :H2]).astype(f32)
+        hi = (hi * extra[..., H2:]).astype(f32)
+    return np.concatenate([lo, hi], axis=-1)

@@ -36,6 +36,32 @@ int ref_kv_append(float* q, const float* k, const float* v, const float* sqk, ui
     return ref_sync_status();
 }
 
+// The reference's multi-slot append, k_qkv_prep_fast_ms (bruce.cu:1835): one row per slot, per-row position,
+// partition and "writes KV" flag; kvk/kvv are layer bases.
+int ref_kv_append_ms(float* q, const float* k, const float* v, const float* sqk, uint8_t* kvk, uint8_t* kvv,
+                     const int* d_pos, const int* d_slot, const int* d_act, int rows, int is_swa, int theta_sel,
+                     int nctx, const float* cs, const float* sn) {
+    ref_set_nctx(nctx);
+    k_qkv_prep_fast_ms<<<rows, 256>>>(q, k, v, sqk, kvk, kvv, d_pos, d_slot, d_act, is_swa, theta_sel, cs, sn);
+    return ref_sync_status();
+}
+
+// The same single-sequence kernel as ref_kv_append with the table selector exposed.
+int ref_kv_append_theta(float* q, const float* k, const float* v, const float* sqk, uint8_t* kvk, uint8_t* kvv,
+                        const int* d_pos, int rows, int is_swa, int theta_sel, int nctx, const float* cs,
+                        const float* sn) {
+    ref_set_nctx(nctx);
+    k_qkv_prep_fast<<<rows, 256>>>(q, k, v, sqk, kvk, kvv, d_pos, is_swa, theta_sel, cs, sn);
+    return ref_sync_status();
+}
+
+// The reference's RoPE table kernels: rows of one sequence (bruce.cu:1641) / one row per slot (:1821).
+int ref_rope_tables(float* cs, float* sn, const int* d_pos, int rows, int per_row_pos) {
+    if (per_row_pos) k_rope_tables_rows_ms<<<rows, 128>>>(cs, sn, d_pos, rows);
+    else             k_rope_tables_rows<<<rows, 128>>>(cs, sn, d_pos, rows);
+    return ref_sync_status();
+}
+
 // The reference's exact fp32 attention: k_attn_rows (bruce.cu:1921) + k_attn_combine_rows (:1999).
 // part must hold rows * N_KV * ns * 4 * (HD + 2) floats.
 int ref_attn_exact(float* out, const float* q, const uint8_t* kvk, const uint8_t* kvv, const int* d_pos,
