@@ -365,8 +365,9 @@ int battn_qkv_prep(battn_handle* h, void* q_out, const float* q, const float* k,
     P.n_slots = g.n_slots; P.status = h->d_status;
     cudaStream_t st = (cudaStream_t)stream;
     cudaError_t e;
-    if (g.HD == 128) e = launch_pdl(k_qkv_prep<128>, dim3(n_seq * rows_per_seq), dim3(256), 0, st, P);
-    else             e = launch_pdl(k_qkv_prep<256>, dim3(n_seq * rows_per_seq), dim3(256), 0, st, P);
+    const dim3 grid(n_seq * rows_per_seq, (g.Hq + g.Hkv + 7) / 8);
+    if (g.HD == 128) e = launch_pdl(k_qkv_prep<128>, grid, dim3(256), 0, st, P);
+    else             e = launch_pdl(k_qkv_prep<256>, grid, dim3(256), 0, st, P);
     h->launches += 1;
     if (e == cudaSuccess) e = cudaGetLastError();
     return e == cudaSuccess ? BATTN_OK : cuda_fail(h, e);

@@ -4,8 +4,8 @@
 // (engine/src/bruce.cu:645-710, 1656-1725, 1732-1812, 1835-1918) and the table kernels
 // k_rope_tables / k_rope_tables_rows / k_rope_tables_rows_ms (:328-336, 1641-1654, 1821-1833).
 //
-// HBM-bound element-wise work: one CTA per row, one warp per head (the whole head lives in the warp's
-// registers, 16-byte loads and stores), no shared memory, no block barrier.  Every fp32 step is written
+// HBM-bound element-wise work: one warp per (row, head) with the whole head in the warp's registers
+// (16-byte loads and stores), eight heads per CTA, no shared memory, no block barrier.  Every fp32 step is written
 // with explicit round-to-nearest intrinsics in the order nvcc generates for the reference source (which
 // fuses x0*c - x1*s into fma(x0, c, -(x1*s)) and the squares into a chain of fma), so q and the K/V
 // records are bit-identical to the reference kernel's and do not depend on this file's compiler flags.
@@ -46,7 +46,9 @@ __global__ void __launch_bounds__(256) k_qkv_prep(const PrepParams P) {
     pdl_trigger();
     const int m = blockIdx.x;                    // row of the launch: sequence m / rows, row m % rows
     const int i = m / P.rows, r = m - i * P.rows;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int lane = threadIdx.x & 31;
+    const int hw = blockIdx.y * 8 + (threadIdx.x >> 5);   // q heads first, then kv heads
+    if (hw >= P.Hq + P.Hkv) return;
 
     float c[VEC], s[VEC];
     {
@@ -79,7 +81,8 @@ __global__ void __launch_bounds__(256) k_qkv_prep(const PrepParams P) {
     };
 
     // ---- q heads: scale, rotate, sqk (bruce.cu:1742-1766) ----------------------------------------------
-    for (int h = warp; h < P.Hq; h += 8) {
+    if (hw < P.Hq) {
+        const int h = hw;
         const size_t base = ((size_t)m * P.Hq + h) * HD + VEC * lane;
         float e[VEC], f[VEC], s0[VEC], s1[VEC];
         load(P.q + base, e); load(P.q + base + H2, f);
@@ -108,6 +111,7 @@ __global__ void __launch_bounds__(256) k_qkv_prep(const PrepParams P) {
                 *reinterpret_cast<float2*>(o + H2) = make_float2(hi[0], hi[1]);
             }
         }
+        return;
     }
 
     // ---- kv heads: k scale + rotate, then quantise k and raw v (bruce.cu:1768-1812, 1866-1918) ---------
@@ -116,11 +120,12 @@ __global__ void __launch_bounds__(256) k_qkv_prep(const PrepParams P) {
     const int p = P.pos[i] + r;
     const bool bad = p < 0 || (P.ring_mask < 0 && p >= P.pstride) || slot < 0 || (P.kslot && slot >= P.n_slots);
     if (bad) {
-        if (threadIdx.x == 0) atomicOr(P.status, BATTN_DEV_BAD_POSITION);
+        if (lane == 0) atomicOr(P.status, BATTN_DEV_BAD_POSITION);
         return;
     }
     const int pp = p & P.ring_mask;               // ring slot (bruce.cu:1796); identity when the mask is -1
-    for (int h = warp; h < P.Hkv; h += 8) {
+    {
+        const int h = hw - P.Hq;
         const size_t base = ((size_t)m * P.Hkv + h) * HD + VEC * lane;
         float e[VEC], f[VEC], v0[VEC], v1[VEC];
         load(P.k + base, e); load(P.k + base + H2, f);

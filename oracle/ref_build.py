@@ -16,7 +16,9 @@ import sys
 import tempfile
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF_ROOT = os.environ.get("BRUCE_REFERENCE_ROOT", "/root/reference")
+# the reference tree: BRUCE_REFERENCE_ROOT, else a checkout named "reference" beside this repository
+REF_ROOT = os.environ.get("BRUCE_REFERENCE_ROOT",
+                          os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference"))
 OUT = os.path.join(HERE, "_ref", "libbruce_ref.so")
 HARNESS = os.path.join(HERE, "ref_harness.cu")
 

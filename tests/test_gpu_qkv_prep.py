@@ -185,3 +185,41 @@ def test_bit_exact_against_the_reference_kernels(ref):
         assert torch.equal(kvk, kvk_r) and torch.equal(kvv, kvv_r), "cache bytes differ from the reference kernel's"
         assert kvk.any()
     assert eng.device_status() == 0
+
+
+def test_bad_requests_are_refused_or_reported_not_executed():
+    from bruce_engine_b200 import capi
+    from bruce_engine_b200.engine import AttnEngine
+    g = _geom("B", slot_ctx=64, window=32, q_dtype=0)
+    eng = AttnEngine(g)
+    HD = g.head_dim
+    rows = 2
+    q = torch.randn((1, rows, g.n_head, HD), device="cuda")
+    k = torch.randn((1, rows, g.n_kv, HD), device="cuda")
+    sqk = torch.ones((g.n_head, HD), device="cuda")
+    cs, sn = torch.ones((rows, HD), device="cuda"), torch.zeros((rows, HD), device="cuda")
+    kvk, kvv = eng.alloc_kv_layer(False, fill=0x11)
+    pos = dev_i32([0], "cuda")
+    with pytest.raises(capi.BattnError) as ei:                       # only tables 1 and 2 exist
+        eng.qkv_prep(q, q, k, k, sqk, cs, sn, kvk, kvv, pos, rows=rows, theta_sel=3)
+    assert ei.value.code == capi.ERR_ARG
+    with pytest.raises(capi.BattnError) as ei:                       # 16-byte alignment of the fp32 operands
+        eng.qkv_prep(q, q, k, k, sqk, cs.view(-1)[1:], sn, kvk, kvv, pos, rows=rows)
+    assert ei.value.code == capi.ERR_ARG
+    kvk_w, kvv_w = eng.alloc_kv_layer(True, fill=0)
+    big = 2 * g.window + 1
+    qb = torch.zeros((1, big, g.n_head, HD), device="cuda")
+    kb = torch.zeros((1, big, g.n_kv, HD), device="cuda")
+    tb = torch.zeros((big, HD), device="cuda")
+    with pytest.raises(capi.BattnError) as ei:                       # one call must not wrap the ring onto itself
+        eng.qkv_prep(qb, qb, kb, kb, sqk, tb, tb, kvk_w, kvv_w, pos, rows=big, is_swa=True)
+    assert ei.value.code == capi.ERR_CAPACITY
+    # a position past the end of the slot: q is still prepared, nothing is written, the status word says why
+    before = q.clone()
+    eng.qkv_prep(q, q, k, k, sqk, cs, sn, kvk, kvv, dev_i32([63], "cuda"), rows=rows)
+    torch.cuda.synchronize()
+    assert eng.device_status() & capi.DEV_BAD_POSITION
+    assert not torch.equal(q, before)
+    rec = kvk.view(g.n_kv, g.slot_ctx, HD + HD // 16)
+    assert (rec[:, :63] == 0x11).all() and not (rec[:, 63] == 0x11).all()       # row 0 (position 63) stored, row 1 refused
+    assert eng.device_status() == 0
