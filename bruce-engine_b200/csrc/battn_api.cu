@@ -90,6 +90,21 @@ inline FdWs fd_workspace(const battn_handle* h, int n_seq, int rows) {
 
 inline int exact_default_splits(int rows) { return rows > 64 ? 2 : (rows > 8 ? 8 : 32); }
 
+// Key splits of the prompt kernel: its grid is (M tiles) x (kv heads), which leaves SMs idle for short chunks and
+// for head_dim 256 (64 CTAs for a 512-row chunk); each (M tile, kv head) is then shared by several CTAs that take
+// contiguous shares of the key tiles and leave split records for the merge kernel.  Positions are device-resident,
+// so the choice depends on the chunk shape only.
+inline int prefill_splits(const battn_handle* h, int rows, int is_swa) {
+    const Geom& g = h->g;
+    if (g.HD != 256) return 1;
+    const int ctas = ((rows + 128 / g.G - 1) / (128 / g.G)) * g.Hkv;
+    int s = h->num_sms / ctas;
+    // a share should keep at least 16 key tiles of 64, or the merge costs more than the split saves; a
+    // sliding-window layer never has more than window/64 + 1 tiles per M tile
+    if (is_swa && s > g.W / (64 * 16)) s = g.W / (64 * 16);
+    return s < 1 ? 1 : (s > 8 ? 8 : s);
+}
+
 inline size_t exact_workspace(const battn_handle* h, int n_seq, int rows, int nsplit) {
     const Geom& g = h->g;
     return (size_t)n_seq * rows * g.Hq * nsplit * (g.HD + 2) * sizeof(float);
@@ -219,7 +234,7 @@ int launch_flash(battn_handle* h, void* out, float* rec_out, const void* q, cons
 
 // prompt chunk on the tcgen05 kernel: one CTA per (128-row M tile, kv head), normalised output
 int launch_prefill(battn_handle* h, void* out, const void* q, const uint8_t* kvk, const uint8_t* kvv, const int* pos,
-                   int rows, int is_swa, cudaStream_t st) {
+                   void* ws, int rows, int is_swa, cudaStream_t st) {
     const Geom& g = h->g;
     if (128 % g.G) return BATTN_ERR_ARG;
     pf::Params P;
@@ -229,14 +244,26 @@ int launch_prefill(battn_handle* h, void* out, const void* q, const uint8_t* kvk
     P.slot_ctx = g.slot_ctx; P.is_swa = is_swa; P.q_f16 = g.q_f16; P.out_f16 = g.out_f16;
     P.scale_log2 = g.scale * LOG2E; P.status = h->d_status;
     const int MR = 128 / g.G;
-    const dim3 grid((rows + MR - 1) / MR, g.Hkv);
+    P.nsplit = prefill_splits(h, rows, is_swa);
+    P.recs = P.nsplit > 1 ? reinterpret_cast<float*>(ws) : nullptr;
+    const dim3 grid((rows + MR - 1) / MR, g.Hkv, P.nsplit);
     {
         ProfScope prof(h, st);
         if (g.HD == 128) pf128::k_prefill_hd128<<<grid, pf128::NTHREADS, pf128::TOTAL, st>>>(P);
         else             pf::k_prefill<256, 64><<<grid, pf::NTHREADS, pf::Cfg<256, 64>::TOTAL, st>>>(P);
     }
     h->launches += 1;
-    const cudaError_t e = cudaGetLastError();
+    cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess && P.nsplit > 1) {
+        MergeParams M{};
+        M.mode = MERGE_GATHERED; M.part = P.recs; M.out = out; M.rec_out = nullptr;
+        M.n_rows = rows; M.rows = 1; M.Hq = g.Hq; M.Hkv = g.Hkv; M.G = g.G;
+        M.count = P.nsplit; M.log2_domain = 1; M.out_f16 = g.out_f16; M.status = h->d_status;
+        if (g.HD == 128) k_merge<128><<<rows * g.Hq, MERGE_THREADS, 0, st>>>(M);
+        else             k_merge<256><<<rows * g.Hq, MERGE_THREADS, 0, st>>>(M);
+        h->launches += 1;
+        e = cudaGetLastError();
+    }
     return e == cudaSuccess ? BATTN_OK : cuda_fail(h, e);
 }
 
@@ -310,6 +337,10 @@ int battn_workspace_bytes(const battn_handle* h, int n_seq, int rows_per_seq, si
     if (!h || !out_bytes || n_seq < 1 || rows_per_seq < 1) return BATTN_ERR_ARG;
     if (n_seq > MAX_SEQ || rows_per_seq > MAX_PREFILL) return BATTN_ERR_CAPACITY;
     size_t need = exact_workspace(h, n_seq, rows_per_seq, exact_default_splits(rows_per_seq));
+    if (rows_per_seq * h->g.G > 32 && n_seq == 1) {
+        const size_t f = exact_workspace(h, 1, rows_per_seq, prefill_splits(h, rows_per_seq, 0));    // same record size
+        if (f > need) need = f;
+    }
     if (rows_per_seq * h->g.G <= 32) {
         const size_t f = fd_workspace(h, n_seq, rows_per_seq).total;
         if (f > need) need = f;
@@ -433,7 +464,7 @@ int battn_prefill(battn_handle* h, void* out, const void* q, const uint8_t* kvk,
     if (h->g.W < 64) return BATTN_ERR_ARG;               // key tiles of 64 / 128 must not wrap the ring
     if (rows * h->g.G <= 32)
         return launch_flash(h, out, nullptr, q, kvk, kvv, pos, nullptr, nullptr, ws, 1, rows, is_swa, (cudaStream_t)stream);
-    return launch_prefill(h, out, q, kvk, kvv, pos, rows, is_swa, (cudaStream_t)stream);
+    return launch_prefill(h, out, q, kvk, kvv, pos, ws, rows, is_swa, (cudaStream_t)stream);
 }
 
 int battn_attend_exact(battn_handle* h, void* out, const void* q, const uint8_t* kvk, const uint8_t* kvv,

@@ -54,6 +54,10 @@ struct Params {
     int W, pstride, ring_mask, slot_ctx, is_swa, q_f16, out_f16;
     float scale_log2;
     int* status;
+    // key split: gridDim.z CTAs share one (M tile, kv head), each takes a contiguous share of the key tiles and
+    // writes split records [split][row][head][HD+2] = (unnormalised o, m in log2 units, l) for the merge kernel
+    int nsplit;
+    float* recs;
 };
 
 template <int HD, int BN>
@@ -248,8 +252,20 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill(const Params P) {
     const int lo_cta = P.is_swa ? max(0, p_first + 1 - P.W) : 0;       // bruce.cu:2801
     const int hi_cta = p_last + 1;
     const int full_lo = P.is_swa ? max(0, p_last + 1 - P.W) : 0;
-    const int tile_first = lo_cta / BN;
-    const int n_tiles = (hi_cta + BN - 1) / BN - tile_first;
+    const int tile_lo = lo_cta / BN;
+    const int n_all = (hi_cta + BN - 1) / BN - tile_lo;                // key tiles of this M tile
+    const int per_split = (n_all + P.nsplit - 1) / P.nsplit;
+    const int tile_first = tile_lo + (int)blockIdx.z * per_split;      // this CTA's share
+    const int n_tiles = max(0, min(per_split, n_all - (int)blockIdx.z * per_split));
+    if (n_tiles == 0) {
+        // more splits than key tiles (shallow context): an empty record, so the merge ignores this share
+        if (tid < 128 && tid / G < rows_eff) {
+            float* rec = P.recs + ((((size_t)blockIdx.z * P.rows) + rbase + tid / G) * P.Hq + kvh * G + tid % G) * (size_t)(HD + 2);
+            for (int i = 0; i < HD; ++i) rec[i] = 0.f;
+            rec[HD] = NEG_BIG; rec[HD + 1] = 0.f;
+        }
+        return;
+    }
 
     // ---- set-up: barriers, tensor memory, the Q operand, the block of ones ---------------------------
     if (tid == 0) {
@@ -342,12 +358,16 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill(const Params P) {
 
     if (warp >= (NSOFT + 2 * NDEQ) / 32) regs_shrink<REGS_CTL>();          // the whole last warpgroup
     if (warp == (NSOFT + 2 * NDEQ) / 32) {
-        // ======================= control thread: every MMA =============================================
+        // ======================= S = Q K^T for every tile ==============================================
+        // A thread of its own: one thread that polls three barriers and issues every MMA of a tile is itself
+        // the critical path.  S of tile j+1 refills the buffer whose P the P.V MMA of tile j-1 consumed.
         if (lane == 0) {
-            const uint32_t idS = umma_idesc(128, BN), idO = umma_idesc(128, HD), idL = umma_idesc(128, 16);
-            const uint32_t qa = smem_u32(Qsm), ka = smem_u32(Ksm), va = smem_u32(Vsm);
-            const uint32_t oa = smem_u32(ONES);
-            auto issue_S = [&](int j) {
+            const uint32_t idS = umma_idesc(128, BN);
+            const uint32_t qa = smem_u32(Qsm), ka = smem_u32(Ksm);
+            for (int j = 0; j < n_tiles; ++j) {
+                wait(B_KF0 + (j & 1), (j >> 1) & 1);
+                if (j >= 2) wait(B_PV0 + (j & 1), ((j - 2) >> 1) & 1);
+                tc_fence_after();
                 const uint32_t d = tmem + ((j & 1) ? C::T_S1 : C::T_S0);
                 const uint32_t kb = ka + (j % C::KV_BUFS) * C::K_BYTES;
 #pragma unroll
@@ -361,16 +381,14 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill(const Params P) {
                     }
                 }
                 umma_commit(&bars[B_S0 + (j & 1)]);
-            };
-            wait(B_KF0, 0);
-            tc_fence_after();
-            issue_S(0);
+            }
+        }
+    } else if (warp == (NSOFT + 2 * NDEQ) / 32 + 2) {
+        // ======================= O += P V (and the denominator block) for every tile ====================
+        if (lane == 0) {
+            const uint32_t idO = umma_idesc(128, HD), idL = umma_idesc(128, 16);
+            const uint32_t va = smem_u32(Vsm), oa = smem_u32(ONES);
             for (int j = 0; j < n_tiles; ++j) {
-                if (j + 1 < n_tiles) {
-                    wait(B_KF0 + ((j + 1) & 1), ((j + 1) >> 1) & 1);
-                    tc_fence_after();
-                    issue_S(j + 1);
-                }
                 wait(B_P0 + (j & 1), (j >> 1) & 1);
                 wait(B_VF0 + (j & 1), (j >> 1) & 1);
                 tc_fence_after();
@@ -404,8 +422,8 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill(const Params P) {
                 bulk_g2s(dst + C::RAW_BYTES, P.kvv + hb + (size_t)sp * REC, bytes, &bars[B_RAW_FULL0 + b]);
             }
         }
-    } else if (warp > (NSOFT + 2 * NDEQ) / 32 + 1) {
-        // idle warps that complete the last warpgroup
+    } else if (warp > (NSOFT + 2 * NDEQ) / 32 + 2) {
+        // idle warp that completes the last warpgroup
     } else if (warp >= (NSOFT + NDEQ) / 32) {
         // ======================= V dequant warps: V^T operand, [dim][key] ============================
         regs_shrink<REGS_DEQ>();
@@ -636,12 +654,23 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill(const Params P) {
         const float l = __uint_as_float(tmem_ld1(tmem + lane_base + C::T_L));
         const float il = l > 0.f ? 1.f / l : 0.f;
         const size_t oi = (((size_t)(rbase + r)) * P.Hq + kvh * G + h) * HD + half * (HD / 2);
+        float* rec = P.nsplit > 1 ? P.recs + ((((size_t)blockIdx.z * P.rows) + rbase + r) * P.Hq + kvh * G + h) * (size_t)(HD + 2)
+                                  : nullptr;
+        if (rec && row_ok && half == 0) {
+            rec[HD] = m_ref > 0.5f * NEG_BIG ? m_ref * c2 : NEG_BIG;
+            rec[HD + 1] = l;
+        }
 #pragma unroll 1
         for (int c = 0; c < HD / 64; ++c) {
             uint32_t o[32];
             tmem_ld32(tmem + lane_base + C::T_O + half * (HD / 2) + c * 32, o);
             if (row_ok) {
-                if (P.out_f16) {
+                if (rec) {
+                    float2* dst = reinterpret_cast<float2*>(rec + half * (HD / 2) + c * 32);    // records are 8-byte aligned
+#pragma unroll
+                    for (int q2 = 0; q2 < 16; ++q2)
+                        dst[q2] = make_float2(__uint_as_float(o[2 * q2]), __uint_as_float(o[2 * q2 + 1]));
+                } else if (P.out_f16) {
                     uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__half*>(P.out) + oi + c * 32);
 #pragma unroll
                     for (int q4 = 0; q4 < 4; ++q4) {

@@ -158,3 +158,52 @@ def test_reference_shipping_kernels_for_context(ref):
     mabs, rel, relmax, _ = errors(to_np(out), want)
     print(f"[reference shipping decode kernel vs its exact path] max-abs {mabs:.2e} rel-l2 {rel:.2e} rel-max {relmax:.2e}")
     assert mabs < 5e-2
+
+
+def test_reference_shipping_prompt_kernel_for_context(ref):
+    """The reference's shipping prompt-chunk dispatch (launch_attn_m with rows = 512 -> k_attn_tc_rs_opt, fp16
+    accumulation, bruce.cu:4021-4078) compiled for sm_100a, timed on this GPU next to this repository's kernel on
+    the same cache and queries (512 rows against 16,384 cached keys, the reference's geometry), and both compared
+    with the reference's exact path.  Context for the measurements; the only assertions are on this
+    repository's result."""
+    n, rows = 16384, 512
+    c = RefCase(ref, n, False, seed=47)
+    g, eng = c.g, c.eng
+    p0 = n - rows
+    q = c.ref_query(rows, seed=11)
+    pos = dev_i32([p0], "cuda")
+    want = to_np(c.ref_exact(q, p0, rows, ns=4))[None]
+    flops = 4.0 * g.head_dim * g.n_head * (rows * p0 + rows * (rows + 1) // 2)
+    # reference shipping kernels: split counts around its own rule (3 at this shape, bruce.cu:7703-7706)
+    best = None
+    for ns in (1, 3, 8):
+        out_r = torch.zeros((rows, g.n_head, g.head_dim), device="cuda")
+        part = torch.zeros(rows * ns * g.n_kv * 4 * (g.head_dim + 2), device="cuda")
+        ms = C.c_float()
+        rc = ref.ref_attn_shipping(_p(out_r), _p(q), _p(c.kvk), _p(c.kvv), _p(pos), _p(part), rows, ns, 0, g.slot_ctx, 5,
+                                   C.byref(ms))
+        assert rc == 0
+        us = ms.value * 1e3 / 5
+        if best is None or us < best[0]:
+            best = (us, ns, out_r)
+    mabs_r, rel_r, _, _ = errors(to_np(best[2])[None], want)
+    # this repository
+    out = new_out(eng, 1, rows, g.n_head, g.head_dim)
+    part = eng.alloc_part(1, rows)
+    for _ in range(3):
+        eng.launch_attn_m(out, q[None].contiguous(), c.kvk, c.kvv, pos, part, rows, False)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(5):
+        eng.launch_attn_m(out, q[None].contiguous(), c.kvk, c.kvv, pos, part, rows, False)
+    e1.record()
+    torch.cuda.synchronize()
+    us_here = e0.elapsed_time(e1) * 1e3 / 5
+    from tests.util import PROMPT_HEAD_REL_TOL
+    mabs, rel = assert_close(to_np(out), want, "prompt kernel vs reference exact kernels at depth 16K",
+                             head_tol=PROMPT_HEAD_REL_TOL)
+    print(f"[reference shipping prompt kernel, sm_100a build] {best[0]:.0f} us (ns={best[1]}) = {flops / best[0] / 1e6:.0f} TFLOPS,"
+          f" max-abs {mabs_r:.2e} rel {rel_r:.2e} vs its exact path;"
+          f" this repository {us_here:.0f} us = {flops / us_here / 1e6:.0f} TFLOPS, max-abs {mabs:.2e} rel {rel:.2e}")
+    assert eng.device_status() == 0
