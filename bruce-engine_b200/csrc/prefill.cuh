@@ -4,26 +4,32 @@
 // Behaviour replaced: k_attn_tc_rs_opt<NW,...> for rows > 8 and its dispatch
 // (engine/src/bruce.cu:2750-3131, 4021-4078); masks as bruce.cu:2799-2805, 3012-3029.
 //
-// Design (sm_100a), one CTA per (128-row M tile, kv head), 20 warps (8 softmax, 4 K-dequant, 4 V-dequant, 1 MMA issuer, 1 loader, 2 idle):
+// This file holds the kernel for head_dim 256 (the reference's own geometry) and the helpers shared with the
+// head_dim 128 kernel (prefill_hd128.cuh).
+//
+// Design (sm_100a), one CTA per (128-row M tile, kv head, key split), 20 warps, each warpgroup resized with
+// setmaxnreg for its role (8 softmax, 4 K-dequant, 4 V-dequant, S issuer, loader, P.V issuer, 1 idle):
 //   * M tile = 128/G consecutive query positions x the G query heads of one kv head (row m = position
 //     m / G, head m % G, the reference's pair packing, bruce.cu:2288-2296): every dequantised K/V tile
 //     serves all G heads, and the causal diagonal of a tile spans only 128/G positions.
-//   * One control thread streams raw K and V tiles (BN records each, one contiguous run per tile because
-//     the cache is head-major) with cp.async.bulk into a double buffer and issues every tcgen05.mma.
-//   * Two groups of four dequant warps (one for K, one for V, running in parallel) turn raw q8_0 records into fp16 operands in 128-byte-swizzled K-major shared
-//     memory: K as [key][dim], V transposed to [dim][key] with byte-permute interleaves, scale folded in.
-//   * S = Q K^T (M 128, N BN, K head_dim) and O += P V (M 128, N head_dim, K BN) run as tcgen05.mma with
-//     fp32 accumulators in tensor memory: O plus two S buffers, so S of tile j+1 is computed while the
-//     softmax warps work on tile j.
+//   * A loader thread streams raw K and V tiles (64 records each, one contiguous run per tile because the
+//     cache is head-major) with cp.async.bulk into a two-stage ring.
+//   * Two groups of four dequant warps (K and V in parallel) turn raw q8_0 records into fp16 operands in
+//     128-byte-swizzled K-major shared memory, double-buffered: K as [key][dim], V transposed to [dim][key]
+//     with byte-permute interleaves, scale folded in.
+//   * S = Q K^T (M 128, N 64, K head_dim) and O += P V (M 128, N head_dim, K 64) run as tcgen05.mma with
+//     fp32 accumulators in tensor memory, issued by two threads (one per product) so that neither waits on
+//     the other's barriers.  Q is the tensor-memory A operand of the first product, P of the second; the
+//     512 tensor-memory columns are O (256) + two S/P buffers (64 each) + Q (128).
 //   * Eight softmax warps: TMEM lane = accumulator row, two threads per row (one per half of the S
-//     columns), so the row max needs one exchange through shared memory and no shuffles.  P never
-//     leaves tensor memory: each thread overwrites the S columns it has just read with its fp16 P
-//     values, and the second MMA takes its A operand from there (S is double-buffered, so P is too and
-//     the softmax warps can run a tile ahead of the P.V MMA).  The softmax denominator is not summed by
-//     the warps at all: a block of ones appended to the V operand makes the tensor core accumulate
-//     sum(P) in fp32 next to O, from exactly the fp16-rounded P it multiplies with V.  O (and that sum)
-//     are rescaled in TMEM only when a row maximum grows by more than 2^8 (the reference value is kept
-//     otherwise and the final normalisation uses the same reference, so the result is unchanged).
+//     columns): one tcgen05.ld, 3-input max, an exchange of the row maximum through shared memory, packed
+//     fma + ex2, and P written back as fp16 pairs over the S columns just read.  With no tensor-memory
+//     column left for it, the softmax denominator is summed by these threads (fp32, next to P).  O is
+//     rescaled in TMEM only when a row maximum grows by more than 2^8 (the reference value is kept otherwise
+//     and the final normalisation uses the same reference, so the result is unchanged).
+//   * Key splits: when the (M tile, kv head) grid leaves SMs idle (64 CTAs for a 512-row chunk), gridDim.z
+//     CTAs share one M tile, each taking a contiguous share of the key tiles and leaving split records
+//     (unnormalised o, m, l) for the merge kernel.
 //   * Row n of the K operand / column n of S holds key kappa(n), a fixed permutation inside each 64-key
 //     span chosen so that every shared-memory access of the dequant warps is bank-conflict free.
 //   * Every mbarrier wait is bounded; a wait that runs out sets the device status word, the remaining
@@ -64,12 +70,13 @@ template <int HD, int BN>
 struct Cfg {
     static constexpr int NBLK = HD / 32;
     static constexpr int REC = HD + 2 * NBLK;
-    // head_dim 128: Q lives in tensor memory (the TMEM A operand of the S MMA) and the shared memory it would
-    // take double-buffers the fp16 K and V operands, so dequantising tile j+1 overlaps the MMAs of tile j.
-    // head_dim 256 has neither the tensor-memory columns nor the shared memory for that: Q in shared memory,
-    // single K/V buffers.
-    static constexpr bool Q_TMEM = HD == 128;
-    static constexpr int KV_BUFS = HD == 128 ? 2 : 1;
+    // Q lives in tensor memory (the TMEM A operand of the S MMA) and the shared memory it would take
+    // double-buffers the fp16 K and V operands, so dequantising tile j+1 overlaps the MMAs of tile j.
+    // At head_dim 256 that uses every tensor-memory column (O 256 + two S buffers of 64 + Q 128), so the
+    // softmax denominator cannot be accumulated by the tensor core there: the softmax threads sum it.
+    static constexpr bool Q_TMEM = true;
+    static constexpr bool L_MMA = HD == 128;
+    static constexpr int KV_BUFS = 2;
     static constexpr int RAW_STAGES = 2;
     static constexpr int Q_BYTES = Q_TMEM ? 0 : 128 * HD * 2;
     static constexpr int K_BYTES = BN * HD * 2;
@@ -78,7 +85,7 @@ struct Cfg {
     static constexpr int OFF_Q = 0;
     static constexpr int OFF_K = OFF_Q + Q_BYTES;
     static constexpr int OFF_V = OFF_K + KV_BUFS * K_BYTES;
-    static constexpr int ONES_BYTES = 16 * BN * 2;           // 16 operand rows of ones: the denominator MMA
+    static constexpr int ONES_BYTES = L_MMA ? 16 * BN * 2 : 0;   // 16 operand rows of ones: the denominator MMA
     static constexpr int OFF_ONES = OFF_V + KV_BUFS * V_BYTES;
     static constexpr int OFF_RAW = OFF_ONES + ONES_BYTES;    // [RAW_STAGES buffers][K | V]
     static constexpr int OFF_BAR = OFF_RAW + RAW_STAGES * 2 * RAW_BYTES;
@@ -88,10 +95,10 @@ struct Cfg {
     static constexpr int TOTAL = OFF_RMAX + 2 * 2 * 128 * 4 + 1024;   // + slack to align the base to 1024
     static constexpr int T_O = 0;                            // TMEM columns
     static constexpr int T_L = HD;                           // 16 columns, each = sum of P
-    static constexpr int T_S0 = HD + 32;
-    static constexpr int T_S1 = HD + 32 + BN;
-    static constexpr int T_Q = HD + 32 + 2 * BN;             // HD/2 columns of fp16 pairs (Q_TMEM only)
-    static_assert(HD + 32 + 2 * BN + (Q_TMEM ? HD / 2 : 0) <= TMEM_COLS, "tensor memory budget");
+    static constexpr int T_S0 = HD + (L_MMA ? 32 : 0);
+    static constexpr int T_S1 = T_S0 + BN;
+    static constexpr int T_Q = T_S1 + BN;                    // HD/2 columns of fp16 pairs
+    static_assert(T_Q + HD / 2 <= TMEM_COLS, "tensor memory budget");
     static_assert(RAW_BYTES % 16 == 0, "bulk copy size");
     static_assert((HD == 128 && BN == 128) || (HD == 256 && BN == 64), "supported tile shapes");
     static_assert(TOTAL <= 226 * 1024, "shared memory budget");
@@ -315,28 +322,31 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill(const Params P) {
         if (tid < NSOFT) {
             const int m = tid & 127, half = tid >> 7;
             const int r = m / G, h = m - r * G;
-            uint32_t qv[32];
+#pragma unroll 1
+            for (int cq = 0; cq < HD / 128; ++cq) {               // 64 dims = 32 columns per store
+                uint32_t qv[32];
 #pragma unroll
-            for (int i = 0; i < 32; ++i) qv[i] = 0u;
-            if (r < rows_eff) {
-                const size_t qi = (((size_t)(rbase + r)) * P.Hq + kvh * G + h) * HD + half * 64;
-                if (P.q_f16) {
-                    const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(P.q) + qi);
+                for (int i = 0; i < 32; ++i) qv[i] = 0u;
+                if (r < rows_eff) {
+                    const size_t qi = (((size_t)(rbase + r)) * P.Hq + kvh * G + h) * HD + half * (HD / 2) + cq * 64;
+                    if (P.q_f16) {
+                        const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(P.q) + qi);
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const uint4 w = src[i];
-                        qv[4 * i] = w.x; qv[4 * i + 1] = w.y; qv[4 * i + 2] = w.z; qv[4 * i + 3] = w.w;
-                    }
-                } else {
-                    const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(P.q) + qi);
+                        for (int i = 0; i < 8; ++i) {
+                            const uint4 w = src[i];
+                            qv[4 * i] = w.x; qv[4 * i + 1] = w.y; qv[4 * i + 2] = w.z; qv[4 * i + 3] = w.w;
+                        }
+                    } else {
+                        const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(P.q) + qi);
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        const float4 w = src[i];
-                        qv[2 * i] = pack_h2(w.x, w.y); qv[2 * i + 1] = pack_h2(w.z, w.w);
+                        for (int i = 0; i < 16; ++i) {
+                            const float4 w = src[i];
+                            qv[2 * i] = pack_h2(w.x, w.y); qv[2 * i + 1] = pack_h2(w.z, w.w);
+                        }
                     }
                 }
+                tmem_st32(tmem + ((uint32_t)((warp & 3) * 32) << 16) + C::T_Q + half * (HD / 4) + cq * 32, qv);
             }
-            tmem_st32(tmem + ((uint32_t)((warp & 3) * 32) << 16) + C::T_Q + half * 32, qv);
             tmem_st_wait();
         }
         tc_fence_before();
@@ -402,7 +412,7 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill(const Params P) {
                     const uint64_t b = umma_desc(vb + (ks >> 2) * (HD * 128)) + 2 * (ks & 3);
                     const uint64_t o = umma_desc(oa + (ks >> 2) * (16 * 128)) + 2 * (ks & 3);
                     umma_f16_ts(tmem + C::T_O, a, b, idO, acc);
-                    umma_f16_ts(tmem + C::T_L, a, o, idL, acc);             // every column = sum of P
+                    if constexpr (C::L_MMA) umma_f16_ts(tmem + C::T_L, a, o, idL, acc);   // every column = sum of P
                 }
                 umma_commit(&bars[B_PV0 + (j & 1)]);
             }
@@ -540,6 +550,7 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill(const Params P) {
         const float c2 = P.scale_log2;
         const float thr = RESCALE_THRESHOLD / c2;              // threshold in raw-score units
         float m_ref = NEG_BIG;                                 // reference maximum, raw-score units
+        float l_part = 0.f;                                    // this thread's share of sum(P) when the tensor core cannot keep it
 
         for (int j = 0; j < n_tiles; ++j) {
             const int t0 = (tile_first + j) * BN;
@@ -617,9 +628,13 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill(const Params P) {
                         for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
                         tmem_st32(ta, o);
                     }
-                    if (half == 0) {
-                        const uint32_t tl = tmem + lane_base + C::T_L;
-                        tmem_st1(tl, __float_as_uint(__uint_as_float(tmem_ld1(tl)) * alpha));
+                    if constexpr (C::L_MMA) {
+                        if (half == 0) {
+                            const uint32_t tl = tmem + lane_base + C::T_L;
+                            tmem_st1(tl, __float_as_uint(__uint_as_float(tmem_ld1(tl)) * alpha));
+                        }
+                    } else {
+                        l_part *= alpha;
                     }
                     tmem_st_wait();
                 }
@@ -639,7 +654,9 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill(const Params P) {
                 for (int i = 0; i < 32; i += 2) {
                     float e0, e1;
                     ffma2(e0, e1, __uint_as_float(v[c][i]), __uint_as_float(v[c][i + 1]), c2p, nbp);
-                    pk[i >> 1] = pack_h2(fast_exp2(e0), fast_exp2(e1));
+                    const float p0 = fast_exp2(e0), p1 = fast_exp2(e1);
+                    if constexpr (!C::L_MMA) l_part += p0 + p1;
+                    pk[i >> 1] = pack_h2(p0, p1);
                 }
                 tmem_st16(tS + c * 16, pk);
             }
@@ -651,7 +668,16 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill(const Params P) {
         // ---- epilogue: O / sum(P) -> global; each thread writes half of its row -----------------------
         wait(B_PV0 + ((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1);
         tc_fence_after();
-        const float l = __uint_as_float(tmem_ld1(tmem + lane_base + C::T_L));
+        float l;
+        if constexpr (C::L_MMA) {
+            l = __uint_as_float(tmem_ld1(tmem + lane_base + C::T_L));
+        } else {
+            // the two threads of a row add their shares; the exchange buffer of the opposite tile parity is idle
+            volatile float* xch = rmax + (n_tiles & 1) * 256;
+            xch[half * 128 + m] = l_part;
+            named_bar_sync(2 + (warp & 3), 64);
+            l = l_part + xch[(half ^ 1) * 128 + m];
+        }
         const float il = l > 0.f ? 1.f / l : 0.f;
         const size_t oi = (((size_t)(rbase + r)) * P.Hq + kvh * G + h) * HD + half * (HD / 2);
         float* rec = P.nsplit > 1 ? P.recs + ((((size_t)blockIdx.z * P.rows) + rbase + r) * P.Hq + kvh * G + h) * (size_t)(HD + 2)
