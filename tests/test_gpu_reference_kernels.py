@@ -207,3 +207,43 @@ def test_reference_shipping_prompt_kernel_for_context(ref):
           f" max-abs {mabs_r:.2e} rel {rel_r:.2e} vs its exact path;"
           f" this repository {us_here:.0f} us = {flops / us_here / 1e6:.0f} TFLOPS, max-abs {mabs:.2e} rel {rel:.2e}")
     assert eng.device_status() == 0
+
+
+def test_reference_shipping_decode_kernel_timing_for_context(ref):
+    """The reference's shipping decode dispatch (launch_attn_m with rows = 1 + k_attn_combine_rows) compiled for
+    sm_100a, timed on this GPU next to battn_decode on the same 65,536-position cache (the reference's geometry).
+    Its split count is tuned for a 28-SM GPU (56, bruce.cu:3926); the largest it supports (128) is tried as well."""
+    n = 65536
+    c = RefCase(ref, n, False, seed=53)
+    g, eng = c.g, c.eng
+    q = c.ref_query(1, seed=3)
+    pos = dev_i32([n - 1], "cuda")
+    want = to_np(c.ref_exact(q, n - 1, 1))[None]
+    nbytes = n * g.n_kv * (g.head_dim + g.head_dim // 16) * 2
+    best = None
+    for ns in (56, 128):
+        out_r = torch.zeros((1, g.n_head, g.head_dim), device="cuda")
+        part = torch.zeros(g.n_kv * ns * 4 * (g.head_dim + 2), device="cuda")
+        ms = C.c_float()
+        rc = ref.ref_attn_shipping(_p(out_r), _p(q), _p(c.kvk), _p(c.kvv), _p(pos), _p(part), 1, ns, 0, g.slot_ctx, 20,
+                                   C.byref(ms))
+        assert rc == 0
+        us = ms.value * 1e3 / 20
+        if best is None or us < best[0]:
+            best = (us, ns)
+    out = new_out(eng, 1, 1, g.n_head, g.head_dim)
+    part = eng.alloc_part(1, 1)
+    for _ in range(3):
+        eng.launch_attn_m(out, q[None].contiguous(), c.kvk, c.kvv, pos, part, 1, False)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(20):
+        eng.launch_attn_m(out, q[None].contiguous(), c.kvk, c.kvv, pos, part, 1, False)
+    e1.record()
+    torch.cuda.synchronize()
+    us_here = e0.elapsed_time(e1) * 1e3 / 20
+    assert_close(to_np(out), want, "decode vs reference exact kernels at 64K")
+    print(f"[reference shipping decode kernel, sm_100a build, 64K] {best[0]:.1f} us (ns={best[1]}) = "
+          f"{nbytes / best[0] / 1e6:.2f} TB/s; this repository {us_here:.1f} us = {nbytes / us_here / 1e6:.2f} TB/s")
+    assert eng.device_status() == 0
