@@ -32,9 +32,11 @@ namespace fd {
 constexpr int NW = 4;                     // consumer warps
 constexpr int TILE = 64;                  // keys per stage
 constexpr int NTHREADS = (NW + 1) * 32;   // + one producer warp
-// pipeline depth; the widest instantiation (head_dim 256, 8 rows) keeps two stages to fit shared memory
+// pipeline depth: three stages of 2 x 8.7 KB at head_dim 128; two stages of 2 x 17.4 KB at head_dim 256, so that
+// three CTAs (twelve consumer warps) still fit one SM -- with three stages only two CTAs fit and the conversion
+// work of the wider head leaves the kernel issue-bound (3.1 instead of 4 TB/s at 64K)
 template <int HD, int NT>
-__host__ __device__ constexpr int stages_of() { return (HD == 256 && NT == 4) ? 2 : 3; }
+__host__ __device__ constexpr int stages_of() { return HD == 256 ? 2 : 3; }
 
 struct Params {
     const void* q;
