@@ -326,6 +326,47 @@ def bench_prefill(torch, AttnEngine, G_B, device, reps: int, window: int = WINDO
     return res
 
 
+def bench_prefill_short_chunks(torch, AttnEngine, G_B, device, reps: int):
+    """Short prompt chunks (64, 128, 256 rows) against 16,384 cached keys, full-causal layer: microseconds per
+    attention call (eager, CUDA events around `reps` back-to-back calls) and TFLOPS.  These shapes leave most SMs
+    without an M tile, which is what the key splits of the prompt kernel are for."""
+    depth = 16384
+    res = {}
+    g = G_B.with_(slot_ctx=depth + 256, window=WINDOW)
+    eng = AttnEngine(g, device)
+    dev = eng.device
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(13)
+    kvk, kvv = eng.alloc_kv_layer(False)
+    pos = torch.zeros(1, dtype=torch.int32, device=dev)
+    for a in range(0, depth, 512):
+        k = torch.randn((1, 512, g.n_kv, g.head_dim), generator=gen, device=dev)
+        v = torch.randn((1, 512, g.n_kv, g.head_dim), generator=gen, device=dev)
+        pos.fill_(a)
+        eng.qkv_prep_store(k, v, kvk, kvv, pos, rows=512)
+    pos.fill_(depth)
+    for rows in (64, 128, 256):
+        k = torch.randn((1, rows, g.n_kv, g.head_dim), generator=gen, device=dev)
+        eng.qkv_prep_store(k, k, kvk, kvv, pos, rows=rows)
+        q = torch.randn((1, rows, g.n_head, g.head_dim), generator=gen, device=dev).half()
+        out = torch.zeros_like(q)
+        part = eng.alloc_part(1, rows)
+        for _ in range(3):
+            eng.launch_attn_m(out, q, kvk, kvv, pos, part, rows, False)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            eng.launch_attn_m(out, q, kvk, kvv, pos, part, rows, False)
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / reps
+        flops = 4.0 * g.head_dim * g.n_head * (rows * depth + rows * (rows + 1) // 2)
+        res[f"rows_{rows}"] = {"us_per_call": us, "TFLOPS": flops / us / 1e6}
+    assert eng.device_status() == 0
+    return res
+
+
 def bench_qkv_prep(torch, AttnEngine, G_B, device, reps: int):
     """The fused QKV prologue + append (L2 scale, RoPE, sqk, q8_0 store, fp16 q for the attention kernels) on a
     512-row prompt chunk and on a 64-slot decode batch: microseconds per call and algorithmic HBM bytes per second
@@ -568,7 +609,8 @@ def run_gpu(args):
     if args.case == "prefill":                      # light run for profiling the prompt-chunk kernel
         from bruce_engine_b200.layout import G_R
         print(json.dumps({"prefill": bench_prefill(torch, AttnEngine, G_B, local, max(1, args.steps)),
-                          "prefill_hd256_w1024": bench_prefill(torch, AttnEngine, G_R, local, max(1, args.steps), window=1024)}))
+                          "prefill_hd256_w1024": bench_prefill(torch, AttnEngine, G_R, local, max(1, args.steps), window=1024),
+                          "short_chunks_at_16k": bench_prefill_short_chunks(torch, AttnEngine, G_B, local, 10)}))
         return 0
     layers = [Layer(c, s, gen, torch, AttnEngine, G_B, local) for c in ctxs for s in (False, True)]
     torch.cuda.synchronize()

@@ -91,12 +91,11 @@ inline FdWs fd_workspace(const battn_handle* h, int n_seq, int rows) {
 inline int exact_default_splits(int rows) { return rows > 64 ? 2 : (rows > 8 ? 8 : 32); }
 
 // Key splits of the prompt kernel: its grid is (M tiles) x (kv heads), which leaves SMs idle for short chunks and
-// for head_dim 256 (64 CTAs for a 512-row chunk); each (M tile, kv head) is then shared by several CTAs that take
+// for few kv heads (64 CTAs for a 512-row chunk in the 16/4/256 geometry); each (M tile, kv head) is then shared by several CTAs that take
 // contiguous shares of the key tiles and leave split records for the merge kernel.  Positions are device-resident,
 // so the choice depends on the chunk shape only.
 inline int prefill_splits(const battn_handle* h, int rows, int is_swa) {
     const Geom& g = h->g;
-    if (g.HD != 256) return 1;
     const int ctas = ((rows + 128 / g.G - 1) / (128 / g.G)) * g.Hkv;
     int s = h->num_sms / ctas;
     // a share should keep at least 16 key tiles of 64, or the merge costs more than the split saves; a

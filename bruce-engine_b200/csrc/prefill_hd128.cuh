@@ -95,8 +95,21 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill_hd128(const Params P) {
     const int lo_cta = P.is_swa ? max(0, p_first + 1 - P.W) : 0;       // bruce.cu:2801
     const int hi_cta = p_last + 1;
     const int full_lo = P.is_swa ? max(0, p_last + 1 - P.W) : 0;
-    const int tile_first = lo_cta / BN;
-    const int n_tiles = (hi_cta + BN - 1) / BN - tile_first;
+    // key split: gridDim.z CTAs share this (M tile, kv head), each takes a contiguous share of the key tiles
+    const int tile_lo = lo_cta / BN;
+    const int n_all = (hi_cta + BN - 1) / BN - tile_lo;
+    const int per_split = (n_all + P.nsplit - 1) / P.nsplit;
+    const int tile_first = tile_lo + (int)blockIdx.z * per_split;
+    const int n_tiles = max(0, min(per_split, n_all - (int)blockIdx.z * per_split));
+    if (n_tiles == 0) {
+        // more splits than key tiles (shallow context): an empty record, so the merge ignores this share
+        if (tid < 128 && tid / G < rows_eff) {
+            float* rec = P.recs + ((((size_t)blockIdx.z * P.rows) + rbase + tid / G) * P.Hq + kvh * G + tid % G) * (size_t)(HD + 2);
+            for (int i = 0; i < HD; ++i) rec[i] = 0.f;
+            rec[HD] = NEG_BIG; rec[HD + 1] = 0.f;
+        }
+        return;
+    }
 
     // ---- set-up: barriers, tensor memory, the rows of ones, Q -----------------------------------------
     if (tid == 0) {
@@ -456,12 +469,25 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill_hd128(const Params P) {
         const float l = __uint_as_float(tmem_ld1(tmem + lane_base + T_L));
         const float il = l > 0.f ? 1.f / l : 0.f;
         const size_t oi = (((size_t)(rbase + r)) * P.Hq + kvh * G + h) * HD + grp * (HD / 2);
+        // with key splits: a split record (unnormalised o, m in log2 units, l) instead of the output row
+        float* rec = P.nsplit > 1 ? P.recs + ((((size_t)blockIdx.z * P.rows) + rbase + r) * P.Hq + kvh * G + h) * (size_t)(HD + 2)
+                                  : nullptr;
+        if (rec && row_ok && grp == 0) {
+            const float mr = mref[m];
+            rec[HD] = mr > 0.5f * NEG_BIG ? mr * c2 : NEG_BIG;
+            rec[HD + 1] = l;
+        }
 #pragma unroll 1
         for (int c = 0; c < HD / 64; ++c) {
             uint32_t o[32];
             tmem_ld32(tmem + lane_base + T_O + grp * (HD / 2) + c * 32, o);
             if (row_ok) {
-                if (P.out_f16) {
+                if (rec) {
+                    float2* dst = reinterpret_cast<float2*>(rec + grp * (HD / 2) + c * 32);     // records are 8-byte aligned
+#pragma unroll
+                    for (int q2 = 0; q2 < 16; ++q2)
+                        dst[q2] = make_float2(__uint_as_float(o[2 * q2]), __uint_as_float(o[2 * q2 + 1]));
+                } else if (P.out_f16) {
                     uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__half*>(P.out) + oi + c * 32);
 #pragma unroll
                     for (int q4 = 0; q4 < 4; ++q4) {
