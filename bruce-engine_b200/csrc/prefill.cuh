@@ -556,7 +556,8 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill(const Params P) {
             const int t0 = (tile_first + j) * BN;
             const uint32_t tS = tmem + lane_base + ((j & 1) ? C::T_S1 : C::T_S0) + half * HC;
             // tiles every row of the CTA sees completely skip the mask code (bruce.cu:2927-2928)
-            const bool masked = !(t0 >= full_lo && t0 + BN - 1 <= p_first) || rows_eff < MR;
+            // (rows past the end of a ragged M tile hold zero queries: whatever they compute is finite and never stored)
+            const bool masked = !(t0 >= full_lo && t0 + BN - 1 <= p_first);
             wait(B_S0 + (j & 1), (j >> 1) & 1);
             tc_fence_after();
             // One read of this thread's S columns; they stay in registers for both the maximum and the

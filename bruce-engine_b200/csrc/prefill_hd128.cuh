@@ -352,7 +352,8 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill_hd128(const Params P) {
             const int t0 = (tile_first + j) * BN;
             const uint32_t tS = tmem + lane_base + T_S + slot(j) * BN;
             // tiles every row of the CTA sees completely skip the mask code (bruce.cu:2927-2928)
-            const bool masked = !(t0 >= full_lo && t0 + BN - 1 <= p_first) || rows_eff < MR;
+            // (rows past the end of a ragged M tile hold zero queries: whatever they compute is finite and never stored)
+            const bool masked = !(t0 >= full_lo && t0 + BN - 1 <= p_first);
             wait(B_S + slot(j), phase(j), 50);
             tc_fence_after();
             uint32_t v[2][32];
