@@ -299,15 +299,28 @@ def bench_prefill(torch, AttnEngine, G_B, device, reps: int, window: int = WINDO
 
         prompt()                                   # warm-up (also fills the cache)
         torch.cuda.synchronize()
+        # per-kernel times: an eager pass with an event pair around every attention launch
         eng.profile_start(n_chunks * reps)
+        for _ in range(reps):
+            prompt()
+        torch.cuda.synchronize()
+        kms = eng.profile_stop()
+        # prompt time: the 32 x (append + attend) launches captured once into a CUDA graph (positions are
+        # device-resident, one tensor per chunk) and replayed, as the reference replays its captured chunk steps;
+        # launched call by call from Python the host's launch rate, not the GPU, would bound the early chunks
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            prompt()
+        graph.replay()
+        torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(reps):
-            prompt()
+            graph.replay()
         e1.record()
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1) / reps
-        kms = eng.profile_stop()
+        del graph
         pairs = prefill_pairs(PREFILL_PROMPT, WINDOW if is_swa else None)
         flops = pairs * flop_per_pair
         last = [kms[r * n_chunks + n_chunks - 1] for r in range(reps)]
