@@ -183,7 +183,10 @@ int battn_verify(battn_handle* h, void* out, const void* q, const uint8_t* kvk, 
 /* Prompt-chunk attention: `rows` (1..512) query rows at pos[0] .. pos[0]+rows-1 against the cache
  * AFTER the chunk's own K/V were appended: launch_attn_m(rows > 8) + the merge
  * (bruce.cu:4021-4078, 2750-3131, call :7729-7732).  Causal plus optional window.
- *   q, out [rows][n_head][head_dim].  kvk/kvv are the slot base. */
+ *   q, out [rows][n_head][head_dim].  kvk/kvv are the slot base.
+ *   ws: scratch of battn_workspace_bytes(1, rows) bytes.  When the chunk's (M tile, kv head) grid would leave
+ *   SMs idle, several CTAs share an M tile over disjoint key ranges and leave split records there, which a merge
+ *   launch turns into `out` (the reference's own prompt kernel does the same with its `ns` splits, :7696-7706). */
 int battn_prefill(battn_handle* h, void* out, const void* q, const uint8_t* kvk, const uint8_t* kvv,
                   const int* pos, void* ws, int rows, int is_swa, void* stream);
 
