@@ -349,9 +349,13 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill(const Params P) {
             }
             tmem_st_wait();
         }
-        tc_fence_before();
-        __syncthreads();
-        tc_fence_after();
+        // Q only concerns its writers (the softmax warps) and its reader (the S issuer): the loader, the dequant
+        // warps and the P.V issuer go straight to work, so the first raw tiles and their conversion overlap the Q load
+        if (warp < NSOFT / 32 || warp == (NSOFT + 2 * NDEQ) / 32) {
+            tc_fence_before();
+            named_bar_sync(6, NSOFT + 32);
+            tc_fence_after();
+        }
     }
 
     // bounded wait that degrades to "do not wait" once any wait has run out

@@ -170,9 +170,13 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill_hd128(const Params P) {
         tmem_st32(tmem + ((uint32_t)((warp & 3) * 32) << 16) + T_Q + half * 32, qv);
         tmem_st_wait();
     }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
+    // Q only concerns its writers (the eight softmax warps) and its reader (the S issuer): the loaders, the dequant
+    // warps and the P.V issuer go straight to work, so the first raw tiles and their conversion overlap the Q load
+    if (warp < 8 || warp == W_MMA) {
+        tc_fence_before();
+        named_bar_sync(3, 9 * 32);
+        tc_fence_after();
+    }
 
     // bounded wait that degrades to "do not wait" once any wait has run out
     auto wait = [&](int b, uint32_t parity, uint32_t sleep_ns) {
