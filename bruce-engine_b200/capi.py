@@ -35,6 +35,7 @@ SIGNATURES = {
     "battn_destroy": (_I, [_P]),
     "battn_kv_layer_bytes": (_I, [_P, _I, _SZP]),
     "battn_workspace_bytes": (_I, [_P, _I, _I, _SZP]),
+    "battn_call_workspace_bytes": (_I, [C.POINTER(CGeom), _I, _I, _I, _SZP]),
     "battn_exact_workspace_bytes": (_I, [_P, _I, _I, _I, _SZP]),
     "battn_kv_append": (_I, [_P] * 8 + [_I, _I, _I, _P]),
     "battn_qkv_prep": (_I, [_P] * 8 + [_I] + [_P] * 5 + [_I, _I, _I, _P]),
@@ -47,6 +48,7 @@ SIGNATURES = {
     "battn_partials": (_I, [_P] * 9 + [_I, _I, _I, _P]),
     "battn_merge": (_I, [_P, _P, _P, _I, _I, _P]),
     "battn_device_status": (_I, [_P, C.POINTER(_I), _I]),
+    "battn_selftest_wait_timeout": (_I, [_P, C.c_uint, _P]),
     "battn_profile_start": (_I, [_P, _I]),
     "battn_profile_stop": (_I, [_P, C.POINTER(C.c_float), _I, C.POINTER(_I)]),
     "battn_last_cuda_error": (_I, [_P]),

@@ -17,6 +17,16 @@ using namespace battn;
 
 namespace {
 
+// The wait self-test: thread 0 waits on an mbarrier that has one pending arrival nobody will make.
+__global__ void k_wait_selftest(int* status, uint32_t limit) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        mbar_fence_init();
+        if (!mbar_wait_bounded(&bar, 0, limit)) atomicOr(status, BATTN_DEV_WAIT_TIMEOUT);
+    }
+}
+
 constexpr size_t SMEM_MAX = 226 * 1024;     // dynamic shared memory per CTA: the 227 KB opt-in limit of sm_100
                                             // minus room for the kernels' static shared variables
 int g_init_cuda_error = 0;                  // cudaError_t of the last failing battn_init
@@ -109,9 +119,17 @@ inline size_t exact_workspace(const battn_handle* h, int n_seq, int rows, int ns
     return (size_t)n_seq * rows * g.Hq * nsplit * (g.HD + 2) * sizeof(float);
 }
 
+// split records of a prompt chunk of `rows` rows (full-attention layers take at least as many splits as
+// sliding-window layers)
+inline size_t prefill_workspace(const battn_handle* h, int rows) {
+    return exact_workspace(h, 1, rows, prefill_splits(h, rows, 0));
+}
+
 int check_seq_args(const battn_handle* h, const void* a, const void* b, const void* c, const void* d,
                    const int* pos, const int* kslot, int n_seq, int rows, int max_rows) {
     if (!h || !a || !b || !c || !d || !pos) return BATTN_ERR_ARG;
+    // every data pointer is read or written with 16-byte accesses (float4 / uint4 loads, bulk copies)
+    if ((((uintptr_t)a | (uintptr_t)b | (uintptr_t)c | (uintptr_t)d) & 15) != 0) return BATTN_ERR_ARG;
     if (n_seq < 1 || rows < 1) return BATTN_ERR_ARG;
     if (!kslot && n_seq != 1) return BATTN_ERR_ARG;
     if (n_seq > MAX_SEQ || rows > max_rows) return BATTN_ERR_CAPACITY;
@@ -221,7 +239,7 @@ int launch_flash(battn_handle* h, void* out, float* rec_out, const void* q, cons
     if (e != cudaSuccess) return cuda_fail(h, e);
 
     MergeParams M{};
-    M.mode = MERGE_BALANCED; M.part = P.part; M.out = out; M.rec_out = rec_out;
+    M.mode = 0; M.part = P.part; M.out = out; M.rec_out = rec_out;
     M.n_rows = n_seq * rows; M.rows = rows; M.Hq = g.Hq; M.Hkv = g.Hkv; M.G = g.G;
     M.count = 0; M.log2_domain = 1; M.out_f16 = g.out_f16; M.hdr = P.hdr; M.status = h->d_status;
     if (g.HD == 128) e = launch_pdl(k_merge_balanced<128>, dim3(n_seq * rows * g.Hq), dim3(MERGE_B_THREADS), 0, st, M);
@@ -266,6 +284,32 @@ int launch_prefill(battn_handle* h, void* out, const void* q, const uint8_t* kvk
     return e == cudaSuccess ? BATTN_OK : cuda_fail(h, e);
 }
 
+// validates a caller's geometry and derives the internal one
+int geom_from(const battn_geom* geom, Geom& g) {
+    if (!geom) return BATTN_ERR_ARG;
+    if (geom->head_dim != 128 && geom->head_dim != 256) return BATTN_ERR_ARG;
+    if (geom->n_head < 1 || geom->n_kv < 1 || geom->n_head % geom->n_kv) return BATTN_ERR_ARG;
+    const int G = geom->n_head / geom->n_kv;
+    if (G > 8) return BATTN_ERR_ARG;
+    if (geom->window < 32 || (geom->window & (geom->window - 1))) return BATTN_ERR_ARG;
+    if (geom->slot_ctx < 2 || (geom->slot_ctx & 1) || geom->n_slots < 1) return BATTN_ERR_ARG;
+    if ((geom->q_dtype != BATTN_F32 && geom->q_dtype != BATTN_F16) ||
+        (geom->out_dtype != BATTN_F32 && geom->out_dtype != BATTN_F16)) return BATTN_ERR_ARG;
+    g.Hq = geom->n_head; g.Hkv = geom->n_kv; g.HD = geom->head_dim; g.G = G;
+    g.W = geom->window; g.ring = 2 * geom->window;
+    g.slot_ctx = geom->slot_ctx; g.n_slots = geom->n_slots;
+    g.nblk = g.HD / 32; g.rec = g.HD + 2 * g.nblk;
+    g.q_f16 = geom->q_dtype == BATTN_F16; g.out_f16 = geom->out_dtype == BATTN_F16;
+    g.scale = geom->softmax_scale != 0.f ? geom->softmax_scale : 1.f / sqrtf((float)g.HD);
+    return BATTN_OK;
+}
+
+// scratch bytes that ONE call of exactly this shape writes (its split records and their header)
+size_t call_workspace(const battn_handle* h, int n_seq, int rows) {
+    if (rows * h->g.G <= 32) return fd_workspace(h, n_seq, rows).total;
+    return n_seq == 1 ? prefill_workspace(h, rows) : 0;
+}
+
 }  // namespace
 
 extern "C" {
@@ -275,24 +319,14 @@ int battn_version(void) { return BATTN_VERSION; }
 int battn_init(const battn_geom* geom, int device, battn_handle** out_handle) {
     if (!geom || !out_handle) return BATTN_ERR_ARG;
     *out_handle = nullptr;
-    if (geom->head_dim != 128 && geom->head_dim != 256) return BATTN_ERR_ARG;
-    if (geom->n_head < 1 || geom->n_kv < 1 || geom->n_head % geom->n_kv) return BATTN_ERR_ARG;
-    const int G = geom->n_head / geom->n_kv;
-    if (G > 8) return BATTN_ERR_ARG;
-    if (geom->window < 32 || (geom->window & (geom->window - 1))) return BATTN_ERR_ARG;
-    if (geom->slot_ctx < 2 || (geom->slot_ctx & 1) || geom->n_slots < 1) return BATTN_ERR_ARG;
-    if ((geom->q_dtype != BATTN_F32 && geom->q_dtype != BATTN_F16) ||
-        (geom->out_dtype != BATTN_F32 && geom->out_dtype != BATTN_F16)) return BATTN_ERR_ARG;
+    Geom g0;
+    const int grc = geom_from(geom, g0);
+    if (grc) return grc;
 
     battn_handle* h = new (std::nothrow) battn_handle();
     if (!h) return BATTN_ERR_ARG;
     Geom& g = h->g;
-    g.Hq = geom->n_head; g.Hkv = geom->n_kv; g.HD = geom->head_dim; g.G = G;
-    g.W = geom->window; g.ring = 2 * geom->window;
-    g.slot_ctx = geom->slot_ctx; g.n_slots = geom->n_slots;
-    g.nblk = g.HD / 32; g.rec = g.HD + 2 * g.nblk;
-    g.q_f16 = geom->q_dtype == BATTN_F16; g.out_f16 = geom->out_dtype == BATTN_F16;
-    g.scale = geom->softmax_scale != 0.f ? geom->softmax_scale : 1.f / sqrtf((float)g.HD);
+    g = g0;
     h->device = device; h->last_cuda_error = 0; h->launches = 0; h->d_status = nullptr;
     h->prof_ev = nullptr; h->prof_cap = 0; h->prof_n = 0;
 
@@ -335,16 +369,28 @@ int battn_kv_layer_bytes(const battn_handle* h, int is_swa, size_t* out_bytes) {
 int battn_workspace_bytes(const battn_handle* h, int n_seq, int rows_per_seq, size_t* out_bytes) {
     if (!h || !out_bytes || n_seq < 1 || rows_per_seq < 1) return BATTN_ERR_ARG;
     if (n_seq > MAX_SEQ || rows_per_seq > MAX_PREFILL) return BATTN_ERR_CAPACITY;
-    size_t need = exact_workspace(h, n_seq, rows_per_seq, exact_default_splits(rows_per_seq));
-    if (rows_per_seq * h->g.G > 32 && n_seq == 1) {
-        const size_t f = exact_workspace(h, 1, rows_per_seq, prefill_splits(h, rows_per_seq, 0));    // same record size
-        if (f > need) need = f;
-    }
-    if (rows_per_seq * h->g.G <= 32) {
-        const size_t f = fd_workspace(h, n_seq, rows_per_seq).total;
+    // The buffer must serve every call of UP TO rows_per_seq rows (a prompt's last chunk is shorter than the
+    // chunk the buffer was sized for), and the split count of a prompt chunk grows as the chunk shrinks, so the
+    // need is not monotone in the row count: take the maximum over all shorter calls.
+    size_t need = 0;
+    for (int r = 1; r <= rows_per_seq; ++r) {
+        size_t f = exact_workspace(h, n_seq, r, exact_default_splits(r));
+        const size_t w = call_workspace(h, n_seq, r);
+        if (w > f) f = w;
         if (f > need) need = f;
     }
     *out_bytes = align_up(need, 256);
+    return BATTN_OK;
+}
+
+int battn_call_workspace_bytes(const battn_geom* geom, int num_sms, int n_seq, int rows_per_seq, size_t* out_bytes) {
+    if (!out_bytes || num_sms < 1 || n_seq < 1 || rows_per_seq < 1) return BATTN_ERR_ARG;
+    if (n_seq > MAX_SEQ || rows_per_seq > MAX_PREFILL) return BATTN_ERR_CAPACITY;
+    battn_handle tmp{};
+    const int rc = geom_from(geom, tmp.g);
+    if (rc) return rc;
+    tmp.num_sms = num_sms;
+    *out_bytes = call_workspace(&tmp, n_seq, rows_per_seq);
     return BATTN_OK;
 }
 
@@ -384,7 +430,7 @@ int battn_qkv_prep(battn_handle* h, void* q_out, const float* q, const float* k,
     const int rc = check_seq_args(h, k, v, kvk, kvv, pos, kslot, n_seq, rows_per_seq, MAX_PREFILL);
     if (rc) return rc;
     if (!q_out || !q || !sqk || !cs || !sn || (theta_sel != 1 && theta_sel != 2)) return BATTN_ERR_ARG;
-    if ((((uintptr_t)q_out | (uintptr_t)q | (uintptr_t)sqk | (uintptr_t)cs | (uintptr_t)sn) & 15) != 0) return BATTN_ERR_ARG;
+    if ((((uintptr_t)q_out | (uintptr_t)q | (uintptr_t)sqk | (uintptr_t)cs | (uintptr_t)sn) & 15) != 0) return BATTN_ERR_ARG;   // k, v, kvk, kvv: check_seq_args
     const Geom& g = h->g;
     if (is_swa && rows_per_seq > g.ring) return BATTN_ERR_CAPACITY;        // as battn_kv_append
     PrepParams P;
@@ -421,7 +467,7 @@ int battn_decode(battn_handle* h, void* out, const void* q, const uint8_t* kvk, 
                  const int* kslot, const int* act, void* ws, int n_seq, int is_swa, void* stream) {
     const int rc = check_seq_args(h, out, q, kvk, kvv, pos, kslot, n_seq, 1, 1);
     if (rc) return rc;
-    if (!ws) return BATTN_ERR_ARG;
+    if (!ws || ((uintptr_t)ws & 15)) return BATTN_ERR_ARG;
     return launch_flash(h, out, nullptr, q, kvk, kvv, pos, kslot, act, ws, n_seq, 1, is_swa, (cudaStream_t)stream);
 }
 
@@ -440,7 +486,7 @@ int battn_verify(battn_handle* h, void* out, const void* q, const uint8_t* kvk, 
                  const int* kslot, const int* act, void* ws, int rows, int batch, int is_swa, void* stream) {
     const int rc = check_seq_args(h, out, q, kvk, kvv, pos, kslot, batch, rows, MAX_VERIFY);
     if (rc) return rc;
-    if (!ws) return BATTN_ERR_ARG;
+    if (!ws || ((uintptr_t)ws & 15)) return BATTN_ERR_ARG;
     return launch_flash(h, out, nullptr, q, kvk, kvv, pos, kslot, act, ws, batch, rows, is_swa, (cudaStream_t)stream);
 }
 
@@ -449,7 +495,7 @@ int battn_partials(battn_handle* h, float* rec, const void* q, const uint8_t* kv
                    void* stream) {
     const int rc = check_seq_args(h, rec, q, kvk, kvv, pos, kslot, batch, rows, MAX_VERIFY);
     if (rc) return rc;
-    if (!ws) return BATTN_ERR_ARG;
+    if (!ws || ((uintptr_t)ws & 15)) return BATTN_ERR_ARG;
     return launch_flash(h, nullptr, rec, q, kvk, kvv, pos, kslot, act, ws, batch, rows, is_swa, (cudaStream_t)stream);
 }
 
@@ -457,7 +503,7 @@ int battn_prefill(battn_handle* h, void* out, const void* q, const uint8_t* kvk,
                   void* ws, int rows, int is_swa, void* stream) {
     const int rc = check_seq_args(h, out, q, kvk, kvv, pos, nullptr, 1, rows, MAX_PREFILL);
     if (rc) return rc;
-    if (!ws) return BATTN_ERR_ARG;
+    if (!ws || ((uintptr_t)ws & 15)) return BATTN_ERR_ARG;
     // the ring must hold the whole chunk plus the oldest row's window (bruce.cu:50-53)
     if (is_swa && rows > h->g.W) return BATTN_ERR_CAPACITY;
     if (h->g.W < 64) return BATTN_ERR_ARG;               // key tiles of 64 / 128 must not wrap the ring
@@ -471,13 +517,14 @@ int battn_attend_exact(battn_handle* h, void* out, const void* q, const uint8_t*
                        int nsplit, int is_swa, void* stream) {
     const int rc = check_seq_args(h, out, q, kvk, kvv, pos, kslot, n_seq, rows_per_seq, MAX_PREFILL);
     if (rc) return rc;
-    if (!ws || nsplit < 1 || nsplit > MAX_SPLITS) return BATTN_ERR_ARG;
+    if (!ws || ((uintptr_t)ws & 15) || nsplit < 1 || nsplit > MAX_SPLITS) return BATTN_ERR_ARG;
     return launch_exact(h, out, nullptr, q, kvk, kvv, pos, kslot, act, ws, n_seq, rows_per_seq, nsplit, is_swa,
                         (cudaStream_t)stream);
 }
 
 int battn_merge(battn_handle* h, void* out, const float* parts, int n_parts, int n_rows, void* stream) {
     if (!h || !out || !parts || n_parts < 1 || n_rows < 1) return BATTN_ERR_ARG;
+    if ((((uintptr_t)out | (uintptr_t)parts) & 15) != 0) return BATTN_ERR_ARG;
     if (n_parts > MERGE_MAX_COUNT) return BATTN_ERR_CAPACITY;
     const Geom& g = h->g;
     MergeParams M{};
@@ -496,6 +543,14 @@ int battn_device_status(battn_handle* h, int* out_bits, int clear) {
     if (!h || !out_bits) return BATTN_ERR_ARG;
     cudaError_t e = cudaMemcpy(out_bits, h->d_status, sizeof(int), cudaMemcpyDeviceToHost);
     if (e == cudaSuccess && clear) e = cudaMemset(h->d_status, 0, sizeof(int));
+    return e == cudaSuccess ? BATTN_OK : cuda_fail(h, e);
+}
+
+int battn_selftest_wait_timeout(battn_handle* h, unsigned poll_limit, void* stream) {
+    if (!h || poll_limit < 1 || poll_limit > (1u << 22)) return BATTN_ERR_ARG;
+    k_wait_selftest<<<1, 32, 0, (cudaStream_t)stream>>>(h->d_status, poll_limit);
+    h->launches += 1;
+    const cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? BATTN_OK : cuda_fail(h, e);
 }
 

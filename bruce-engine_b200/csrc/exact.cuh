@@ -6,9 +6,9 @@
 // It is the slow, tensor-core-free path used to validate the fast kernels at sizes the CPU oracle
 // cannot reach, and the reference's own "--prefill-tc 0" behaviour.
 //
-// k_merge is the merge of k_attn_combine / k_attn_combine_rows (bruce.cu:992-1007, 1999-2016) for
-// three record layouts: the reference's regular [row][kvh][split][head] layout, the layout of
-// records gathered from several devices, and the work-balanced layout of the flash-decode kernel.
+// k_merge is the merge of k_attn_combine / k_attn_combine_rows (bruce.cu:992-1007, 1999-2016) for the
+// reference's regular [row][kvh][split][head] record layout and for records gathered from several
+// devices; k_merge_balanced merges the work-balanced records of the flash-decode kernels.
 #pragma once
 #include "common.cuh"
 
@@ -105,10 +105,10 @@ __global__ void __launch_bounds__(256) k_attn_exact(const ExactParams P) {
 
 // ------------------------------------------------------------------------------------------------
 
-enum { MERGE_REGULAR = 0, MERGE_GATHERED = 1, MERGE_BALANCED = 2 };
+enum { MERGE_REGULAR = 0, MERGE_GATHERED = 1 };
 
 struct MergeParams {
-    int mode;
+    int mode;              // k_merge only: MERGE_REGULAR or MERGE_GATHERED
     const float* part;     // records
     void* out;             // normalised output (out_f16 ? half : float), or null
     float* rec_out;        // merged record [row][head][HD+2] in natural-log units, or null
@@ -122,7 +122,7 @@ struct MergeParams {
     const int* pos; const int* kslot; const int* act;
     int is_swa, W, slot_ctx, n_slots;
     int* status;
-    // BALANCED only: header written by the flash-decode kernel: {tiles_per_cta, total, cum[n_seq+1]}
+    // k_merge_balanced only: header written by the flash-decode kernel: {tiles_per_cta, total, cum[n_seq+1]}
     const int* hdr;
 };
 
@@ -139,7 +139,7 @@ __global__ void __launch_bounds__(MERGE_THREADS) k_merge(const MergeParams P) {
     __shared__ float s_red[MERGE_THREADS / 32];
     __shared__ float2 s_acc[MERGE_THREADS];
     const int hq = blockIdx.x % P.Hq, rowidx = blockIdx.x / P.Hq;
-    const int i = rowidx / P.rows, r = rowidx % P.rows;
+    const int i = rowidx / P.rows;
     const int kvh = hq / P.G, h = hq % P.G;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const float* base;
@@ -151,22 +151,10 @@ __global__ void __launch_bounds__(MERGE_THREADS) k_merge(const MergeParams P) {
         count = P.count;
         base = P.part + (((size_t)rowidx * P.Hkv + kvh) * count * P.G + h) * (size_t)(HD + 2);
         stride = (size_t)P.G * (HD + 2);
-    } else if (P.mode == MERGE_GATHERED) {
+    } else {                                     // MERGE_GATHERED
         count = P.count;
         base = P.part + ((size_t)rowidx * P.Hq + hq) * (size_t)(HD + 2);
         stride = (size_t)P.n_rows * P.Hq * (HD + 2);
-    } else {
-        const int per = P.hdr[0];
-        const int c0 = P.hdr[2 + i], c1 = P.hdr[3 + i];
-        const int nt = c1 - c0;
-        if (nt <= 0) return;                                            // inactive sequence
-        const int item = i * P.Hkv + kvh;
-        const long long t0 = (long long)P.Hkv * c0 + (long long)kvh * nt, t1 = t0 + nt;
-        const int clo = (int)(t0 / per), chi = (int)((t1 - 1) / per);
-        const int RG = P.rows * P.G;
-        count = chi - clo + 1;
-        base = P.part + ((size_t)(clo + item) * RG + r * P.G + h) * (size_t)(HD + 2);
-        stride = (size_t)RG * (HD + 2);
     }
     count = min(count, MERGE_MAX_COUNT);
 
@@ -232,7 +220,7 @@ __global__ void __launch_bounds__(MERGE_THREADS) k_merge(const MergeParams P) {
     }
 }
 
-// The merge behind the flash-decode kernel (MERGE_BALANCED records only).  Those records are padded to
+// The merge behind the flash-decode kernels (their work-balanced records only).  Those records are padded to
 // HD + 4 floats so that every record is 16-byte aligned: 1024 threads = HD/4 float4 lanes x 32 (or 16)
 // record groups, so the ~74..592 records of a (row, head) are read in one or two rounds of independent
 // 16-byte loads instead of a long latency chain.

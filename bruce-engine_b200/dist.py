@@ -114,6 +114,8 @@ class SeqSplitDecoder:
     """Decode attention over one sequence whose KV cache is split by position range across the ranks
     of a process group (full-causal layers; window layers stay on the owner of the tail)."""
 
+    MAX_ROWS = 8     # rows per decode call (the verify limit, bruce.cu:94)
+
     def __init__(self, engine, n_total: int, group=None):
         self.eng, self.group = engine, group
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
@@ -122,7 +124,10 @@ class SeqSplitDecoder:
         if g.slot_ctx < self.shard.capacity:
             raise ValueError("engine slot_ctx is smaller than this rank's shard")
         dev = engine.device
-        self.part = engine.alloc_part(8, 1)
+        # decode() runs either `rows` one-row sequences (shards that lie wholly before the block) or one
+        # sequence of `rows` rows (the shard that holds the block): the scratch must serve both shapes
+        self.part = torch.empty(max(engine.workspace_bytes(self.MAX_ROWS, 1), engine.workspace_bytes(1, self.MAX_ROWS)),
+                                dtype=torch.uint8, device=dev)
         self._pos = torch.zeros(8, dtype=torch.int32, device=dev)
         self._kslot = torch.zeros(8, dtype=torch.int32, device=dev)
 
@@ -137,6 +142,8 @@ class SeqSplitDecoder:
     def decode(self, out, q, kvk, kvv, p0: int, rows: int = 1):
         """q, out: [rows][n_head][head_dim] (replicated on every rank).  Returns out."""
         g, eng = self.eng.geom, self.eng
+        if not 1 <= rows <= self.MAX_ROWS or rows * g.group > 32:
+            raise ValueError(f"rows must be 1..{self.MAX_ROWS} with rows * heads-per-kv-head <= 32")
         active, lp0, lrows = local_query(self.shard, p0, rows)
         rec = empty_records(rows, g.n_head, g.head_dim, eng.device)
         if active and lrows == 0:

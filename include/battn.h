@@ -23,8 +23,10 @@
  *     address = base + ((s * n_kv + h) * pstride + p') * record_bytes
  *     pstride = slot_ctx (full-attention layer) or 2*window (sliding-window layer, a ring)
  *     p'      = p (full) or p & (2*window - 1) (sliding window)
- * Requirements added by this implementation: the buffers are 16-byte aligned, slot_ctx is even,
- * window is a power of two >= 32.
+ * Requirements added by this implementation: slot_ctx is even, window is a power of two >= 32, and EVERY
+ * data pointer handed to an entry point (q, q_out, k, v, out, rec, parts, kvk, kvv, ws, sqk, cs, sn) is
+ * 16-byte aligned: the kernels use 16-byte loads, stores and bulk copies.  A misaligned pointer is
+ * rejected on the host with BATTN_ERR_ARG.
  */
 #ifndef BATTN_H
 #define BATTN_H
@@ -82,8 +84,17 @@ int battn_destroy(battn_handle* h);
 int battn_kv_layer_bytes(const battn_handle* h, int is_swa, size_t* out_bytes);
 
 /* Bytes of the split-K scratch (`part` in the reference, bruce.cu:1058-1070, 5564) needed for a
- * call with up to n_seq sequences of up to rows_per_seq query rows each. */
+ * call with up to n_seq sequences of up to rows_per_seq query rows each: a buffer of this size serves
+ * every call with 1..rows_per_seq rows (a prompt's shorter last chunk included). */
 int battn_workspace_bytes(const battn_handle* h, int n_seq, int rows_per_seq, size_t* out_bytes);
+
+/* Bytes of scratch that ONE call of exactly (n_seq sequences x rows_per_seq rows) writes on a device with
+ * num_sms multiprocessors -- the term battn_workspace_bytes maximises over all row counts up to its
+ * argument.  Needs no handle and no device: hosts use it to size `part` before a device is initialised
+ * (the reference sizes it from compile-time constants, bruce.cu:1058-1066), tests use it to check that
+ * battn_workspace_bytes covers every shorter call.  0 for shapes that use no scratch. */
+int battn_call_workspace_bytes(const battn_geom* geom, int num_sms, int n_seq, int rows_per_seq,
+                               size_t* out_bytes);
 
 /* Bytes of scratch battn_attend_exact needs for an explicit split count (the reference sizes
  * `part` as rows * nsplit records, bruce.cu:1060-1066). */
@@ -216,6 +227,14 @@ int battn_merge(battn_handle* h, void* out, const float* parts, int n_parts, int
 /* Device status word (bits BATTN_DEV_*), read with a blocking copy; clears it when `clear` != 0.
  * Not for use inside stream capture. */
 int battn_device_status(battn_handle* h, int* out_bits, int clear);
+
+/* Self-test of the bounded waits: launches one tiny kernel in which a thread waits, with the same
+ * bounded mbarrier wait the attention kernels use, on a barrier nothing ever arrives on; after
+ * poll_limit polls (1 .. 1<<22) the wait gives up, the kernel sets BATTN_DEV_WAIT_TIMEOUT in the device
+ * status word and returns normally.  Shows that a wait that runs out is reported through
+ * battn_device_status and leaves the context usable.  (The reference has no bounded waits: its kernels
+ * use __syncthreads only, and a stuck launch is a hung process.) */
+int battn_selftest_wait_timeout(battn_handle* h, unsigned poll_limit, void* stream);
 
 /* Per-kernel timing, the counterpart of the reference's --probe CUDA-event phase timing
  * (bruce.cu:8334-8397).  Between battn_profile_start and battn_profile_stop every attention call

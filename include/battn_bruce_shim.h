@@ -7,9 +7,10 @@
  * bruce.cu:7665-7761 (batched) and :7936-7980 (single row) change by a rename at most.
  *
  * What differs from the reference, by design:
- *   - k and v arrive already RoPE'd / normalised: the model-specific prologue of k_qkv_prep* (L2 norm,
- *     NeoX RoPE, sqk scale; bruce.cu:657-687, 1742-1780) stays in a host kernel; `kv_append_*` below
- *     replaces only the quantise-and-store half (:690-710).
+ *   - two forms of the append: `qkv_prep_rows` / `qkv_prep_ms` do everything k_qkv_prep* does in one launch
+ *     (L2 norm, NeoX RoPE, sqk scale, quantised store; bruce.cu:657-710, 1742-1812), bit-identical to the
+ *     reference; `kv_append_*` is only the quantise-and-store half (:690-710) for hosts whose k and v
+ *     arrive already RoPE'd and normalised.
  *   - launch_attn_m / launch_attn_ms write the NORMALISED output and ignore `ns`: the host then takes its
  *     existing ns == 1 branch (k_gate_norm_vec4 on `out`, bruce.cu:7745-7751) and never launches
  *     k_attn_combine* / k_combine_gate_norm_rows_opt.
@@ -26,6 +27,7 @@
 #include "battn.h"
 
 static battn_handle* g_battn = nullptr;   /* set once by battn_shim_init() from alloc_buffers() */
+static int g_battn_group = 1;             /* query heads per KV head */
 
 static inline void battn_shim_fail(const char* what, int rc) {
     std::fprintf(stderr, "battn: %s failed with status %d (cudaError %d)\n", what, rc,
@@ -39,6 +41,7 @@ static inline void battn_shim_fail(const char* what, int rc) {
 static inline void battn_shim_init(int n_head, int n_kv, int hd, int swa, int slot_ctx, int n_slots) {
     battn_geom g = {n_head, n_kv, hd, swa, slot_ctx, n_slots, BATTN_F32, BATTN_F32, 0.f};
     BATTN_CK(battn_init(&g, 0, &g_battn));
+    g_battn_group = n_head / n_kv;
 }
 /* size of M.part (bruce.cu:5564): rows = MBUF for the prompt path */
 static inline size_t battn_shim_part_bytes(int max_slots, int max_rows) {
@@ -87,9 +90,12 @@ static inline void rope_tables_rows_ms(float* cs, float* sn, const int* row_pos,
 /* launch_attn_m (bruce.cu:3942; calls :7729, :7732, :7958) with the merge folded in */
 static inline void launch_attn_m(float* out, const float* q, const uint8_t* kvk, const uint8_t* kvv,
                                  const int* pos, float* part, int rows, int /*ns*/, int is_swa, cudaStream_t st) {
-    if (rows == 1)      BATTN_CK(battn_decode(g_battn, out, q, kvk, kvv, pos, nullptr, nullptr, part, 1, is_swa, st));
-    else if (rows <= 8) BATTN_CK(battn_verify(g_battn, out, q, kvk, kvv, pos, nullptr, nullptr, part, rows, 1, is_swa, st));
-    else                BATTN_CK(battn_prefill(g_battn, out, q, kvk, kvv, pos, part, rows, is_swa, st));
+    /* battn_verify shares one KV sweep among at most 32 (row, head) pairs per KV head; geometries with more
+     * than 4 query heads per KV head reach that limit before 8 rows and take the prompt-chunk path instead */
+    const int group = g_battn_group;
+    if (rows == 1)                             BATTN_CK(battn_decode(g_battn, out, q, kvk, kvv, pos, nullptr, nullptr, part, 1, is_swa, st));
+    else if (rows <= 8 && rows * group <= 32)  BATTN_CK(battn_verify(g_battn, out, q, kvk, kvv, pos, nullptr, nullptr, part, rows, 1, is_swa, st));
+    else                                       BATTN_CK(battn_prefill(g_battn, out, q, kvk, kvv, pos, part, rows, is_swa, st));
 }
 
 /* launch_attn_ms (bruce.cu:4158; call :7720) with the merge folded in */

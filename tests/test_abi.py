@@ -79,8 +79,39 @@ def test_reference_shim_header_compiles():
             f.write('#include "battn_bruce_shim.h"\n'
                     "void use(float* o, const float* q, const uint8_t* k, const uint8_t* v, const int* p, float* part,\n"
                     "         cudaStream_t st) { launch_attn_m(o, q, k, v, p, part, 1, 56, 0, st);\n"
-                    "  launch_attn_ms(o, q, k, v, p, p, p, part, 8, 7, 1, st); launch_attn_exact(o, q, k, v, p, part, 4, 8, 0, st); }\n")
+                    "  launch_attn_ms(o, q, k, v, p, p, p, part, 8, 7, 1, st); launch_attn_exact(o, q, k, v, p, part, 4, 8, 0, st);\n"
+                    "  launch_attn_m(o, q, k, v, p, part, 8, 28, 0, st); launch_attn_m(o, q, k, v, p, part, 512, 2, 1, st); }\n")
         r = subprocess.run([nvcc, "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-I",
                             os.path.join(ROOT, "include"), "-c", src, "-o", os.path.join(d, "shim_check.o")],
                            capture_output=True, text=True)
         assert r.returncode == 0, r.stderr
+
+
+def test_workspace_covers_every_shorter_call():
+    """battn_workspace_bytes(n_seq, R) must serve calls of 1..R rows: a prompt's last chunk is shorter than the
+    chunk `part` was sized for, and shorter chunks take MORE key splits.  battn_call_workspace_bytes is the
+    per-shape need on a device with the given SM count; the handle-based size is its maximum over r <= R (the
+    maximisation itself runs in tests/test_gpu_prefill.py, which has a handle); here the handle-free function is
+    checked for the shapes that once overflowed."""
+    lib = capi.load()
+    for geom, sms in ((G_R, 148), (G_B, 148), (G_B, 132)):
+        cg = capi.CGeom(geom.n_head, geom.n_kv, geom.head_dim, geom.window, 65536, 1, geom.q_dtype, geom.out_dtype, 0.0)
+        need = {}
+        for r in range(1, 513):
+            n = C.c_size_t()
+            assert lib.battn_call_workspace_bytes(C.byref(cg), sms, 1, r, C.byref(n)) == capi.OK
+            need[r] = n.value
+        rec = (geom.head_dim + 2) * 4 * geom.n_head
+        # a prompt chunk of r rows with s key splits writes r * s records of n_head * (HD + 2) floats
+        for r in (40, 96, 160, 192, 384, 512):
+            if r * geom.group > 32:
+                assert need[r] % (r * rec) == 0 and 1 <= need[r] // (r * rec) <= 8
+        # the shapes of the old overflow: a 512-row buffer sized by its own split count alone is too small
+        worst = max(need.values())
+        assert worst >= need[512]
+        if geom is G_R:
+            assert max(need[r] for r in range(147, 385)) > need[512]
+    bad = C.c_size_t()
+    cg = capi.CGeom(32, 8, 128, 4096, 8192, 1, 1, 1, 0.0)
+    assert lib.battn_call_workspace_bytes(C.byref(cg), 0, 1, 1, C.byref(bad)) == capi.ERR_ARG
+    assert lib.battn_call_workspace_bytes(C.byref(cg), 148, 1, 513, C.byref(bad)) == capi.ERR_CAPACITY

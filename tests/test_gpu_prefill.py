@@ -97,3 +97,48 @@ def test_prefill_matches_exact_device_path_at_depth():
         torch.cuda.synchronize()
         assert_close(to_np(out), to_np(ref), f"prefill at depth swa={is_swa}", head_tol=PROMPT_HEAD_REL_TOL)
     assert eng.device_status() == 0
+
+
+@pytest.mark.parametrize("name", ["R", "B"])
+def test_scratch_sized_for_512_rows_serves_every_shorter_chunk(name):
+    """`part` is allocated once for the longest chunk (MBUF rows, bruce.cu:1058-1066, 5564) and reused for a prompt's
+    shorter last chunk.  Shorter chunks take MORE key splits, so their split records can outgrow those of the
+    512-row chunk: the size battn_workspace_bytes reports must cover them all.  A guard region behind the buffer
+    must stay untouched, and the results must still match the exact path."""
+    import ctypes as C
+
+    from bruce_engine_b200 import capi
+    from bruce_engine_b200.engine import AttnEngine
+    depth = 4096
+    g = _geom(name, slot_ctx=depth + 512, window=1024)
+    eng = AttnEngine(g)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    size = eng.workspace_bytes(1, 512)
+    cg = capi.CGeom(g.n_head, g.n_kv, g.head_dim, g.window, g.slot_ctx, g.n_slots, g.q_dtype, g.out_dtype, 0.0)
+    for r in range(1, 513):
+        n = C.c_size_t()
+        assert eng.lib.battn_call_workspace_bytes(C.byref(cg), sms, 1, r, C.byref(n)) == capi.OK
+        assert n.value <= size, f"a {r}-row call needs {n.value} B, the 512-row buffer has {size} B"
+    guard = 1 << 20
+    buf = torch.full((size + guard,), 0xA5, dtype=torch.uint8, device="cuda")
+    part = buf[:size]
+    gen = torch.Generator(device="cuda"); gen.manual_seed(17)
+    kvk, kvv = eng.alloc_kv_layer(False)
+    pos = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for a in range(0, depth + 512, 512):
+        kk = torch.randn((1, 512, g.n_kv, g.head_dim), generator=gen, device="cuda")
+        vv = torch.randn((1, 512, g.n_kv, g.head_dim), generator=gen, device="cuda")
+        pos.fill_(a)
+        eng.qkv_prep_store(kk, vv, kvk, kvv, pos, rows=512)
+    pos.fill_(depth)
+    for rows in (96, 160, 192, 384, 512):
+        q = torch.randn((1, rows, g.n_head, g.head_dim), generator=gen, device="cuda").to(eng.q_torch)
+        out = new_out(eng, 1, rows, g.n_head, g.head_dim)
+        eng.launch_attn_m(out, q, kvk, kvv, pos, part, rows, False)
+        ref = torch.empty_like(out)
+        ws = torch.empty(eng.exact_workspace_bytes(1, rows, 4), dtype=torch.uint8, device="cuda")
+        eng.attn_exact(ref, q, kvk, kvv, pos, ws, 1, rows, 4, False)
+        torch.cuda.synchronize()
+        assert bool((buf[size:] == 0xA5).all()), f"a {rows}-row chunk wrote past the end of the scratch buffer"
+        assert_close(to_np(out), to_np(ref), f"{name} {rows}-row chunk on the 512-row scratch", head_tol=PROMPT_HEAD_REL_TOL)
+    assert eng.device_status() == 0

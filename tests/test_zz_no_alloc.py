@@ -12,7 +12,8 @@ import pytest
 import torch
 
 from tests.gpu_util import dev_i32, gpu_fill, new_out, to_np
-from tests.util import assert_close, draw_qkv
+from oracle import oracle as O
+from tests.util import assert_close, draw_qkv, oracle_fill, oracle_geom
 
 pytestmark = pytest.mark.gpu
 
@@ -28,11 +29,15 @@ def test_noalloc_decode_matches_decode_on_two_consecutive_calls():
     g = G_B.with_(slot_ctx=4096, window=512, n_slots=3)
     eng = AttnEngine(g)
     lens = [4096, 777, 65]
+    og = oracle_geom(g)
+    okvk, okvv = {}, {}
     for is_swa in (False, True):
         kvk, kvv = eng.alloc_kv_layer(is_swa, fill=0)
+        okvk[is_swa], okvv[is_swa] = O.new_cache(og, is_swa), O.new_cache(og, is_swa)
         for s, n in enumerate(lens):
             _, k, v = draw_qkv(g, n, 1, seed=300 + s)
             gpu_fill(eng, k, v, kvk, kvv, is_swa, slot=s)
+            oracle_fill(og, k, v, is_swa, slot=s, kvk=okvk[is_swa], kvv=okvv[is_swa])
         rng = np.random.default_rng(8)
         q = torch.from_numpy(rng.standard_normal((3, 1, g.n_head, g.head_dim), dtype=np.float32)).cuda().half()
         part = eng.alloc_part(3, 1)
@@ -55,6 +60,11 @@ def test_noalloc_decode_matches_decode_on_two_consecutive_calls():
             assert rc == capi.OK
             torch.cuda.synchronize()
             assert_close(to_np(got), to_np(want), f"noalloc vs decode swa={is_swa} n_seq={n_seq}")
+            # ... and against the CPU oracle, so that this is not only a comparison of the library with itself
+            sl = [int(x) for x in kslot.cpu()]
+            ref = O.attend(og, to_np(qq), okvk[is_swa], okvv[is_swa], [int(x) for x in pos.cpu()], kslot=sl, rows=1,
+                           is_swa=is_swa)
+            assert_close(to_np(got), ref, f"noalloc vs oracle swa={is_swa} n_seq={n_seq}")
     assert eng.device_status() == 0
 
 
