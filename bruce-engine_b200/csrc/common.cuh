@@ -66,6 +66,14 @@ __device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
     return *reinterpret_cast<const uint32_t*>(&r);
 }
 
+// a * b - p with one rounding, p = the fp16-rounded product a * b: the exact rounding error of that product
+// (an 8-bit integer times an 11-bit scale has 19 significant bits; the residual fits fp16 exactly)
+__device__ __forceinline__ uint32_t hfma2_residual(uint32_t a, uint32_t b, uint32_t p) {
+    const __half2 r = __hfma2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b),
+                              __hneg2(*reinterpret_cast<const __half2*>(&p)));
+    return *reinterpret_cast<const uint32_t*>(&r);
+}
+
 __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
     const __half2 r = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&r);

@@ -12,15 +12,19 @@
 //   warps 8-11  K dequant: raw q8_0 records -> fp16 K operand [key][dim], scale folded in
 //   warps 12-15 V dequant: raw q8_0 records -> fp16 V^T operand [dim][key], scale folded in
 //   warp 16     issues the S MMAs, warp 19 the P.V MMAs;  warps 17/18 stream raw K / V tiles with bulk copies
-// Data flow per key tile j (every ring below is four deep and indexed j mod 4):
+// Data flow per key tile j (every ring below is three deep and indexed j mod 3):
 //   loader -> raw K/V tile (shared memory) -> dequant -> fp16 operand (128-byte-swizzled shared memory)
-//   S_j = Q K_j^T     Q lives in tensor memory (the A operand), S_j in one of four 64-column buffers
+//   K operand         two fp16 parts per value: hi = fp16(d*x) and lo = d*x - hi (exact: the product of an int8
+//                     and an fp16 scale has 19 significant bits, fp16 keeps 11, the rest fits the second part),
+//                     so S carries no rounding of K -- a single folded operand alone moves single (row, head)
+//                     outputs by up to 7e-4 relative, most of the 1e-3 budget
+//   S_j = Q K_hi^T + Q K_lo^T   Q lives in tensor memory (the A operand), S_j in one of three 64-column buffers
 //   softmax           the owning group reads S_j once into registers, takes the row maximum, and writes
 //                     P_j = 2^(S_j*c - ref) as fp16 pairs over the first half of the same buffer
 //   O += P_j [V_j | 1]  P_j is the tensor-memory A operand; sixteen rows of ones appended to the V^T
 //                     operand make the same MMA accumulate sum(P) in fp32 next to O, from exactly the
 //                     fp16-rounded P it multiplies with V
-// The S issuer runs up to four tiles ahead of O, so when a softmax group finishes tile j, S_{j+2} is ready;
+// The S issuer runs up to three tiles ahead of O, so when a softmax group finishes tile j, S_{j+2} is ready;
 // the two groups run half a tile apart, which lets one group's exponentials (the special-function pipe)
 // overlap the other group's loads, maxima and stores.
 // The row reference `ref` (a lazily updated running maximum, bruce.cu:3034-3060 in spirit) is shared by
@@ -40,7 +44,14 @@ namespace pf128 {
 
 using namespace pf;
 
-constexpr int HD = 128, BN = 64, NB = 4;               // NB: depth of every ring (raw tiles, operands, S/P)
+#ifndef BATTN_PF_NB
+#define BATTN_PF_NB 3
+#endif
+#ifndef BATTN_PF_KLO
+#define BATTN_PF_KLO 1
+#endif
+constexpr int HD = 128, BN = 64, NB = BATTN_PF_NB;     // NB: depth of every ring (raw tiles, operands, S/P)
+constexpr bool KLO = BATTN_PF_KLO != 0;
 constexpr int NBLK = HD / 32, REC = HD + 2 * NBLK;
 constexpr int NTHREADS = 640;
 constexpr int W_KDQ = 8, W_VDQ = 12, W_MMA = 16, W_LDK = 17, W_LDV = 18, W_PV = 19;
@@ -51,8 +62,9 @@ constexpr int VROWS = HD + 16;                         // V^T operand rows: head
 constexpr int K_BYTES = BN * HD * 2;                   // two 64-dim sub-tiles of [64 keys][128 B]
 constexpr int V_BYTES = VROWS * 128;                   // [144 rows][64 keys] fp16
 constexpr int RAW_BYTES = BN * REC;
-constexpr int OFF_K = 0;
-constexpr int OFF_V = OFF_K + NB * K_BYTES;
+constexpr int OFF_K = 0;                                // K operand, high part: fp16(d * x)
+constexpr int OFF_KLO = OFF_K + NB * K_BYTES;           // K operand, low part: fp16(d * x - high part), exact
+constexpr int OFF_V = OFF_KLO + (KLO ? NB * K_BYTES : 0);
 constexpr int OFF_RAWK = OFF_V + NB * V_BYTES;
 constexpr int OFF_RAWV = OFF_RAWK + NB * RAW_BYTES;
 constexpr int OFF_BAR = OFF_RAWV + NB * RAW_BYTES;
@@ -66,7 +78,7 @@ static_assert(K_BYTES % 1024 == 0 && V_BYTES % 1024 == 0 && RAW_BYTES % 16 == 0,
 
 constexpr int T_O = 0;                                  // tensor-memory columns
 constexpr int T_L = HD;                                 // 16 columns, each = sum of P
-constexpr int T_S = HD + 32;                            // four S/P buffers of BN columns
+constexpr int T_S = HD + 32;                            // NB S/P buffers of BN columns
 constexpr int T_Q = T_S + NB * BN;                      // HD/2 columns of fp16 pairs
 static_assert(T_Q + HD / 2 <= TMEM_COLS, "tensor memory budget");
 
@@ -74,6 +86,7 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill_hd128(const Params P) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);      // 1024-byte aligned
     uint8_t* Ksm = smem + OFF_K;
+    uint8_t* Klo = smem + OFF_KLO;
     uint8_t* Vsm = smem + OFF_V;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
     volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(smem + OFF_MISC);
@@ -188,7 +201,7 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill_hd128(const Params P) {
         }
     };
     // ring slot and phase parity of tile j
-    auto slot = [](int j) { return j & (NB - 1); };
+    auto slot = [](int j) { return j % NB; };
     auto phase = [](int j) { return (uint32_t)((j / NB) & 1); };
 
     const size_t hb = (size_t)kvh * P.pstride * (size_t)REC;
@@ -200,16 +213,22 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill_hd128(const Params P) {
             // Runs ahead of the P.V issuer as far as the rings allow: S of tile j refills the buffer whose P
             // the P.V MMA of tile j-NB has consumed.
             const uint32_t idS = umma_idesc(128, BN);
-            const uint64_t kd0 = umma_desc(smem_u32(Ksm));
+            const uint64_t kd0 = umma_desc(smem_u32(Ksm)), kl0 = umma_desc(smem_u32(Klo));
             for (int j = 0; j < n_tiles; ++j) {
                 wait(B_KF + slot(j), phase(j), 20);
                 if (j >= NB) wait(B_PV + slot(j), phase(j - NB), 20);
                 tc_fence_after();
                 const uint32_t d = tmem + T_S + slot(j) * BN;
                 const uint64_t kd = kd0 + (uint64_t)(slot(j) * (K_BYTES >> 4));
+                const uint64_t kl = kl0 + (uint64_t)(slot(j) * (K_BYTES >> 4));
+                // S = Q K_hi^T + Q K_lo^T: the two fp16 parts add up to the exact product d * x of every cached
+                // value, so the scores carry no rounding of the K operand
 #pragma unroll
                 for (int ks = 0; ks < HD / 16; ++ks)
                     umma_f16_ts(d, tmem + T_Q + 8 * ks, kd + (uint64_t)((ks >> 2) * ((BN * 128) >> 4) + 2 * (ks & 3)), idS, ks > 0);
+#pragma unroll
+                for (int ks = 0; KLO && ks < HD / 16; ++ks)
+                    umma_f16_ts(d, tmem + T_Q + 8 * ks, kl + (uint64_t)((ks >> 2) * ((BN * 128) >> 4) + 2 * (ks & 3)), idS, 1u);
                 umma_commit(&bars[B_S + slot(j)]);
             }
         } else if (warp == W_PV && lane == 0) {
@@ -233,7 +252,7 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill_hd128(const Params P) {
             uint8_t* ring = smem + (isv ? OFF_RAWV : OFF_RAWK);
             const int full = isv ? B_VRAW_FULL : B_KRAW_FULL, free_ = isv ? B_VRAW_FREE : B_KRAW_FREE;
             for (int j = 0; j < n_tiles; ++j) {
-                if (j >= NB) wait(free_ + slot(j), phase(j - NB), 200);         // the dequant group left it (no hurry: the ring is four deep)
+                if (j >= NB) wait(free_ + slot(j), phase(j - NB), 200);         // the dequant group left it (no hurry: the ring is three deep)
                 const int sp = ((tile_first + j) * BN) & P.ring_mask;
                 const int nk = min(BN, P.pstride - sp);
                 const uint32_t bytes = (uint32_t)nk * REC;
@@ -315,6 +334,7 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill_hd128(const Params P) {
             // the S MMA that last read this K buffer (tile j - NB) must be complete
             if (j >= NB) wait(B_S + slot(j), phase(j - NB), 50);
             uint8_t* Kdst = Ksm + slot(j) * K_BYTES + sub * (BN * 128);
+            uint8_t* Ldst = Klo + slot(j) * K_BYTES + sub * (BN * 128);
 #pragma unroll
             for (int blk = 0; blk < 2; ++blk) {
                 const __half sc = reinterpret_cast<const __half*>(src)[2 * sub + blk];
@@ -325,12 +345,15 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill_hd128(const Params P) {
                     const int ch = 4 * blk + c;                 // 16-byte chunk inside the sub-tile row
                     const uint2 w = *reinterpret_cast<const uint2*>(src + 2 * NBLK + (8 * sub + ch) * 8);
                     const uint32_t x = w.x ^ 0x80808080u, y = w.y ^ 0x80808080u;
-                    uint4 o;
-                    o.x = hmul2_u32(sub1152(widen_lo(x)), su);
-                    o.y = hmul2_u32(sub1152(widen_hi(x)), su);
-                    o.z = hmul2_u32(sub1152(widen_lo(y)), su);
-                    o.w = hmul2_u32(sub1152(widen_hi(y)), su);
+                    const uint32_t i0 = sub1152(widen_lo(x)), i1 = sub1152(widen_hi(x));
+                    const uint32_t i2 = sub1152(widen_lo(y)), i3 = sub1152(widen_hi(y));
+                    uint4 o, r;
+                    o.x = hmul2_u32(i0, su); r.x = hfma2_residual(i0, su, o.x);
+                    o.y = hmul2_u32(i1, su); r.y = hfma2_residual(i1, su, o.y);
+                    o.z = hmul2_u32(i2, su); r.z = hfma2_residual(i2, su, o.z);
+                    o.w = hmul2_u32(i3, su); r.w = hfma2_residual(i3, su, o.w);
                     *reinterpret_cast<uint4*>(Kdst + sw128(krow, ch)) = o;
+                    if (KLO) *reinterpret_cast<uint4*>(Ldst + sw128(krow, ch)) = r;
                 }
             }
             proxy_fence();
@@ -469,6 +492,14 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill_hd128(const Params P) {
             if (lane == 0) mbar_arrive(&bars[B_P + slot(j)]);
         }
         // ---- epilogue: O / sum(P) -> global; each of the two threads of a row writes half of it ----------
+        // A parity wait on phase k of a barrier is only meaningful once phase k-1 is known to be complete (before
+        // that it is satisfied at once).  The group that did not own the last tile therefore first waits for the
+        // P.V product of its OWN last tile -- whose predecessor in that ring slot completed before this group was
+        // handed the tile's scores -- and only then for the last tile's.
+        {
+            const int own_last = n_tiles - 1 - ((n_tiles - 1 - grp) & 1);
+            if (own_last >= 0 && own_last != n_tiles - 1) wait(B_PV + slot(own_last), phase(own_last), 50);
+        }
         wait(B_PV + slot(n_tiles - 1), phase(n_tiles - 1), 50);
         tc_fence_after();
         const float l = __uint_as_float(tmem_ld1(tmem + lane_base + T_L));
