@@ -15,8 +15,11 @@
 //   * A loader thread streams raw K and V tiles (64 records each, one contiguous run per tile because the
 //     cache is head-major) with cp.async.bulk into a two-stage ring.
 //   * Two groups of four dequant warps (K and V in parallel) turn raw q8_0 records into fp16 operands in
-//     128-byte-swizzled K-major shared memory, double-buffered: K as [key][dim], V transposed to [dim][key]
-//     with byte-permute interleaves, scale folded in.
+//     128-byte-swizzled K-major shared memory: K as [key][dim] in two fp16 parts, hi = fp16(d*x) and
+//     lo = d*x - hi (exact), so that S carries no rounding of the K operand (a single folded operand alone moves
+//     single (row, head) outputs by up to 7e-4 relative); V transposed to [dim][key] with byte-permute
+//     interleaves, scale folded in, double-buffered.  The K buffers hold one 128-dim half of the tile each and
+//     are refilled half by half as the S MMAs release them.
 //   * S = Q K^T (M 128, N 64, K head_dim) and O += P V (M 128, N head_dim, K 64) run as tcgen05.mma with
 //     fp32 accumulators in tensor memory, issued by two threads (one per product) so that neither waits on
 //     the other's barriers.  Q is the tensor-memory A operand of the first product, P of the second; the
@@ -79,7 +82,12 @@ struct Cfg {
     static constexpr int KV_BUFS = 2;
     static constexpr int RAW_STAGES = 2;
     static constexpr int Q_BYTES = Q_TMEM ? 0 : 128 * HD * 2;
-    static constexpr int K_BYTES = BN * HD * 2;
+    // K operand: two buffers, one per 128-dim half of the head, each holding that half of the current tile twice:
+    // hi = fp16(d * x) and lo = d * x - hi (exact), 16 KB each.  (Not double-buffered across tiles: the dequant
+    // of half h of tile j+1 starts as soon as the S MMAs over half h of tile j have completed.)
+    static constexpr int K_PART_BYTES = BN * 128 * 2;          // [BN keys][128 dims] fp16 = two 64-dim sub-tiles
+    static constexpr int K_HALF_BYTES = 2 * K_PART_BYTES;      // hi + lo
+    static constexpr int K_BYTES = BN * HD * 2;                // KV_BUFS * K_BYTES == 2 * K_HALF_BYTES
     static constexpr int V_BYTES = HD * BN * 2;
     static constexpr int RAW_BYTES = BN * REC;              // one raw K (or V) tile
     static constexpr int OFF_Q = 0;
@@ -89,7 +97,7 @@ struct Cfg {
     static constexpr int OFF_ONES = OFF_V + KV_BUFS * V_BYTES;
     static constexpr int OFF_RAW = OFF_ONES + ONES_BYTES;    // [RAW_STAGES buffers][K | V]
     static constexpr int OFF_BAR = OFF_RAW + RAW_STAGES * 2 * RAW_BYTES;
-    static constexpr int N_BARS = 16;
+    static constexpr int N_BARS = 18;
     static constexpr int OFF_MISC = OFF_BAR + N_BARS * 8;    // tmem base, abort flag
     static constexpr int OFF_RMAX = OFF_MISC + 16;           // [tile parity][2 halves][128 rows] row maxima
     static constexpr int TOTAL = OFF_RMAX + 2 * 2 * 128 * 4 + 1024;   // + slack to align the base to 1024
@@ -100,14 +108,15 @@ struct Cfg {
     static constexpr int T_Q = T_S1 + BN;                    // HD/2 columns of fp16 pairs
     static_assert(T_Q + HD / 2 <= TMEM_COLS, "tensor memory budget");
     static_assert(RAW_BYTES % 16 == 0, "bulk copy size");
-    static_assert((HD == 128 && BN == 128) || (HD == 256 && BN == 64), "supported tile shapes");
+    static_assert(HD == 256 && BN == 64 && KV_BUFS == 2, "supported tile shape");
     static_assert(TOTAL <= 226 * 1024, "shared memory budget");
 };
 
 // barrier indices
 // every role-to-role barrier exists twice and alternates with the tile parity, so that no role can complete
 // two phases of a barrier before its waiter has observed the first
-enum { B_RAW_FULL0 = 0, B_RAW_FREE0 = 3, B_KF0 = 6, B_VF0 = 8, B_S0 = 10, B_P0 = 12, B_PV0 = 14 };
+// (B_KF0 + h and B_KFREE0 + h are indexed by the 128-dim half h of the K operand instead and complete once per tile)
+enum { B_RAW_FULL0 = 0, B_RAW_FREE0 = 3, B_KF0 = 6, B_VF0 = 8, B_S0 = 10, B_P0 = 12, B_PV0 = 14, B_KFREE0 = 16 };
 
 // byte offset of 16-byte chunk `chunk` (0..7) of row `row` inside a [rows x 64 halves] sub-tile stored
 // K-major with the 128-byte swizzle (8-row atoms of 1024 B, chunk index XOR row-in-atom)
@@ -281,7 +290,8 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill(const Params P) {
             mbar_init(&bars[B_RAW_FREE0 + st], 2 * NDEQ / 32);
         }
         for (int par = 0; par < 2; ++par) {
-            mbar_init(&bars[B_KF0 + par], NDEQ / 32); mbar_init(&bars[B_VF0 + par], NDEQ / 32);
+            mbar_init(&bars[B_KF0 + par], NDEQ / 64); mbar_init(&bars[B_VF0 + par], NDEQ / 32);
+            mbar_init(&bars[B_KFREE0 + par], 1);
             mbar_init(&bars[B_S0 + par], 1); mbar_init(&bars[B_PV0 + par], 1);
             mbar_init(&bars[B_P0 + par], NSOFT / 32);
         }
@@ -377,22 +387,24 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill(const Params P) {
         // the critical path.  S of tile j+1 refills the buffer whose P the P.V MMA of tile j-1 consumed.
         if (lane == 0) {
             const uint32_t idS = umma_idesc(128, BN);
-            const uint32_t qa = smem_u32(Qsm), ka = smem_u32(Ksm);
+            const uint32_t ka = smem_u32(Ksm);
             for (int j = 0; j < n_tiles; ++j) {
-                wait(B_KF0 + (j & 1), (j >> 1) & 1);
                 if (j >= 2) wait(B_PV0 + (j & 1), ((j - 2) >> 1) & 1);
-                tc_fence_after();
                 const uint32_t d = tmem + ((j & 1) ? C::T_S1 : C::T_S0);
-                const uint32_t kb = ka + (j % C::KV_BUFS) * C::K_BYTES;
 #pragma unroll
-                for (int ks = 0; ks < HD / 16; ++ks) {
-                    const uint64_t b = umma_desc(kb + (ks >> 2) * (BN * 128)) + 2 * (ks & 3);
-                    if constexpr (C::Q_TMEM) {
-                        umma_f16_ts(d, tmem + C::T_Q + 8 * ks, b, idS, ks > 0);
-                    } else {
-                        const uint64_t a = umma_desc(qa + (ks >> 2) * (128 * 128)) + 2 * (ks & 3);
-                        umma_f16(d, a, b, idS, ks > 0);
-                    }
+                for (int hf = 0; hf < 2; ++hf) {
+                    wait(B_KF0 + hf, j & 1);
+                    tc_fence_after();
+                    // S += Q_half K_hi^T + Q_half K_lo^T: the two fp16 parts add up to the exact product d * x of
+                    // every cached value, so the scores carry no rounding of the K operand
+#pragma unroll
+                    for (int part = 0; part < 2; ++part)
+#pragma unroll
+                        for (int ks = 0; ks < 8; ++ks) {
+                            const uint64_t b = umma_desc(ka + hf * C::K_HALF_BYTES + part * C::K_PART_BYTES + (ks >> 2) * (BN * 128)) + 2 * (ks & 3);
+                            umma_f16_ts(d, tmem + C::T_Q + 8 * (8 * hf + ks), b, idS, (hf | part | ks) != 0);
+                        }
+                    umma_commit(&bars[B_KFREE0 + hf]);          // the dequant warps may refill this half
                 }
                 umma_commit(&bars[B_S0 + (j & 1)]);
             }
@@ -508,38 +520,41 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill(const Params P) {
         // ======================= K dequant warps: K operand, [key][dim] ==============================
         regs_shrink<REGS_DEQ>();
         const int t = tid - NSOFT;
-        const int krow = t & (BN - 1);                          // each thread converts KCH chunks of one row
-        constexpr int KCH = (BN * HD / 8) / NDEQ;
-        const int kch0 = (t / BN) * KCH;
+        const int krow = t & (BN - 1);                          // each thread converts one 128-dim half of one row
+        const int hf = t / BN;                                  // which half: warps 0-1 -> dims 0..127, warps 2-3 -> 128..255
         const int kkey = kappa(krow);
         for (int j = 0; j < n_tiles; ++j) {
             const int b = j % C::RAW_STAGES;
             const uint8_t* Kraw = RAW + b * 2 * C::RAW_BYTES;
             wait(B_RAW_FULL0 + b, (j / C::RAW_STAGES) & 1);
-            // the S MMA that last read this K buffer (tile j - KV_BUFS) must be complete
-            if (j >= C::KV_BUFS) wait(B_S0 + ((j - C::KV_BUFS) & 1), ((j - C::KV_BUFS) >> 1) & 1);
-            uint8_t* Kdst = Ksm + (j % C::KV_BUFS) * C::K_BYTES;
+            // the S MMAs over this half of tile j - 1 must be complete before the buffer is refilled
+            if (j >= 1) wait(B_KFREE0 + hf, (j - 1) & 1);
+            uint8_t* Kdst = Ksm + hf * C::K_HALF_BYTES;
             {
                 const uint8_t* src = Kraw + kkey * REC;
 #pragma unroll 2
-                for (int c = 0; c < KCH; ++c) {
-                    const int ch = kch0 + c;
+                for (int c = 0; c < 16; ++c) {
+                    const int ch = 16 * hf + c;                 // 16-byte chunk of the fp16 row (8 dims)
                     const __half sc = reinterpret_cast<const __half*>(src)[ch >> 2];
                     const __half2 s2 = __half2half2(sc);
                     const uint32_t su = *reinterpret_cast<const uint32_t*>(&s2);
                     const uint2 w = *reinterpret_cast<const uint2*>(src + 2 * NBLK + ch * 8);
                     const uint32_t x = w.x ^ 0x80808080u, y = w.y ^ 0x80808080u;
-                    uint4 o;
-                    o.x = hmul2_u32(sub1152(widen_lo(x)), su);
-                    o.y = hmul2_u32(sub1152(widen_hi(x)), su);
-                    o.z = hmul2_u32(sub1152(widen_lo(y)), su);
-                    o.w = hmul2_u32(sub1152(widen_hi(y)), su);
-                    *reinterpret_cast<uint4*>(Kdst + (ch >> 3) * (BN * 128) + sw128(krow, ch & 7)) = o;
+                    const uint32_t i0 = sub1152(widen_lo(x)), i1 = sub1152(widen_hi(x));
+                    const uint32_t i2 = sub1152(widen_lo(y)), i3 = sub1152(widen_hi(y));
+                    uint4 o, r;
+                    o.x = hmul2_u32(i0, su); r.x = hfma2_residual(i0, su, o.x);
+                    o.y = hmul2_u32(i1, su); r.y = hfma2_residual(i1, su, o.y);
+                    o.z = hmul2_u32(i2, su); r.z = hfma2_residual(i2, su, o.z);
+                    o.w = hmul2_u32(i3, su); r.w = hfma2_residual(i3, su, o.w);
+                    const uint32_t off = (c >> 3) * (BN * 128) + sw128(krow, c & 7);
+                    *reinterpret_cast<uint4*>(Kdst + off) = o;
+                    *reinterpret_cast<uint4*>(Kdst + C::K_PART_BYTES + off) = r;
                 }
             }
             proxy_fence();
             __syncwarp();
-            if (lane == 0) { mbar_arrive(&bars[B_KF0 + (j & 1)]); mbar_arrive(&bars[B_RAW_FREE0 + b]); }
+            if (lane == 0) { mbar_arrive(&bars[B_KF0 + hf]); mbar_arrive(&bars[B_RAW_FREE0 + b]); }
         }
     } else {
         // ======================= softmax warps: two threads per accumulator row ========================
@@ -659,9 +674,14 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill(const Params P) {
                 for (int i = 0; i < 32; i += 2) {
                     float e0, e1;
                     ffma2(e0, e1, __uint_as_float(v[c][i]), __uint_as_float(v[c][i + 1]), c2p, nbp);
-                    const float p0 = fast_exp2(e0), p1 = fast_exp2(e1);
-                    if constexpr (!C::L_MMA) l_part += p0 + p1;
-                    pk[i >> 1] = pack_h2(p0, p1);
+                    const uint32_t ph = pack_h2(fast_exp2(e0), fast_exp2(e1));
+                    if constexpr (!C::L_MMA) {
+                        // the denominator sums the fp16-rounded weights the MMA multiplies with V, so that
+                        // out = sum(p v) / sum(p) stays a convex combination of the V rows
+                        const float2 pf = __half22float2(*reinterpret_cast<const __half2*>(&ph));
+                        l_part += pf.x + pf.y;
+                    }
+                    pk[i >> 1] = ph;
                 }
                 tmem_st16(tS + c * 16, pk);
             }

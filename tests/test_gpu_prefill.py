@@ -1,5 +1,4 @@
-"""Parity of the tcgen05 prompt-chunk kernel with the CPU oracle (tolerances: tests/util.py; this path
-has its own per-(row, head) bound, explained there).  A prompt is processed the way the reference does it (bruce.cu:7665-7737): for
+"""Parity of the tcgen05 prompt-chunk kernels with the CPU oracle (tolerances: tests/util.py).  A prompt is processed the way the reference does it (bruce.cu:7665-7737): for
 each chunk, append the chunk's K/V rows, then attend the chunk's query rows against the cache."""
 import numpy as np
 import pytest
@@ -13,8 +12,11 @@ pytestmark = pytest.mark.gpu
 
 
 def _geom(name, **kw):
-    from bruce_engine_b200.layout import G_B, G_R
-    return (G_B if name == "B" else G_R).with_(**kw)
+    """"B": the graded geometry (fp16 q and out); "B32": the same with fp32 outputs, where the max-norm ratio is
+    gated as well (tests/util.py); "R": the reference's own geometry (fp32 q and out)."""
+    from bruce_engine_b200.layout import F32, G_B, G_R
+    base = {"B": G_B, "B32": G_B.with_(out_dtype=F32), "R": G_R}[name]
+    return base.with_(**kw)
 
 
 def _run_prompt(name, n_prompt, chunk, is_swa, window, seed, check_chunks=None):
@@ -49,14 +51,14 @@ def _run_prompt(name, n_prompt, chunk, is_swa, window, seed, check_chunks=None):
     return worst
 
 
-@pytest.mark.parametrize("name", ["B", "R"])
+@pytest.mark.parametrize("name", ["B", "B32", "R"])
 @pytest.mark.parametrize("is_swa", [False, True])
 def test_chunked_prompt_small(name, is_swa):
     """Ragged sizes: prompt not a multiple of the chunk, chunk not a multiple of the M tile."""
     _run_prompt(name, n_prompt=700, chunk=200, is_swa=is_swa, window=256, seed=21)
 
 
-@pytest.mark.parametrize("name", ["B", "R"])
+@pytest.mark.parametrize("name", ["B", "B32", "R"])
 def test_single_small_chunks(name):
     """Chunks of 9..40 rows (one partial M tile) at position 0 and deeper."""
     for rows, n0 in ((9, 0), (33, 0), (40, 300), (31, 129)):
@@ -68,6 +70,15 @@ def test_prompt_4k_in_512_row_chunks(is_swa):
     """BASELINE config 2 at reduced length: 512-row chunks against a growing cache, window 1024 so
     that later chunks exercise the sliding window; all rows of chunks 0, 3 and 7 are checked."""
     _run_prompt("B", n_prompt=4096, chunk=512, is_swa=is_swa, window=1024, seed=0, check_chunks={0, 3, 7})
+
+
+@pytest.mark.parametrize("name", ["B", "B32"])
+@pytest.mark.parametrize("is_swa", [False, True])
+def test_prompt_16k_config2_full_size(name, is_swa):
+    """BASELINE config 2 at full size: a 16,384-token prompt in 512-row chunks against the growing cache, window
+    4096 on the sliding-window layer; ALL rows of chunks 0, 15 and 31 are compared with the CPU oracle (OpenMP),
+    the other chunks only feed the cache; the cache bytes of the whole prompt must equal the oracle's."""
+    _run_prompt(name, n_prompt=16384, chunk=512, is_swa=is_swa, window=4096, seed=0, check_chunks={0, 15, 31})
 
 
 def test_prefill_matches_exact_device_path_at_depth():

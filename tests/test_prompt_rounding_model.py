@@ -1,24 +1,30 @@
-"""CPU model of the prompt path's operand roundings, the basis of its per-(row, head) tolerance.
+"""CPU model of the prompt path's operand roundings: why its K operand is split into two fp16 parts.
 
-The tensor-core prompt kernel feeds fp16 operands with the q8_0 block scale folded in: K = fp16(q * d),
-V = fp16(q * d), P = fp16(2^(s - ref)); everything else is fp32 or exact.  This test applies exactly
-those three roundings, one at a time and together, to a double-precision causal attention over
-quantised N(0,1) inputs and records how far a single (row, head) softmax can move.  No kernel runs
-here: the figures bound what ANY schedule of that arithmetic can achieve, and the GPU parity tests use
-PROMPT_HEAD_REL_TOL from tests/util.py accordingly."""
+The tensor-core prompt kernels feed fp16 operands.  Folding the q8_0 block scale into ONE fp16 K operand,
+K = fp16(x * d), rounds a 19-bit product to 11 bits; V = fp16(x * d) and P = fp16(2^(s - ref)) are rounded the
+same way; everything else is fp32 or exact.  This test applies those roundings, one at a time and together, to a
+double-precision causal attention over quantised N(0,1) inputs and records how far a single (row, head) softmax
+moves.  No kernel runs here: the figures bound what ANY schedule of that arithmetic can achieve.  They show that
+the folded K operand alone eats most of the 1e-3 budget (with V and P nothing is left), and that
+the split operand K = hi + lo, hi = fp16(x*d), lo = fp16(x*d - hi) -- which reproduces x*d exactly -- brings the
+whole path well inside it."""
 import numpy as np
 
 from oracle import oracle as O
-from tests.util import PROMPT_HEAD_REL_TOL, REL_TOL
+from tests.util import REL_TOL
 
-HD, N, H, HKV = 128, 384, 8, 2
+HD, N, H, HKV = 128, 512, 8, 2
+
+
+def _f16(a):
+    return a.astype(np.float16).astype(np.float64)
 
 
 def _quantised(x):
     """Dequantised values of x through the reference quantiser: (exact double, fp16-folded)."""
     rec = O.np_quant_records(x.reshape(-1, HD))
     exact = O.np_dequant_records(rec, HD).astype(np.float64).reshape(x.shape)
-    return exact, exact.astype(np.float16).astype(np.float64)
+    return exact, _f16(exact)
 
 
 def _attend(q, K, V, round_p):
@@ -29,35 +35,40 @@ def _attend(q, K, V, round_p):
         s = np.where(causal, (q[:, h] @ K[:, kv].T) / np.sqrt(HD), -np.inf)
         p = np.exp(s - s.max(1, keepdims=True))
         if round_p:
-            p = p.astype(np.float16).astype(np.float64)
+            p = _f16(p)
         out[:, h] = (p @ V[:, kv]) / p.sum(1, keepdims=True)
     return out
 
 
-def test_operand_rounding_bounds_the_prompt_path_error():
+def test_operand_rounding_model_of_the_prompt_path():
     rng = np.random.default_rng(0)
-    q = rng.standard_normal((N, H, HD), dtype=np.float32).astype(np.float16).astype(np.float64)
+    q = _f16(rng.standard_normal((N, H, HD), dtype=np.float32))
     k = rng.standard_normal((N, HKV, HD), dtype=np.float32)
     v = rng.standard_normal((N, HKV, HD), dtype=np.float32)
     Kx, K16 = _quantised(k)
     Vx, V16 = _quantised(v)
+    Klo = _f16(Kx - K16)
+    assert np.array_equal(K16 + Klo, Kx), "hi + lo must reproduce the dequantised K exactly"
     ref = _attend(q, Kx, Vx, False)
 
     def worst(o):
         d = o - ref
         head = np.sqrt((d ** 2).sum(-1)) / np.sqrt((ref ** 2).sum(-1))
-        row = np.sqrt((d ** 2).sum((-1, -2))) / np.sqrt((ref ** 2).sum((-1, -2)))
-        return head.max(), row.max()
+        mxn = np.abs(d).max(-1) / np.abs(ref).max(-1)
+        return head.max(), mxn.max()
 
-    k_only, _ = worst(_attend(q, K16, Vx, False))
+    k_only, k_only_mx = worst(_attend(q, K16, Vx, False))
     v_only, _ = worst(_attend(q, Kx, V16, False))
     p_only, _ = worst(_attend(q, Kx, Vx, True))
-    all_head, all_row = worst(_attend(q, K16, V16, True))
-    print(f"[rounding model] per-(row, head): K {k_only:.2e} V {v_only:.2e} P {p_only:.2e} all {all_head:.2e};"
-          f" per row: {all_row:.2e}")
-    # the folded K operand is the largest single source and already takes half of a 1e-3 budget
+    folded, folded_mx = worst(_attend(q, K16, V16, True))
+    split, split_mx = worst(_attend(q, K16 + Klo, V16, True))
+    print(f"[rounding model] per-(row, head) 2-norm: K {k_only:.2e} V {v_only:.2e} P {p_only:.2e}; "
+          f"folded K+V+P {folded:.2e} (max-norm {folded_mx:.2e}); split K, V+P {split:.2e} (max-norm {split_mx:.2e})")
+    # the folded K operand is the largest single source and takes half of the 1e-3 budget on its own
     assert k_only > 4e-4 and k_only > v_only and k_only > p_only
     assert 2e-4 < v_only < 4e-4 and 2e-4 < p_only < 4e-4
-    # all three together: close to 1e-3 per (row, head) on a few thousand softmaxes, well inside the bounds used
-    assert 5e-4 < all_head < PROMPT_HEAD_REL_TOL
-    assert all_row < 0.6 * REL_TOL
+    # all three together leave no margin on a few thousand softmaxes (the worst of the ~500K (row, head) pairs of
+    # a 16K prompt lands at 1.0e-3 .. 1.2e-3); the split operand restores a 1.5x margin
+    assert folded > 0.7 * REL_TOL and folded_mx > 0.7 * REL_TOL
+    assert split < 0.6 * REL_TOL and split_mx < 0.75 * REL_TOL
+    assert split < 0.6 * folded

@@ -5,25 +5,22 @@ import numpy as np
 
 from oracle import oracle as O
 
-# Tolerances of the attention outputs against the double-accumulated oracle:
-#   max-abs  : max |gpu - oracle| over every element                                        <= 2e-3
-#   relative : per token row (all heads: the vector the engine consumes),
-#              ||gpu - oracle||_2 / ||oracle||_2                                            <= 1e-3
-#              and per (row, head) the same ratio                                           <= 1e-3
-#              except on the tensor-core prompt path, where the per-(row, head) bound is    <= 1.5e-3
-# Why the prompt path gets its own per-head bound: its MMA operands are fp16 with the q8_0 block scale
-# folded in (int8 * fp16 scale needs up to 18 significant bits, fp16 keeps 11).  The K operand's
-# rounding alone perturbs single (row, head) softmaxes by up to ~7e-4 on N(0,1) inputs, the V and P
-# roundings add ~3e-4 each in random directions (tests/test_prompt_rounding_model.py reproduces these
-# figures on the CPU), so the worst of ~16K (row, head) pairs lands at 0.8e-3 .. 1.0e-3 whatever the
-# kernel's schedule.  The decode, verify and exact paths apply K scales in fp32 after the MMA and stay
-# under 3e-4.
-# The per-(row, head) max-norm ratio max|diff| / max|oracle| is also computed and printed; it is not
-# a gate because rounding the OUTPUT to fp16 alone contributes up to 4.9e-4 to it on rows that see
-# one or two keys (nothing averages out there).
+# Tolerances of the attention outputs against the double-accumulated oracle (every path, every geometry):
+#   max-abs   : max |gpu - oracle| over every element                                        <= 2e-3
+#   relative  : per (row, head), max|gpu - oracle| / max|oracle|                             <= 1e-3   (*)
+#               per (row, head) and per token row (all heads: the vector the engine consumes),
+#               ||gpu - oracle||_2 / ||oracle||_2                                            <= 1e-3
+# (*) The max-norm ratio is gated on fp32 outputs.  When the library writes fp16 outputs, rounding the OUTPUT alone
+#     contributes up to 4.9e-4 to it on rows that see one or two keys (half an fp16 ulp of the largest element,
+#     nothing averages out there), which says nothing about the attention arithmetic; the same cases therefore run
+#     a second time with out_dtype = fp32 (geometry "B32" in the GPU tests) and are gated there.  The 2-norm
+#     ratios and max-abs are gated for both output types.
+# Error sources by design: Q, dequantised V and P are fp16 MMA operands (one rounding each); K enters the decode
+# and verify kernels as exact integers with the block scale applied in fp32, and the prompt kernels as an exact
+# two-part fp16 operand (hi + lo); every accumulation is fp32.
 MAX_ABS_TOL = 2e-3
 REL_TOL = 1e-3
-PROMPT_HEAD_REL_TOL = 1.5e-3
+PROMPT_HEAD_REL_TOL = REL_TOL        # the prompt path has no bound of its own any more
 
 
 def oracle_geom(g) -> O.Geom:
@@ -64,11 +61,25 @@ def errors(got: np.ndarray, ref: np.ndarray):
     return float(np.abs(diff).max()), float(l2.max()), float(mx.max()), float(row.max())
 
 
-def assert_close(got, ref, what="", head_tol: float = REL_TOL):
+def is_fp16_valued(x: np.ndarray) -> bool:
+    """True when every element is exactly representable in fp16 (the library wrote an fp16 output)."""
+    x = np.asarray(x, dtype=np.float32)
+    with np.errstate(over="ignore"):
+        return bool(np.array_equal(x, x.astype(np.float16).astype(np.float32), equal_nan=True))
+
+
+def assert_close(got, ref, what="", head_tol: float = REL_TOL, maxnorm=None):
+    """Gates max-abs, the per-token-row and per-(row, head) 2-norm ratios, and -- for fp32 outputs, or when
+    maxnorm=True -- the per-(row, head) max-norm ratio max|diff| / max|ref|."""
     mabs, rel, relmax, relrow = errors(got, ref)
     assert np.isfinite(np.asarray(got, dtype=np.float64)).all(), f"{what}: non-finite output"
     assert mabs <= MAX_ABS_TOL, f"{what}: max-abs {mabs:.3e} > {MAX_ABS_TOL}"
     assert relrow <= REL_TOL, f"{what}: relative per token row {relrow:.3e} > {REL_TOL}"
     assert rel <= head_tol, f"{what}: relative per (row, head) {rel:.3e} > {head_tol} (max-norm {relmax:.3e})"
-    print(f"[parity] {what}: max-abs {mabs:.2e} rel-row {relrow:.2e} rel-head {rel:.2e} rel-max {relmax:.2e}")
+    if maxnorm is None:
+        maxnorm = not is_fp16_valued(got)
+    if maxnorm:
+        assert relmax <= REL_TOL, f"{what}: max-norm ratio per (row, head) {relmax:.3e} > {REL_TOL}"
+    print(f"[parity] {what}: max-abs {mabs:.2e} rel-row {relrow:.2e} rel-head {rel:.2e} rel-max {relmax:.2e}"
+          f"{' (gated)' if maxnorm else ''}")
     return mabs, rel
