@@ -45,9 +45,11 @@ CPU_SAMPLE_CTXS = [8192, 16384, 32768, 65536]
 WINDOW = 4096
 POS_BYTES = 2176                      # K+V bytes per cached position per layer
 METRIC = "decode-attn HBM TB/s (ctx sweep 8K-256K, full + window-4096 layer per ctx)"
-# DRAM bytes (read + write) of one flash-decode launch at 256K from the ncu capture summarised in
-# profiles/; None until a capture exists
-NCU_TRAFFIC_256K = 570504448 + 4723968   # dram__bytes_read.sum + dram__bytes_write.sum, profiles/flash_decode_256k_ncu.md
+# DRAM bytes (read + write) of one flash-decode launch at 256K, from an ncu capture of the library revision named
+# beside it (dram__bytes_read.sum + dram__bytes_write.sum).  Reported as roofline.traffic only while the loaded
+# library still is that revision (battn_version()); a changed kernel needs a new capture.
+NCU_TRAFFIC_256K = {"lib_version": 2, "bytes": None}
+MIN_TIMED_S = 0.5                     # the K-step block is repeated until the timed region is at least this long
 
 
 def visible(ctx: int, is_swa: bool) -> int:
@@ -150,10 +152,32 @@ def cpu_workload(ctxs):
     return items
 
 
-def cpu_step(items, nthreads=0):
+def cpu_threads():
+    """(pool workers, OpenMP threads per oracle call, host threads used).  One oracle call runs its 8 KV heads on
+    up to 8 OpenMP threads; calls on different (context, layer) items run side by side from a thread pool, so that
+    all host cores are used whatever OMP_NUM_THREADS the launcher exported (torchrun sets it to 1)."""
+    cores = os.cpu_count() or 1
+    per_call = min(8, cores)
+    workers = max(1, cores // per_call)
+    return workers, per_call, workers * per_call
+
+
+def cpu_step(items):
+    from concurrent.futures import ThreadPoolExecutor
+
     from oracle import oracle as O
-    for g, q, kvk, kvv, pos, is_swa in items:
-        O.attend(g, q, kvk, kvv, [pos], rows=1, is_swa=is_swa, nthreads=nthreads)
+    workers, per_call, _ = cpu_threads()
+
+    def one(it):
+        g, q, kvk, kvv, pos, is_swa = it
+        O.attend(g, q, kvk, kvv, [pos], rows=1, is_swa=is_swa, nthreads=per_call)
+
+    if workers == 1:
+        for it in items:
+            one(it)
+    else:
+        with ThreadPoolExecutor(max_workers=workers) as ex:
+            list(ex.map(one, sorted(items, key=lambda it: -it[4])))      # longest contexts first
 
 
 def cpu_baseline(budget_s: float = 10.0):
@@ -168,9 +192,9 @@ def cpu_baseline(budget_s: float = 10.0):
         if dt >= budget_s or n >= 200:
             break
     tbs = n * step_bytes(CPU_SAMPLE_CTXS) / dt / 1e12
-    return {"value": tbs, "unit": "TB/s", "cores": O.num_threads(), "kind": "port",
+    return {"value": tbs, "unit": "TB/s", "cores": cpu_threads()[2], "kind": "port",
             "sample": f"decode sweep restricted to ctx {CPU_SAMPLE_CTXS} (full + window layer), {n} passes in {dt:.1f} s, "
-                      "double-accumulating scalar C oracle, OpenMP over KV heads"}
+                      "double-accumulating scalar C oracle, OpenMP over KV heads x a thread pool over (context, layer)"}
 
 
 def run_reference(args):
@@ -195,7 +219,7 @@ def run_reference(args):
         "data": "synthetic",
         "config": {"workload": "decode-attention context sweep (BASELINE config 1), CPU sample", "ctxs": CPU_SAMPLE_CTXS,
                    "n_head": 32, "n_kv": 8, "head_dim": 128, "window": WINDOW, "batch": 1},
-        "cpu_baseline": {"value": val, "unit": "TB/s", "cores": O.num_threads(), "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": val, "unit": "TB/s", "cores": cpu_threads()[2], "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": "TB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }

@@ -8,6 +8,7 @@ import os
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libbattn.so")
 
+IPC_HANDLE_BYTES = 64
 OK, ERR_ARG, ERR_CAPACITY, ERR_CUDA, ERR_DEVICE = 0, 1, 2, 3, 4
 DEV_BAD_POSITION, DEV_WAIT_TIMEOUT = 1, 2
 STATUS_NAMES = {0: "BATTN_OK", 1: "BATTN_ERR_ARG", 2: "BATTN_ERR_CAPACITY", 3: "BATTN_ERR_CUDA",
@@ -47,6 +48,14 @@ SIGNATURES = {
     "battn_attend_exact": (_I, [_P] * 9 + [_I, _I, _I, _I, _P]),
     "battn_partials": (_I, [_P] * 9 + [_I, _I, _I, _P]),
     "battn_merge": (_I, [_P, _P, _P, _I, _I, _P]),
+    "battn_xchg_create": (_I, [_P, _I, _I, _I, C.POINTER(_P), _P]),
+    "battn_xchg_connect": (_I, [_P, _P]),
+    "battn_xchg_area": (_I, [_P, C.POINTER(_P), _SZP]),
+    "battn_xchg_connect_ptrs": (_I, [_P, C.POINTER(_P)]),
+    "battn_xchg_set_wait_polls": (_I, [_P, C.c_uint]),
+    "battn_xchg_destroy": (_I, [_P]),
+    "battn_partials_push": (_I, [_P] * 10 + [_I, _I, _I, _P, _I, _P]),
+    "battn_merge_wait": (_I, [_P, _P, _P, _I, _P, _P]),
     "battn_device_status": (_I, [_P, C.POINTER(_I), _I]),
     "battn_selftest_wait_timeout": (_I, [_P, C.c_uint, _P]),
     "battn_profile_start": (_I, [_P, _I]),

@@ -2,6 +2,7 @@
 // No allocation, synchronisation or host read of device state happens inside the per-step entry
 // points, so they can be recorded into CUDA graphs like the reference's launches
 // (engine/src/bruce.cu:7877-7900, 8046-8055).
+#include <cstring>
 #include <new>
 
 #include "common.cuh"
@@ -196,7 +197,7 @@ cudaError_t launch_fd_kernel(const fd::Params& P, int grid, size_t smem, cudaStr
 // decode / verify / multi-slot decode through the flash-decode kernel and the balanced merge
 int launch_flash(battn_handle* h, void* out, float* rec_out, const void* q, const uint8_t* kvk, const uint8_t* kvv,
                  const int* pos, const int* kslot, const int* act, void* ws, int n_seq, int rows, int is_swa,
-                 cudaStream_t st) {
+                 cudaStream_t st, const XchgView* xv = nullptr, int* epoch_ptr = nullptr, int epoch_advance = 0) {
     const Geom& g = h->g;
     const int RG = rows * g.G;
     if (RG > 32) return BATTN_ERR_CAPACITY;
@@ -210,6 +211,7 @@ int launch_flash(battn_handle* h, void* out, float* rec_out, const void* q, cons
     P.W = g.W; P.pstride = is_swa ? g.ring : g.slot_ctx; P.ring_mask = is_swa ? g.ring - 1 : -1;
     P.slot_ctx = g.slot_ctx; P.n_slots = g.n_slots; P.is_swa = is_swa; P.q_f16 = g.q_f16;
     P.scale_log2 = g.scale * LOG2E; P.status = h->d_status;
+    P.epoch_ptr = epoch_ptr; P.epoch_advance = epoch_advance;
 
     cudaError_t e;
     if (RG > 16) {
@@ -242,6 +244,7 @@ int launch_flash(battn_handle* h, void* out, float* rec_out, const void* q, cons
     M.mode = 0; M.part = P.part; M.out = out; M.rec_out = rec_out;
     M.n_rows = n_seq * rows; M.rows = rows; M.Hq = g.Hq; M.Hkv = g.Hkv; M.G = g.G;
     M.count = 0; M.log2_domain = 1; M.out_f16 = g.out_f16; M.hdr = P.hdr; M.status = h->d_status;
+    if (xv) M.xchg = *xv;
     if (g.HD == 128) e = launch_pdl(k_merge_balanced<128>, dim3(n_seq * rows * g.Hq), dim3(MERGE_B_THREADS), 0, st, M);
     else             e = launch_pdl(k_merge_balanced<256>, dim3(n_seq * rows * g.Hq), dim3(MERGE_B_THREADS), 0, st, M);
     h->launches += 2;
@@ -282,6 +285,18 @@ int launch_prefill(battn_handle* h, void* out, const void* q, const uint8_t* kvk
         e = cudaGetLastError();
     }
     return e == cudaSuccess ? BATTN_OK : cuda_fail(h, e);
+}
+
+// device-side view of an exchange for one launch
+XchgView xchg_view(const battn_xchg* x, const int* epoch, int push, int wait) {
+    XchgView v{};
+    for (int d = 0; d < x->world; ++d) {
+        v.rec[d] = reinterpret_cast<float*>(x->area[d]);
+        v.flag[d] = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(x->area[d]) + x->rec_bytes);
+    }
+    v.world = x->world; v.rank = x->rank; v.max_items = x->max_items; v.epoch_ptr = epoch;
+    v.wait_polls = x->wait_polls; v.push = push; v.wait = wait;
+    return v;
 }
 
 // validates a caller's geometry and derives the internal one
@@ -520,6 +535,111 @@ int battn_attend_exact(battn_handle* h, void* out, const void* q, const uint8_t*
     if (!ws || ((uintptr_t)ws & 15) || nsplit < 1 || nsplit > MAX_SPLITS) return BATTN_ERR_ARG;
     return launch_exact(h, out, nullptr, q, kvk, kvv, pos, kslot, act, ws, n_seq, rows_per_seq, nsplit, is_swa,
                         (cudaStream_t)stream);
+}
+
+int battn_xchg_create(battn_handle* h, int rank, int world, int max_rows, battn_xchg** out_x, void* ipc_handle_out) {
+    if (!h || !out_x || world < 1 || world > XCHG_MAX_WORLD || rank < 0 || rank >= world) return BATTN_ERR_ARG;
+    if (max_rows < 1 || max_rows > MAX_VERIFY) return BATTN_ERR_ARG;
+    *out_x = nullptr;
+    battn_xchg* x = new (std::nothrow) battn_xchg();
+    if (!x) return BATTN_ERR_ARG;
+    const Geom& g = h->g;
+    x->h = h; x->world = world; x->rank = rank; x->max_items = max_rows * g.Hq;
+    x->rec_bytes = align_up((size_t)2 * world * x->max_items * (g.HD + 4) * sizeof(float), 256);
+    x->bytes = x->rec_bytes + align_up((size_t)world * x->max_items * sizeof(int), 256);
+    x->wait_polls = 1u << 17;                          // about 20 ms
+    for (int d = 0; d < 8; ++d) { x->area[d] = nullptr; x->ipc_opened[d] = false; }
+    cudaError_t e = cudaSetDevice(h->device);
+    if (e == cudaSuccess) e = cudaMalloc(&x->area[rank], x->bytes);
+    if (e == cudaSuccess) e = cudaMemset(x->area[rank], 0, x->bytes);      // flags start below every epoch >= 1
+    if (e == cudaSuccess && ipc_handle_out) {
+        cudaIpcMemHandle_t ih;
+        e = cudaIpcGetMemHandle(&ih, x->area[rank]);
+        if (e == cudaSuccess) memcpy(ipc_handle_out, &ih, sizeof(ih));
+    }
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) {
+        if (x->area[rank]) cudaFree(x->area[rank]);
+        delete x;
+        return cuda_fail(h, e);
+    }
+    *out_x = x;
+    return BATTN_OK;
+}
+
+int battn_xchg_connect(battn_xchg* x, const void* all_ipc_handles) {
+    if (!x || (!all_ipc_handles && x->world > 1)) return BATTN_ERR_ARG;
+    cudaError_t e = cudaSetDevice(x->h->device);
+    for (int d = 0; d < x->world && e == cudaSuccess; ++d) {
+        if (d == x->rank || x->area[d]) continue;
+        cudaIpcMemHandle_t ih;
+        memcpy(&ih, reinterpret_cast<const uint8_t*>(all_ipc_handles) + (size_t)d * BATTN_IPC_HANDLE_BYTES, sizeof(ih));
+        e = cudaIpcOpenMemHandle(&x->area[d], ih, cudaIpcMemLazyEnablePeerAccess);
+        if (e == cudaSuccess) x->ipc_opened[d] = true;
+    }
+    return e == cudaSuccess ? BATTN_OK : cuda_fail(x->h, e);
+}
+
+int battn_xchg_connect_ptrs(battn_xchg* x, void* const* areas) {
+    if (!x || !areas) return BATTN_ERR_ARG;
+    for (int d = 0; d < x->world; ++d) {
+        if (d == x->rank) continue;
+        if (!areas[d] || ((uintptr_t)areas[d] & 255)) return BATTN_ERR_ARG;
+        x->area[d] = areas[d];
+    }
+    return BATTN_OK;
+}
+
+int battn_xchg_area(const battn_xchg* x, void** out_ptr, size_t* out_bytes) {
+    if (!x || !out_ptr || !out_bytes) return BATTN_ERR_ARG;
+    *out_ptr = x->area[x->rank]; *out_bytes = x->bytes;
+    return BATTN_OK;
+}
+
+int battn_xchg_set_wait_polls(battn_xchg* x, unsigned polls) {
+    if (!x || polls < 1) return BATTN_ERR_ARG;
+    x->wait_polls = polls;
+    return BATTN_OK;
+}
+
+int battn_xchg_destroy(battn_xchg* x) {
+    if (!x) return BATTN_ERR_ARG;
+    cudaSetDevice(x->h->device);
+    cudaDeviceSynchronize();
+    for (int d = 0; d < x->world; ++d)
+        if (x->ipc_opened[d]) cudaIpcCloseMemHandle(x->area[d]);
+    if (x->area[x->rank]) cudaFree(x->area[x->rank]);
+    delete x;
+    return BATTN_OK;
+}
+
+int battn_partials_push(battn_handle* h, battn_xchg* x, void* out, const void* q, const uint8_t* kvk,
+                        const uint8_t* kvv, const int* pos, const int* kslot, const int* act, void* ws, int rows,
+                        int batch, int is_swa, int* epoch, int epoch_advance, void* stream) {
+    const int rc = check_seq_args(h, q, q, kvk, kvv, pos, kslot, batch, rows, MAX_VERIFY);
+    if (rc) return rc;
+    if (!x || x->h != h || !ws || ((uintptr_t)ws & 15) || ((uintptr_t)out & 15) || !epoch || epoch_advance < 0) return BATTN_ERR_ARG;
+    if (batch * rows * h->g.Hq > x->max_items) return BATTN_ERR_CAPACITY;
+    for (int d = 0; d < x->world; ++d)
+        if (!x->area[d]) return BATTN_ERR_ARG;                  // battn_xchg_connect has not run
+    const XchgView v = xchg_view(x, epoch, 1, out != nullptr);
+    return launch_flash(h, out, nullptr, q, kvk, kvv, pos, kslot, act, ws, batch, rows, is_swa, (cudaStream_t)stream, &v,
+                        epoch, epoch_advance);
+}
+
+int battn_merge_wait(battn_handle* h, battn_xchg* x, void* out, int n_rows, const int* epoch, void* stream) {
+    if (!h || !x || x->h != h || !out || ((uintptr_t)out & 15) || n_rows < 1 || !epoch) return BATTN_ERR_ARG;
+    if (n_rows * h->g.Hq > x->max_items) return BATTN_ERR_CAPACITY;
+    const Geom& g = h->g;
+    MergeParams M{};
+    M.out = out; M.out_f16 = g.out_f16; M.Hq = g.Hq; M.status = h->d_status;
+    M.xchg = xchg_view(x, epoch, 0, 1);
+    cudaError_t e;
+    if (g.HD == 128) e = launch_pdl(k_merge_wait<128>, dim3(n_rows * g.Hq), dim3(32), 0, (cudaStream_t)stream, M);
+    else             e = launch_pdl(k_merge_wait<256>, dim3(n_rows * g.Hq), dim3(64), 0, (cudaStream_t)stream, M);
+    h->launches += 1;
+    if (e == cudaSuccess) e = cudaGetLastError();
+    return e == cudaSuccess ? BATTN_OK : cuda_fail(h, e);
 }
 
 int battn_merge(battn_handle* h, void* out, const float* parts, int n_parts, int n_rows, void* stream) {

@@ -42,6 +42,16 @@ struct battn_handle {
     int fd_smem[3];
 };
 
+// Receive area of one device in a sequence split (see XchgView in exact.cuh) and its mappings of the peers' areas.
+struct battn_xchg {
+    battn_handle* h;
+    int world, rank, max_items;
+    size_t rec_bytes, bytes;          // records, then flags
+    void* area[8];                    // area[d]: device d's receive area as mapped into this process
+    bool ipc_opened[8];
+    unsigned wait_polls;
+};
+
 namespace battn {
 
 // ---- small device helpers ---------------------------------------------------------------------

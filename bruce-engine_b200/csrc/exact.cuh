@@ -107,6 +107,89 @@ __global__ void __launch_bounds__(256) k_attn_exact(const ExactParams P) {
 
 enum { MERGE_REGULAR = 0, MERGE_GATHERED = 1 };
 
+// Exchange of split records between the devices that hold the position shards of ONE sequence.
+// Every device owns a receive area, mapped into all peers: records [2 parities][world][max_items][HD + 4] floats
+// (o[HD], m in log2 units, l, pad) followed by flags [world][max_items] ints.  Device `rank` pushes its merged
+// record of item (row, head) for step `epoch` into slot [epoch & 1][rank][item] of EVERY device (its own included)
+// with plain stores, fences them system-wide, and then stores `epoch` into flag [rank][item] there.  A reader
+// polls its local flags until they reach its epoch.  Two record buffers suffice: a device cannot push step e + 2
+// before its own merge of step e + 1 completed, which needed every peer's push of e + 1, which those peers issue
+// after their merge of step e.
+constexpr int XCHG_MAX_WORLD = 8;
+struct XchgView {
+    float* rec[XCHG_MAX_WORLD];     // receive area of device d as mapped HERE (rec[rank] is the local one), or null
+    int* flag[XCHG_MAX_WORLD];
+    int world, rank, max_items;
+    const int* epoch_ptr;           // device-resident step number, advanced by the decode kernel of the same call
+    unsigned wait_polls;            // bound of the acquire-spin (polls of ~100 ns)
+    int push, wait;                 // which halves of the exchange this launch performs
+};
+
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Waits (bounded) until every device's record of `item` for X.epoch has landed in the local receive area, then
+// merges them: called by the first HD/4 threads' block after a block-wide barrier.  Returns false on time-out.
+template <int HD, int NTHR>
+__device__ __forceinline__ bool xchg_wait(const XchgView& X, int epoch, int item, int* status) {
+    bool ok = true;
+    if (threadIdx.x < X.world) {
+        ok = false;
+        const int* f = X.flag[X.rank] + (size_t)threadIdx.x * X.max_items + item;
+        for (unsigned it = 0; it < X.wait_polls; ++it) {
+            if (ld_acquire_sys(f) - epoch >= 0) { ok = true; break; }
+            __nanosleep(100);
+        }
+    }
+    ok = __syncthreads_and(ok);
+    if (!ok && threadIdx.x == 0) atomicOr(status, BATTN_DEV_WAIT_TIMEOUT);
+    return ok;
+}
+
+// Merge of the `world` records of `item` in the local receive area; thread dq owns dims 4dq .. 4dq+3.
+template <int HD>
+__device__ __forceinline__ void xchg_merge_store(const XchgView& X, int epoch, int item, int dq, void* out, int out_f16,
+                                                 size_t oi) {
+    constexpr int RS = HD + 4;
+    const float* base = X.rec[X.rank] + ((size_t)(epoch & 1) * X.world * X.max_items + item) * RS;
+    const size_t stride = (size_t)X.max_items * RS;
+    float4 o[XCHG_MAX_WORLD];
+    float2 ml[XCHG_MAX_WORLD];
+    float M = NEG_BIG;
+#pragma unroll
+    for (int r = 0; r < XCHG_MAX_WORLD; ++r)
+        if (r < X.world) {
+            o[r] = __ldcg(reinterpret_cast<const float4*>(base + r * stride + 4 * dq));
+            ml[r] = __ldcg(reinterpret_cast<const float2*>(base + r * stride + HD));
+            M = fmaxf(M, ml[r].x);
+        }
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float L = 0.f;
+#pragma unroll
+    for (int r = 0; r < XCHG_MAX_WORLD; ++r)
+        if (r < X.world) {
+            const float w = fast_exp2(ml[r].x - M);
+            L = fmaf(ml[r].y, w, L);
+            acc.x = fmaf(o[r].x, w, acc.x); acc.y = fmaf(o[r].y, w, acc.y);
+            acc.z = fmaf(o[r].z, w, acc.z); acc.w = fmaf(o[r].w, w, acc.w);
+        }
+    const float il = L > 0.f ? 1.f / L : 0.f;
+    if (out_f16) {
+        const __half2 a = __floats2half2_rn(acc.x * il, acc.y * il), b = __floats2half2_rn(acc.z * il, acc.w * il);
+        *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(out) + oi) =
+            make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
+    } else {
+        *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + oi) =
+            make_float4(acc.x * il, acc.y * il, acc.z * il, acc.w * il);
+    }
+}
+
 struct MergeParams {
     int mode;              // k_merge only: MERGE_REGULAR or MERGE_GATHERED
     const float* part;     // records
@@ -124,6 +207,8 @@ struct MergeParams {
     int* status;
     // k_merge_balanced only: header written by the flash-decode kernel: {tiles_per_cta, total, cum[n_seq+1]}
     const int* hdr;
+    // sequence split across devices (k_merge_balanced as the pushing epilogue, k_merge_wait): see XchgView
+    XchgView xchg;
 };
 
 constexpr int MERGE_THREADS = 256;
@@ -243,12 +328,14 @@ __global__ void __launch_bounds__(MERGE_B_THREADS) k_merge_balanced(const MergeP
     const int per = P.hdr[0];
     const int c0 = P.hdr[2 + i], c1 = P.hdr[3 + i];
     const int nt = c1 - c0;
-    if (nt <= 0) return;                                         // inactive sequence: no output
+    const bool xq = P.xchg.world > 0;                            // this launch feeds a cross-device exchange
+    if (nt <= 0 && !xq) return;                                  // inactive sequence: no output
     const int item = i * P.Hkv + kvh;
     const long long t0 = (long long)P.Hkv * c0 + (long long)kvh * nt, t1 = t0 + nt;
     const int clo = (int)(t0 / per), chi = (int)((t1 - 1) / per);
     const int RG = P.rows * P.G;
-    const int count = min(chi - clo + 1, MERGE_MAX_COUNT);
+    // (an inactive shard of a split sequence contributes the empty record (0, -1e30, 0), bruce.cu:2319-2322)
+    const int count = nt <= 0 ? 0 : min(chi - clo + 1, MERGE_MAX_COUNT);
     const float* base = P.part + ((size_t)(clo + item) * RG + r * P.G + h) * (size_t)RS;
     const size_t stride = (size_t)RG * RS;
 
@@ -300,11 +387,35 @@ __global__ void __launch_bounds__(MERGE_B_THREADS) k_merge_balanced(const MergeP
         }
         __syncthreads();
     }
-    if (grp != 0) return;
     const int d4 = 4 * dq;
+    const size_t oi = ((size_t)rowidx * P.Hq + hq) * HD + d4;
+    if (xq) {
+        // ---- sequence split: push this device's record to every peer, then merge what the peers pushed ----
+        const XchgView& X = P.xchg;
+        const int xitem = rowidx * P.Hq + hq;
+        const int epoch = *X.epoch_ptr;
+        if (X.push && grp == 0) {
+            const size_t slot = (((size_t)(epoch & 1) * X.world + X.rank) * X.max_items + xitem) * RS;
+#pragma unroll
+            for (int d = 0; d < XCHG_MAX_WORLD; ++d)
+                if (d < X.world) {
+                    float* dst = X.rec[d] + slot;                // plain stores into the peer's memory
+                    *reinterpret_cast<float4*>(dst + d4) = acc;
+                    if (dq == 0) *reinterpret_cast<float2*>(dst + HD) = make_float2(M, L);
+                }
+            __threadfence_system();
+        }
+        __syncthreads();
+        if (X.push && tid < X.world)
+            st_release_sys(X.flag[tid] + (size_t)X.rank * X.max_items + xitem, epoch);
+        if (!X.wait || !P.out) return;
+        if (!xchg_wait<HD, MERGE_B_THREADS>(X, epoch, xitem, P.status)) return;
+        if (grp == 0) xchg_merge_store<HD>(X, epoch, xitem, dq, P.out, P.out_f16, oi);
+        return;
+    }
+    if (grp != 0) return;
     if (P.out) {
         const float il = L > 0.f ? 1.f / L : 0.f;
-        const size_t oi = ((size_t)rowidx * P.Hq + hq) * HD + d4;
         if (P.out_f16) {
             const __half2 a = __floats2half2_rn(acc.x * il, acc.y * il), b = __floats2half2_rn(acc.z * il, acc.w * il);
             *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(P.out) + oi) =
@@ -323,6 +434,19 @@ __global__ void __launch_bounds__(MERGE_B_THREADS) k_merge_balanced(const MergeP
             ro[HD + 1] = L;
         }
     }
+}
+
+// The receiving half of the exchange on its own: one block per (row, head) waits for every device's record of the
+// step and merges them (for hosts that put other work between the push and the merge).
+template <int HD>
+__global__ void __launch_bounds__(HD / 4 < 32 ? 32 : HD / 4) k_merge_wait(const MergeParams P) {
+    pdl_wait();
+    pdl_trigger();
+    const int xitem = blockIdx.x;
+    const int epoch = *P.xchg.epoch_ptr;
+    if (!xchg_wait<HD, HD / 4>(P.xchg, epoch, xitem, P.status)) return;
+    if ((int)threadIdx.x < HD / 4)
+        xchg_merge_store<HD>(P.xchg, epoch, xitem, threadIdx.x, P.out, P.out_f16, (size_t)xitem * HD + 4 * threadIdx.x);
 }
 
 }  // namespace battn

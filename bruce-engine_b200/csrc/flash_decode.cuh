@@ -51,6 +51,10 @@ struct Params {
     int W, pstride, ring_mask, slot_ctx, n_slots, is_swa, q_f16;
     float scale_log2;   // softmax scale * log2(e): scores are kept in log2 units
     int* status;
+    // sequence split across devices: the step counter the merge epilogue reads is advanced here, one kernel
+    // earlier, so that every block of the epilogue sees the same value (null when there is no exchange)
+    int* epoch_ptr;
+    int epoch_advance;
 };
 
 template <int HD>
@@ -118,6 +122,7 @@ k_flash_decode(const Params P) {
     }
     pdl_wait();          // nothing above reads or writes global memory
     pdl_trigger();
+    if (P.epoch_ptr && blockIdx.x == 0 && tid == 0) *P.epoch_ptr += P.epoch_advance;
     if (P.n_seq == 1) {
         // one sequence (decode / verify of a single stream): no prefix sum, one barrier
         if (tid == 0) {

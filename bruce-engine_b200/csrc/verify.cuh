@@ -73,6 +73,7 @@ __global__ void __launch_bounds__(NTHREADS, HD == 128 ? 3 : 1) k_verify_wide(con
     }
     pdl_wait();
     pdl_trigger();
+    if (P.epoch_ptr && blockIdx.x == 0 && tid == 0) *P.epoch_ptr += P.epoch_advance;
     // ---- the flash-decode work cut: every CTA derives the same tile shares from the positions -------
     for (int i = tid; i < P.n_seq; i += NTHREADS) {
         const SeqRange sr = seq_range(P.pos, P.kslot, P.act, i, P.rows, P.is_swa, P.W, P.slot_ctx, P.n_slots, P.status);

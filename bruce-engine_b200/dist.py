@@ -111,25 +111,63 @@ def empty_records(rows: int, n_head: int, head_dim: int, device) -> torch.Tensor
 
 
 class SeqSplitDecoder:
-    """Decode attention over one sequence whose KV cache is split by position range across the ranks
-    of a process group (full-causal layers; window layers stay on the owner of the tail)."""
+    """Decode attention over one sequence whose KV cache is split by position range across the ranks of a process
+    group (full-causal layers).  Sliding-window layers read only the last `window` keys: they are not split --
+    `owner_of(p0, ...)` names the rank that holds the tail and serves them alone (`decode_window`).
+
+    Two exchanges of the per-shard (o, m, l) records:
+      * "push" (default on CUDA): the decode kernel's merge epilogue stores the records straight into every peer's
+        receive area over NVLink and merges what the peers stored (battn_partials_push) -- no collective call;
+      * "nccl": battn_partials, all_gather_into_tensor, battn_merge -- the baseline the push form is measured against.
+    Everything a step needs is allocated here; a step allocates nothing, and each (mode, rows) shape is captured
+    into a CUDA graph on its second use and replayed from then on (the shard's local position, its activity flag
+    and the step counter are device-resident)."""
 
     MAX_ROWS = 8     # rows per decode call (the verify limit, bruce.cu:94)
 
-    def __init__(self, engine, n_total: int, group=None):
+    def __init__(self, engine, n_total: int, group=None, exchange: str = "push", use_graphs: bool = True):
         self.eng, self.group = engine, group
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         self.shard = shard_of(n_total, self.rank, self.world)
+        self.n_total = n_total
         g = engine.geom
         if g.slot_ctx < self.shard.capacity:
             raise ValueError("engine slot_ctx is smaller than this rank's shard")
+        if exchange not in ("push", "nccl"):
+            raise ValueError("exchange must be 'push' or 'nccl'")
         dev = engine.device
+        R = self.MAX_ROWS
         # decode() runs either `rows` one-row sequences (shards that lie wholly before the block) or one
         # sequence of `rows` rows (the shard that holds the block): the scratch must serve both shapes
-        self.part = torch.empty(max(engine.workspace_bytes(self.MAX_ROWS, 1), engine.workspace_bytes(1, self.MAX_ROWS)),
+        self.part = torch.empty(max(engine.workspace_bytes(R, 1), engine.workspace_bytes(1, R)),
                                 dtype=torch.uint8, device=dev)
-        self._pos = torch.zeros(8, dtype=torch.int32, device=dev)
-        self._kslot = torch.zeros(8, dtype=torch.int32, device=dev)
+        # device-resident step parameters (the kernels read them, so captured graphs replay at new values): local
+        # position and activity flag of this shard, and the step counter, which the decode kernel advances itself
+        self._pos = torch.zeros(R, dtype=torch.int32, device=dev)
+        self._act = torch.ones(R, dtype=torch.int32, device=dev)
+        self._epoch = torch.zeros(1, dtype=torch.int32, device=dev)
+        self._cur = (0, 1)                                   # (position, activity) currently held on the device
+        self._behind = 0                                     # steps of the group this rank sat out
+        self._kslot = torch.zeros(R, dtype=torch.int32, device=dev)
+        self._rec = torch.zeros((R, g.n_head, g.head_dim + 2), dtype=torch.float32, device=dev)
+        self._recs = torch.zeros((self.world, R, g.n_head, g.head_dim + 2), dtype=torch.float32, device=dev)
+        self.exchange, self.use_graphs = exchange, use_graphs
+        self.step = 0
+        self._graphs, self._seen = {}, set()
+        self.x = None
+        if exchange == "push":
+            self.x, mine = engine.xchg_create(self.rank, self.world, R)
+            handles = [None] * self.world
+            dist.all_gather_object(handles, mine, group=group)
+            engine.xchg_connect(self.x, b"".join(handles))
+            dist.barrier(group=group)                        # every area is mapped before anyone pushes
+
+    def close(self):
+        if self.x is not None:
+            torch.cuda.synchronize()
+            dist.barrier(group=self.group)                   # nobody still pushes into an area that goes away
+            self.eng.xchg_destroy(self.x)
+            self.x = None
 
     def append(self, k, v, kvk, kvv, p0: int, rows: int = 1):
         """Store rows at global positions p0.. on their owner (other ranks do nothing)."""
@@ -139,21 +177,61 @@ class SeqSplitDecoder:
         self.eng.qkv_prep_store(k, v, kvk, kvv, pos, rows=rows)
         return True
 
+    # ---- one step -----------------------------------------------------------------------------------------
+    def _enqueue(self, mode: str, rows: int, out, q, kvk, kvv, advance: int = 1):
+        """The device work of one step (no allocation, no host synchronisation: capturable)."""
+        eng, g = self.eng, self.eng.geom
+        if mode == "seqs":          # every row sees the whole shard: `rows` one-row sequences of slot 0
+            n_seq, r = rows, 1
+        else:                       # "block": the shard holds the block; "idle": it starts behind it (act = 0)
+            n_seq, r = 1, rows
+        pos, act, kslot = self._pos[:n_seq], self._act[:n_seq], self._kslot[:n_seq]
+        if self.exchange == "push":
+            eng.attn_partials_push(self.x, out, q, kvk, kvv, pos, self.part, self._epoch, rows=r, batch=n_seq,
+                                   kslot=kslot, act=act, epoch_advance=advance)
+        else:
+            rec = self._rec[:rows]
+            eng.attn_partials(rec, q, kvk, kvv, pos, self.part, rows=r, batch=n_seq, kslot=kslot, act=act)
+            flat = self._recs.view(-1)[:self.world * rec.numel()]
+            dist.all_gather_into_tensor(flat, rec.reshape(-1), group=self.group)
+            eng.attn_combine(out, flat.view(self.world, rows, g.n_head, g.head_dim + 2), self.world, rows)
+
+    def skip_step(self):
+        """This rank sits out one step of the group (it neither pushes nor merges).  Its peers' merge of that step
+        runs into the bounded wait and reports BATTN_DEV_WAIT_TIMEOUT; the step after it is in step again."""
+        self._behind += 1
+
     def decode(self, out, q, kvk, kvv, p0: int, rows: int = 1):
         """q, out: [rows][n_head][head_dim] (replicated on every rank).  Returns out."""
-        g, eng = self.eng.geom, self.eng
+        g = self.eng.geom
         if not 1 <= rows <= self.MAX_ROWS or rows * g.group > 32:
             raise ValueError(f"rows must be 1..{self.MAX_ROWS} with rows * heads-per-kv-head <= 32")
         active, lp0, lrows = local_query(self.shard, p0, rows)
-        rec = empty_records(rows, g.n_head, g.head_dim, eng.device)
-        if active and lrows == 0:
-            # every row sees the whole shard: rows become independent 1-row sequences of slot 0
-            self._pos[:rows].fill_(lp0)
-            eng.attn_partials(rec, q, kvk, kvv, self._pos[:rows], self.part, rows=1, batch=rows,
-                              kslot=self._kslot[:rows])
-        elif active:
-            self._pos[:1].fill_(lp0)
-            eng.attn_partials(rec, q, kvk, kvv, self._pos[:1], self.part, rows=rows, batch=1)
-        recs = gather_records(rec, self.group)
-        eng.attn_combine(out, recs, self.world, rows)
+        mode = "idle" if not active else ("seqs" if lrows == 0 else "block")
+        if self._cur != (lp0, int(active)):                  # stream-ordered updates, only when something changed
+            if self._cur[0] != lp0:
+                self._pos.fill_(lp0)
+            if self._cur[1] != int(active):
+                self._act.fill_(int(active))
+            self._cur = (lp0, int(active))
+        if self.exchange == "nccl" and not active:
+            # the plain-partials path writes no record for an inactive sequence: keep the empty one in place
+            self._rec[:rows].zero_()
+            self._rec[:rows, :, g.head_dim] = EMPTY_M
+        advance, self._behind = 1 + self._behind, 0
+        key = (mode, rows, out.data_ptr(), q.data_ptr(), kvk.data_ptr(), kvv.data_ptr())
+        gr = self._graphs.get(key) if advance == 1 else None
+        if gr is not None:
+            gr.replay()
+        elif self.use_graphs and advance == 1 and key in self._seen and self.exchange == "push":
+            # second use of this shape: capture it (the captured launches do not run), then replay
+            gr = torch.cuda.CUDAGraph()
+            torch.cuda.synchronize()
+            with torch.cuda.graph(gr):
+                self._enqueue(mode, rows, out, q, kvk, kvv)
+            self._graphs[key] = gr
+            gr.replay()
+        else:
+            self._seen.add(key)
+            self._enqueue(mode, rows, out, q, kvk, kvv, advance)
         return out

@@ -169,6 +169,47 @@ class AttnEngine:
         rc = self.lib.battn_merge(self.h, _ptr(out), _ptr(parts), n_parts, n_rows, self._stream())
         self._check("battn_merge", rc)
 
+    # ---- one sequence split by position range across devices ----------------------------------------
+    def xchg_create(self, rank: int, world: int, max_rows: int = 8):
+        """This device's receive area for the cross-device exchange of split records.  Returns (exchange, its
+        IPC handle as bytes) -- the handle goes to the other processes."""
+        x = C.c_void_p()
+        buf = C.create_string_buffer(capi.IPC_HANDLE_BYTES)
+        self._check("battn_xchg_create", self.lib.battn_xchg_create(self.h, rank, world, max_rows, C.byref(x), buf))
+        return x, bytes(buf.raw)
+
+    def xchg_connect(self, x, all_handles: bytes):
+        self._check("battn_xchg_connect", self.lib.battn_xchg_connect(x, all_handles))
+
+    def xchg_area(self, x):
+        ptr, n = C.c_void_p(), C.c_size_t()
+        self._check("battn_xchg_area", self.lib.battn_xchg_area(x, C.byref(ptr), C.byref(n)))
+        return ptr.value, n.value
+
+    def xchg_connect_ptrs(self, x, ptrs):
+        arr = (C.c_void_p * len(ptrs))(*ptrs)
+        self._check("battn_xchg_connect_ptrs", self.lib.battn_xchg_connect_ptrs(x, arr))
+
+    def xchg_set_wait_polls(self, x, polls: int):
+        self._check("battn_xchg_set_wait_polls", self.lib.battn_xchg_set_wait_polls(x, polls))
+
+    def xchg_destroy(self, x):
+        self.lib.battn_xchg_destroy(x)
+
+    def attn_partials_push(self, x, out, q, kvk, kvv, pos, part, epoch, rows: int = 1, batch: int = 1,
+                           is_swa: bool = False, kslot=None, act=None, epoch_advance: int = 1):
+        """Decode on this device's shard, push the merged (o, m, l) records to every device of the group and --
+        when `out` is given -- wait for the peers' records of the same step and merge them (one decode launch + one
+        merge launch).  `epoch`: int32 device tensor holding this device's step counter (advanced on the device)."""
+        rc = self.lib.battn_partials_push(self.h, x, _ptr(out), _ptr(q), _ptr(kvk), _ptr(kvv), _ptr(pos), _ptr(kslot),
+                                          _ptr(act), _ptr(part), rows, batch, int(is_swa), _ptr(epoch),
+                                          int(epoch_advance), self._stream())
+        self._check("battn_partials_push", rc)
+
+    def attn_merge_wait(self, x, out, n_rows: int, epoch):
+        rc = self.lib.battn_merge_wait(self.h, x, _ptr(out), n_rows, _ptr(epoch), self._stream())
+        self._check("battn_merge_wait", rc)
+
     # ---- diagnostics -------------------------------------------------------------------------------
     def device_status(self, clear: bool = True) -> int:
         bits = C.c_int()

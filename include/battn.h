@@ -38,7 +38,7 @@
 extern "C" {
 #endif
 
-#define BATTN_VERSION 1
+#define BATTN_VERSION 2
 
 /* status codes */
 enum {
@@ -223,6 +223,44 @@ int battn_partials(battn_handle* h, float* rec, const void* q, const uint8_t* kv
  *   out = sum_s o_s e^(m_s-M) / sum_s l_s e^(m_s-M), M = max_s m_s; empty records contribute 0. */
 int battn_merge(battn_handle* h, void* out, const float* parts, int n_parts, int n_rows,
                 void* stream);
+
+/* ---- One sequence split by position range across several devices (no counterpart in the reference, which is
+ * single-GPU; built on its split record and merge, bruce.cu:781-783, 992-1007) ------------------------------------
+ * Device r of `world` holds positions [r*N/world, (r+1)*N/world) of the sequence in its own cache, with LOCAL
+ * positions.  A decode step runs the ordinary split-K decode on every shard; the epilogue of that kernel stores the
+ * shard's merged record (o, m, l) of every (row, head) straight into a receive area on EVERY device of the group
+ * (plain stores through peer-mapped pointers over NVLink, a system-scope fence, then an epoch flag), and then
+ * waits -- bounded -- until the other devices' records of the same step have landed locally and merges them.
+ * No collective library call, no host round trip: one decode + one merge launch per step per device.
+ *
+ * battn_xchg_create allocates this device's receive area (cudaMalloc; call outside stream capture) and returns a
+ * BATTN_IPC_HANDLE_BYTES-byte handle the host passes to the other processes by whatever transport it has;
+ * battn_xchg_connect maps the peers' areas from their handles (`all_ipc_handles`: world handles in rank order;
+ * the own entry is ignored).  A host that drives several devices from ONE process exchanges raw pointers
+ * instead (battn_xchg_area / battn_xchg_connect_ptrs, after enabling peer access itself).
+ *
+ * battn_partials_push: arguments as battn_partials, minus `rec`.  `epoch` points to this device's step counter in
+ * DEVICE memory (4 bytes the host allocates and zeroes once); the call adds `epoch_advance` to it on the device
+ * before use -- 1 in the normal case, so that a captured graph replays at successive steps; 1 + k after this
+ * device sat out k steps of the group -- and the resulting step number must be the same on every device.  With
+ * out != NULL the same launch also performs the wait-and-merge and writes the normalised output
+ * [batch*rows][n_head][head_dim]; with out == NULL it only pushes and battn_merge_wait finishes the step later.
+ * A device whose shard holds no visible key passes act = {0}: it pushes the empty record.
+ * If a peer's record does not arrive within the wait bound (battn_xchg_set_wait_polls, polls of ~100 ns, default
+ * 2^17), the launch sets BATTN_DEV_WAIT_TIMEOUT in the device status word, leaves `out` untouched and returns
+ * normally; the next step can proceed. */
+#define BATTN_IPC_HANDLE_BYTES 64
+typedef struct battn_xchg battn_xchg;
+int battn_xchg_create(battn_handle* h, int rank, int world, int max_rows, battn_xchg** out_x, void* ipc_handle_out);
+int battn_xchg_connect(battn_xchg* x, const void* all_ipc_handles);
+int battn_xchg_area(const battn_xchg* x, void** out_ptr, size_t* out_bytes);
+int battn_xchg_connect_ptrs(battn_xchg* x, void* const* areas);
+int battn_xchg_set_wait_polls(battn_xchg* x, unsigned polls);
+int battn_xchg_destroy(battn_xchg* x);
+int battn_partials_push(battn_handle* h, battn_xchg* x, void* out, const void* q, const uint8_t* kvk,
+                        const uint8_t* kvv, const int* pos, const int* kslot, const int* act, void* ws, int rows,
+                        int batch, int is_swa, int* epoch, int epoch_advance, void* stream);
+int battn_merge_wait(battn_handle* h, battn_xchg* x, void* out, int n_rows, const int* epoch, void* stream);
 
 /* Device status word (bits BATTN_DEV_*), read with a blocking copy; clears it when `clear` != 0.
  * Not for use inside stream capture. */

@@ -1,6 +1,9 @@
-"""Sequence split across GPUs (BASELINE config 4b at small size): every rank runs battn_partials on
-its position shard, the (o, m, l) records are all-gathered over NCCL and merged by battn_merge; the
-result must equal the single-cache oracle.  Needs >= 2 GPUs (skipped otherwise)."""
+"""Sequence split across GPUs (BASELINE config 4b at small size): every rank decodes on its position shard; the
+per-shard (o, m, l) records are exchanged either by the push epilogue (plain stores into the peers' receive areas
+over NVLink, battn_partials_push) or by an NCCL all-gather (battn_partials + battn_merge); the result must equal
+the single-cache oracle on every rank.  Also: a rank that sits out a step between two steps (a host-side decision;
+no kernel is in flight on it) makes its peers' merge give up at its wait bound and report the status bit, and the
+step after that is correct again.  Needs >= 2 GPUs (skipped otherwise)."""
 import os
 import socket
 
@@ -19,13 +22,15 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, n_total, cases, q_all, k, v, ret):
+def _worker(rank, world, port, n_total, cases, q_all, k, v, exchange, skip_case, ret):
     import torch.distributed as dist
 
+    from bruce_engine_b200 import capi
     from bruce_engine_b200 import dist as bd
     from bruce_engine_b200.engine import AttnEngine
     from bruce_engine_b200.layout import G_B
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
@@ -33,7 +38,9 @@ def _worker(rank, world, port, n_total, cases, q_all, k, v, ret):
         g = G_B.with_(slot_ctx=max(2, sh.capacity), window=128)
         eng = AttnEngine(g, rank)
         kvk, kvv = eng.alloc_kv_layer(False, fill=0)
-        dec = bd.SeqSplitDecoder(eng, n_total)
+        dec = bd.SeqSplitDecoder(eng, n_total, exchange=exchange)
+        if dec.x is not None:
+            eng.xchg_set_wait_polls(dec.x, 20000)           # a few milliseconds: the skipped step must not take long
         kd, vd = torch.from_numpy(k).cuda(), torch.from_numpy(v).cuda()
         for a in range(0, n_total, 128):                    # every rank sees every append; owners store
             b = min(n_total, a + 128)
@@ -42,26 +49,41 @@ def _worker(rank, world, port, n_total, cases, q_all, k, v, ret):
                 lo, hi = max(a, so.start), min(b, so.end)
                 if lo < hi:
                     dec.append(kd[None, lo:hi], vd[None, lo:hi], kvk, kvv, lo, hi - lo)
-        outs = []
+        outs, status = [], []
         for ci, (p0, rows) in enumerate(cases):
             q = torch.from_numpy(q_all[ci][:rows]).cuda().half().contiguous()
             out = torch.full((rows, g.n_head, g.head_dim), float("nan"), dtype=torch.float16, device="cuda")
-            dec.decode(out, q, kvk, kvv, p0, rows)
+            if ci == skip_case and rank == world - 1:
+                dec.skip_step()                             # this rank sits the step out (decided between steps)
+            else:
+                dec.decode(out, q, kvk, kvv, p0, rows)
             torch.cuda.synchronize()
+            dist.barrier()                                  # a step ends before the next one starts
             outs.append(out.float().cpu().numpy())
-        assert eng.device_status() == 0
-        # every rank must hold the same merged output
-        chk = torch.from_numpy(np.concatenate([o.reshape(-1) for o in outs])).cuda()
-        ref = chk.clone()
-        dist.broadcast(ref, 0)
-        assert torch.equal(chk, ref)
+            status.append(eng.device_status())
+        # every rank that took part must hold the same merged output
+        for ci in range(len(cases)):
+            if ci == skip_case:
+                continue
+            chk = torch.from_numpy(outs[ci].reshape(-1)).cuda()
+            ref = chk.clone()
+            dist.broadcast(ref, 0)
+            assert torch.equal(chk, ref)
+        if skip_case is not None:
+            want = 0 if rank == world - 1 else capi.DEV_WAIT_TIMEOUT
+            assert status[skip_case] == want, f"rank {rank}: status {status[skip_case]} on the skipped step"
+            assert np.isnan(outs[skip_case]).all()
+            assert all(s == 0 for i, s in enumerate(status) if i != skip_case)
+        else:
+            assert all(s == 0 for s in status)
+        dec.close()
         if rank == 0:
             ret.put(outs)
     finally:
         dist.destroy_process_group()
 
 
-def test_sequence_split_decode_over_nccl():
+def _run(n_total, cases, exchange, skip_case=None, seed=31):
     import torch.multiprocessing as mp
 
     from oracle import oracle as O
@@ -69,26 +91,49 @@ def test_sequence_split_decode_over_nccl():
     world = min(torch.cuda.device_count(), 4)
     if world < 2:
         pytest.skip("needs at least 2 GPUs")
-    n_total = 4000
     g = O.Geom(n_head=32, n_kv=8, head_dim=128, window=128, slot_ctx=n_total)
-    rng = np.random.default_rng(31)
+    rng = np.random.default_rng(seed)
     k = rng.standard_normal((n_total, g.n_kv, g.head_dim), dtype=np.float32)
     v = rng.standard_normal((n_total, g.n_kv, g.head_dim), dtype=np.float32)
-    cases = [(n_total - 1, 1), (n_total - 4, 4), (n_total // world - 2, 2), (0, 1)]
-    q_all = [rng.standard_normal((4, g.n_head, g.head_dim), dtype=np.float32).astype(np.float16).astype(np.float32)
+    q_all = [rng.standard_normal((8, g.n_head, g.head_dim), dtype=np.float32).astype(np.float16).astype(np.float32)
              for _ in cases]
     kvk, kvv = O.new_cache(g, False), O.new_cache(g, False)
     O.kv_append(g, k[None], v[None], kvk, kvv, [0], rows=n_total)
     ctx = mp.get_context("spawn")
     ret = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, n_total, cases, q_all, k, v, ret)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, n_total, cases, q_all, k, v, exchange, skip_case, ret))
+             for r in range(world)]
     for p in procs:
         p.start()
     outs = ret.get(timeout=300)
     for p in procs:
         p.join(timeout=120)
         assert p.exitcode == 0
-    for (p0, rows), q, got in zip(cases, q_all, outs):
+    for ci, ((p0, rows), q, got) in enumerate(zip(cases, q_all, outs)):
+        if ci == skip_case:
+            continue
         want = O.attend(g, q[None, :rows], kvk, kvv, [p0], rows=rows)[0]
-        assert_close(got, want, f"sequence split world={world} p0={p0} rows={rows}")
+        assert_close(got, want, f"sequence split ({exchange}) world={world} p0={p0} rows={rows}")
+
+
+@pytest.mark.parametrize("exchange", ["push", "nccl"])
+def test_sequence_split_decode(exchange):
+    world = min(torch.cuda.device_count(), 4)
+    n_total = 4000
+    # the same shape twice in a row: the second and third use run from the captured graph
+    cases = [(n_total - 1, 1), (n_total - 1, 1), (n_total - 1, 1), (n_total - 4, 4), (n_total // max(world, 1) - 2, 2),
+             (0, 1), (n_total - 4, 4), (n_total - 4, 4)]
+    _run(n_total, cases, exchange)
+
+
+def test_eight_rows_on_deep_shards():
+    """rows = 8 (the wide verify kernel, 32 (row, head) pairs per KV head) on shards of more than 4K positions:
+    the scratch must be sized for this shape on the rank that holds the block and for 8 one-row sequences elsewhere."""
+    n_total = 20000
+    _run(n_total, [(n_total - 8, 8), (n_total - 8, 8), (n_total - 8, 8)], "push", seed=37)
+
+
+def test_a_rank_that_sits_out_a_step_times_out_its_peers_and_the_next_step_recovers():
+    n_total = 3000
+    _run(n_total, [(n_total - 1, 1), (n_total - 1, 1), (n_total - 2, 2), (n_total - 1, 1)], "push", skip_case=1, seed=41)

@@ -151,5 +151,7 @@ def test_scratch_sized_for_512_rows_serves_every_shorter_chunk(name):
         eng.attn_exact(ref, q, kvk, kvv, pos, ws, 1, rows, 4, False)
         torch.cuda.synchronize()
         assert bool((buf[size:] == 0xA5).all()), f"a {rows}-row chunk wrote past the end of the scratch buffer"
-        assert_close(to_np(out), to_np(ref), f"{name} {rows}-row chunk on the 512-row scratch", head_tol=PROMPT_HEAD_REL_TOL)
+        # (a sanity check of the result next to the guard check, against the fp32 device path rather than the
+        # oracle: max-abs and the 2-norm ratios; the max-norm gate belongs to the oracle comparisons above)
+        assert_close(to_np(out), to_np(ref), f"{name} {rows}-row chunk on the 512-row scratch", maxnorm=False)
     assert eng.device_status() == 0
