@@ -239,7 +239,6 @@ int launch_flash(battn_handle* h, void* out, float* rec_out, const void* q, cons
         else             e = idx == 0 ? launch_fd_kernel<256, 1>(P, grid, smem, st) : launch_fd_kernel<256, 2>(P, grid, smem, st);
     }
     if (e != cudaSuccess) return cuda_fail(h, e);
-
     MergeParams M{};
     M.mode = 0; M.part = P.part; M.out = out; M.rec_out = rec_out;
     M.n_rows = n_seq * rows; M.rows = rows; M.Hq = g.Hq; M.Hkv = g.Hkv; M.G = g.G;
