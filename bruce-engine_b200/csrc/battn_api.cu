@@ -13,6 +13,7 @@
 #include "prefill.cuh"
 #include "prefill_hd128.cuh"
 #include "verify.cuh"
+#include "verify_tc.cuh"
 
 using namespace battn;
 
@@ -76,6 +77,10 @@ template <int HD>
 cudaError_t fd_prepare_all(battn_handle* h) {
     cudaError_t e;
     if ((e = vw_prepare<HD>(h)) != cudaSuccess) return e;
+    if (HD == 128) {
+        e = cudaFuncSetAttribute((const void*)vt::k_verify_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX);
+        if (e != cudaSuccess) return e;
+    }
     if (HD == 128) e = cudaFuncSetAttribute((const void*)pf128::k_prefill_hd128, cudaFuncAttributeMaxDynamicSharedMemorySize, pf128::TOTAL);
     else           e = cudaFuncSetAttribute((const void*)pf::k_prefill<256, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, pf::Cfg<256, 64>::TOTAL);
     if (e != cudaSuccess) return e;
@@ -214,7 +219,12 @@ int launch_flash(battn_handle* h, void* out, float* rec_out, const void* q, cons
     P.epoch_ptr = epoch_ptr; P.epoch_advance = epoch_advance;
 
     cudaError_t e;
-    if (RG > 16) {
+    if (RG > 16 && g.HD == 128 && g.W >= 64 && vt::smem_bytes(n_seq) <= SMEM_MAX) {
+        // 5..8 rows at head_dim 128: the tensor-memory verify kernel, one CTA per SM (128-key tiles must not wrap the
+        // ring, hence the window bound; very large batches exceed its shared memory and take the kernel below)
+        ProfScope prof(h, st);
+        e = launch_pdl(vt::k_verify_tc, dim3(h->num_sms), dim3(vt::NTHREADS), vt::smem_bytes(n_seq), st, P);
+    } else if (RG > 16) {
         // 5..8 rows: the wide verify kernel (each warp owns 8 pairs over all keys of a tile)
         const size_t smem = g.HD == 128 ? vw::smem_bytes<128>(n_seq) : vw::smem_bytes<256>(n_seq);
         if (smem > SMEM_MAX) return BATTN_ERR_CAPACITY;
