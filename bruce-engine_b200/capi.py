@@ -45,6 +45,8 @@ SIGNATURES = {
     "battn_decode_noalloc": (_I, [_P] * 8 + [_I, _I, _P]),
     "battn_verify": (_I, [_P] * 9 + [_I, _I, _I, _P]),
     "battn_prefill": (_I, [_P] * 7 + [_I, _I, _P]),
+    "battn_gate_norm": (_I, [_P] * 8 + [_I, _P]),
+    "battn_prefill_gate_norm": (_I, [_P] * 12 + [_I, _I, _P]),
     "battn_attend_exact": (_I, [_P] * 9 + [_I, _I, _I, _I, _P]),
     "battn_partials": (_I, [_P] * 9 + [_I, _I, _I, _P]),
     "battn_merge": (_I, [_P, _P, _P, _I, _I, _P]),

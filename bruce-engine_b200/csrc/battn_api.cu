@@ -8,6 +8,7 @@
 #include "common.cuh"
 #include "exact.cuh"
 #include "flash_decode.cuh"
+#include "gate_norm.cuh"
 #include "kv_append.cuh"
 #include "qkv_prep.cuh"
 #include "prefill.cuh"
@@ -263,7 +264,7 @@ int launch_flash(battn_handle* h, void* out, float* rec_out, const void* q, cons
 
 // prompt chunk on the tcgen05 kernel: one CTA per (128-row M tile, kv head), normalised output
 int launch_prefill(battn_handle* h, void* out, const void* q, const uint8_t* kvk, const uint8_t* kvv, const int* pos,
-                   void* ws, int rows, int is_swa, cudaStream_t st) {
+                   void* ws, int rows, int is_swa, cudaStream_t st, const GateNormParams* gn = nullptr) {
     const Geom& g = h->g;
     if (128 % g.G) return BATTN_ERR_ARG;
     pf::Params P;
@@ -274,7 +275,7 @@ int launch_prefill(battn_handle* h, void* out, const void* q, const uint8_t* kvk
     P.scale_log2 = g.scale * LOG2E; P.status = h->d_status;
     const int MR = 128 / g.G;
     P.nsplit = prefill_splits(h, rows, is_swa);
-    P.recs = P.nsplit > 1 ? reinterpret_cast<float*>(ws) : nullptr;
+    P.recs = (P.nsplit > 1 || gn) ? reinterpret_cast<float*>(ws) : nullptr;
     const dim3 grid((rows + MR - 1) / MR, g.Hkv, P.nsplit);
     {
         ProfScope prof(h, st);
@@ -283,6 +284,16 @@ int launch_prefill(battn_handle* h, void* out, const void* q, const uint8_t* kvk
     }
     h->launches += 1;
     cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess && gn) {
+        // the fused epilogue: merge of the split records, sigmoid gate, L2 norm and q8 copy, one block per row
+        GateNormParams G = *gn;
+        G.recs = P.recs; G.nsplit = P.nsplit; G.rows = rows; G.Hq = g.Hq; G.n = g.Hq * g.HD;
+        if (g.HD == 128) e = launch_pdl(k_merge_gate_norm<128>, dim3(rows), dim3(256), 0, st, G);
+        else             e = launch_pdl(k_merge_gate_norm<256>, dim3(rows), dim3(256), 0, st, G);
+        h->launches += 1;
+        if (e == cudaSuccess) e = cudaGetLastError();
+        return e == cudaSuccess ? BATTN_OK : cuda_fail(h, e);
+    }
     if (e == cudaSuccess && P.nsplit > 1) {
         MergeParams M{};
         M.mode = MERGE_GATHERED; M.part = P.recs; M.out = out; M.rec_out = nullptr;
@@ -534,6 +545,40 @@ int battn_prefill(battn_handle* h, void* out, const void* q, const uint8_t* kvk,
     if (rows * h->g.G <= 32)
         return launch_flash(h, out, nullptr, q, kvk, kvv, pos, nullptr, nullptr, ws, 1, rows, is_swa, (cudaStream_t)stream);
     return launch_prefill(h, out, q, kvk, kvv, pos, ws, rows, is_swa, (cudaStream_t)stream);
+}
+
+int battn_gate_norm(battn_handle* h, float* dst, const void* aout, const float* gate, const float* sgate, int8_t* xq,
+                    float* xd, int* xsum, int rows, void* stream) {
+    if (!h || !aout || !gate || !sgate || !xq || !xd || !xsum || rows < 1) return BATTN_ERR_ARG;
+    if ((((uintptr_t)dst | (uintptr_t)aout | (uintptr_t)gate | (uintptr_t)sgate | (uintptr_t)xq) & 15) != 0) return BATTN_ERR_ARG;
+    const Geom& g = h->g;
+    const int n = g.Hq * g.HD;
+    if (n % 1024 || n > 4096) return BATTN_ERR_ARG;
+    GateNormParams G{};
+    G.dst = dst; G.aout = aout; G.aout_f16 = g.out_f16; G.gate = gate; G.sgate = sgate; G.xq = xq; G.xd = xd; G.xsum = xsum;
+    G.n = n;
+    cudaError_t e = launch_pdl(k_gate_norm, dim3(rows), dim3(256), 0, (cudaStream_t)stream, G);
+    h->launches += 1;
+    if (e == cudaSuccess) e = cudaGetLastError();
+    return e == cudaSuccess ? BATTN_OK : cuda_fail(h, e);
+}
+
+int battn_prefill_gate_norm(battn_handle* h, float* dst, const void* q, const uint8_t* kvk, const uint8_t* kvv,
+                            const int* pos, void* ws, const float* gate, const float* sgate, int8_t* xq, float* xd,
+                            int* xsum, int rows, int is_swa, void* stream) {
+    const int rc = check_seq_args(h, q, q, kvk, kvv, pos, nullptr, 1, rows, MAX_PREFILL);
+    if (rc) return rc;
+    if (!ws || ((uintptr_t)ws & 15) || !gate || !sgate || !xq || !xd || !xsum) return BATTN_ERR_ARG;
+    if ((((uintptr_t)dst | (uintptr_t)gate | (uintptr_t)sgate | (uintptr_t)xq) & 15) != 0) return BATTN_ERR_ARG;
+    const Geom& g = h->g;
+    const int n = g.Hq * g.HD;
+    if (n % 1024 || n > 4096 || g.Hq > 32) return BATTN_ERR_ARG;
+    if (rows * g.G <= 32) return BATTN_ERR_ARG;              // short calls: battn_decode / battn_verify, then battn_gate_norm
+    if (is_swa && rows > g.W) return BATTN_ERR_CAPACITY;
+    if (g.W < 64) return BATTN_ERR_ARG;
+    GateNormParams G{};
+    G.dst = dst; G.gate = gate; G.sgate = sgate; G.xq = xq; G.xd = xd; G.xsum = xsum;
+    return launch_prefill(h, nullptr, q, kvk, kvv, pos, ws, rows, is_swa, (cudaStream_t)stream, &G);
 }
 
 int battn_attend_exact(battn_handle* h, void* out, const void* q, const uint8_t* kvk, const uint8_t* kvv,

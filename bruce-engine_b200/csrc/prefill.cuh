@@ -64,7 +64,9 @@ struct Params {
     float scale_log2;
     int* status;
     // key split: gridDim.z CTAs share one (M tile, kv head), each takes a contiguous share of the key tiles and
-    // writes split records [split][row][head][HD+2] = (unnormalised o, m in log2 units, l) for the merge kernel
+    // writes split records [split][row][head][HD+2] = (unnormalised o, m in log2 units, l) for the merge kernel;
+    // recs != null with nsplit == 1 leaves the single record per row in place of the output (for the fused
+    // merge + gate-norm epilogue)
     int nsplit;
     float* recs;
 };
@@ -705,7 +707,7 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill(const Params P) {
         }
         const float il = l > 0.f ? 1.f / l : 0.f;
         const size_t oi = (((size_t)(rbase + r)) * P.Hq + kvh * G + h) * HD + half * (HD / 2);
-        float* rec = P.nsplit > 1 ? P.recs + ((((size_t)blockIdx.z * P.rows) + rbase + r) * P.Hq + kvh * G + h) * (size_t)(HD + 2)
+        float* rec = P.recs ? P.recs + ((((size_t)blockIdx.z * P.rows) + rbase + r) * P.Hq + kvh * G + h) * (size_t)(HD + 2)
                                   : nullptr;
         if (rec && row_ok && half == 0) {
             rec[HD] = m_ref > 0.5f * NEG_BIG ? m_ref * c2 : NEG_BIG;

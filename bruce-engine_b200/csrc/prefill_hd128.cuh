@@ -506,7 +506,7 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill_hd128(const Params P) {
         const float il = l > 0.f ? 1.f / l : 0.f;
         const size_t oi = (((size_t)(rbase + r)) * P.Hq + kvh * G + h) * HD + grp * (HD / 2);
         // with key splits: a split record (unnormalised o, m in log2 units, l) instead of the output row
-        float* rec = P.nsplit > 1 ? P.recs + ((((size_t)blockIdx.z * P.rows) + rbase + r) * P.Hq + kvh * G + h) * (size_t)(HD + 2)
+        float* rec = P.recs ? P.recs + ((((size_t)blockIdx.z * P.rows) + rbase + r) * P.Hq + kvh * G + h) * (size_t)(HD + 2)
                                   : nullptr;
         if (rec && row_ok && grp == 0) {
             const float mr = mref[m];

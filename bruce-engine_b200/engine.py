@@ -169,6 +169,20 @@ class AttnEngine:
         rc = self.lib.battn_merge(self.h, _ptr(out), _ptr(parts), n_parts, n_rows, self._stream())
         self._check("battn_merge", rc)
 
+    # ---- the step after attention ------------------------------------------------------------------------
+    def gate_norm(self, dst, aout, gate, sgate, xq, xd, xsum, rows: int):
+        """k_gate_norm_vec4 (bruce.cu:1526): sigmoid gate, L2 norm, q8 activation copy; dst may be None."""
+        rc = self.lib.battn_gate_norm(self.h, _ptr(dst), _ptr(aout), _ptr(gate), _ptr(sgate), _ptr(xq), _ptr(xd),
+                                      _ptr(xsum), rows, self._stream())
+        self._check("battn_gate_norm", rc)
+
+    def prefill_gate_norm(self, dst, q, kvk, kvv, pos, part, gate, sgate, xq, xd, xsum, rows: int, is_swa: bool = False):
+        """Prompt-chunk attention fused with the gate-norm step (k_combine_gate_norm_rows_opt, bruce.cu:1577)."""
+        rc = self.lib.battn_prefill_gate_norm(self.h, _ptr(dst), _ptr(q), _ptr(kvk), _ptr(kvv), _ptr(pos), _ptr(part),
+                                              _ptr(gate), _ptr(sgate), _ptr(xq), _ptr(xd), _ptr(xsum), rows, int(is_swa),
+                                              self._stream())
+        self._check("battn_prefill_gate_norm", rc)
+
     # ---- one sequence split by position range across devices ----------------------------------------
     def xchg_create(self, rank: int, world: int, max_rows: int = 8):
         """This device's receive area for the cross-device exchange of split records.  Returns (exchange, its

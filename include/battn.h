@@ -201,6 +201,26 @@ int battn_verify(battn_handle* h, void* out, const void* q, const uint8_t* kvk, 
 int battn_prefill(battn_handle* h, void* out, const void* q, const uint8_t* kvk, const uint8_t* kvv,
                   const int* pos, void* ws, int rows, int is_swa, void* stream);
 
+/* The step after attention: sigmoid gate, L2 norm over the token's whole attention vector and the q8 activation copy
+ * for the output projection -- k_gate_norm_vec4 (bruce.cu:1526-1568; calls :7746-7755, :7975).  Per token row m with
+ * n = n_head * head_dim (a multiple of 1024, at most 4096):
+ *     t = aout / (1 + __expf(-(gate * sgate))),  k = l2_scale(sum t^2, n) (:305-307),  v = t * k
+ *     per 32 values: d = amax * (1/127), q = clamp(rint(v / d), -127, 127)   (the ACTIVATION quantiser, :1405-1428)
+ *   aout  [rows][n] in out_dtype        gate [rows][n] fp32        sgate [n] fp32
+ *   dst   [rows][n] fp32 or NULL        xq [rows][n] int8          xd [rows][n/32] fp32      xsum [rows][n/32] int32
+ * Sums are formed in the reference kernel's order: for fp32 aout the outputs are bit-identical to k_gate_norm_vec4's. */
+int battn_gate_norm(battn_handle* h, float* dst, const void* aout, const float* gate, const float* sgate, int8_t* xq,
+                    float* xd, int* xsum, int rows, void* stream);
+
+/* Prompt-chunk attention fused with that step: battn_prefill whose result never goes to memory as an attention
+ * output -- the chunk's split records are merged, gated, normalised and quantised by one block per token row, as
+ * the reference's k_combine_gate_norm_rows_opt does with its own records (bruce.cu:1577-1639, call :7743).
+ * Arguments as battn_prefill (without `out`) and battn_gate_norm (without `aout`); rows * (n_head / n_kv) > 32
+ * (shorter calls: battn_decode / battn_verify followed by battn_gate_norm). */
+int battn_prefill_gate_norm(battn_handle* h, float* dst, const void* q, const uint8_t* kvk, const uint8_t* kvv,
+                            const int* pos, void* ws, const float* gate, const float* sgate, int8_t* xq, float* xd,
+                            int* xsum, int rows, int is_swa, void* stream);
+
 /* The exact fp32 path: per-key online softmax in fp32 with no tensor cores, the same arithmetic as
  * k_attn / k_attn_rows / k_attn_m (bruce.cu:713-785, 1921-1997, 2087-2143) followed by
  * k_attn_combine_rows (:1999-2016).  Any rows_per_seq >= 1.  `nsplit` (1..128) is the reference's

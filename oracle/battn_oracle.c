@@ -418,3 +418,80 @@ int oracle_num_threads(void) {
     return 1;
 #endif
 }
+
+/* ---- the step after attention: sigmoid gate, L2 norm, q8 activation copy ----
+ * k_gate_norm_vec4 (bruce.cu:1526-1568) with its helpers l2_scale (:305-307), block_red_n<8> (:1252-1265),
+ * warp_sum (:263-267) and q8_group_vec4 (:1405-1428).  Per token row m, n = n_head * head_dim values:
+ *     t = a / (1 + exp(-(gate * sgate)));  k = l2_scale(sum t^2, n);  v = t * k -> dst
+ *     per 32 values: d = amax * (1/127), id = d > 0 ? 1/d : 0, q = clamp(rint(v * id), -127, 127)
+ * The partial sums are formed in the kernel's order: thread i (of 256) owns the float4 i + 256 b, adds
+ * (x^2 + y^2) + (z^2 + w^2) per float4 with the products contracted the way nvcc contracts them, then the
+ * shuffle-down trees.  One thing cannot be restated on a CPU: the kernel's exponential is the GPU's approximate
+ * ex2 unit (__expf), this one is expf; values agree to a few ulp, so quantised bytes may differ by one step where a
+ * value sits on a rounding boundary (the tests bound both).
+ * aout fp32 [rows][n]; dst may be NULL. */
+static float gn_tree_down(float* v, int count) {
+    /* v += shfl_down(v, o) for o = 16 .. 1 over `count` lanes (lanes beyond read their own value: unused results) */
+    float t[32];
+    for (int i = 0; i < 32; ++i) t[i] = i < count ? v[i] : 0.f;
+    for (int o = 16; o > 0; o >>= 1) {
+        float nx[32];
+        for (int i = 0; i < 32; ++i) nx[i] = t[i] + (i + o < 32 ? t[i + o] : t[i]);
+        for (int i = 0; i < 32; ++i) t[i] = nx[i];
+    }
+    return t[0];
+}
+
+int oracle_gate_norm(int n, int rows, const float* aout, const float* gate, const float* sgate, float* dst,
+                     int8_t* xq, float* xd, int* xsum) {
+    if (n % 1024 || n > 4096) return 1;
+    const int nb = n / 1024;
+    float* t = (float*)malloc(sizeof(float) * (size_t)n);
+    for (int m = 0; m < rows; ++m) {
+        const float* a = aout + (size_t)m * n;
+        const float* g = gate + (size_t)m * n;
+        for (int i = 0; i < n; ++i) {
+            const float gx = g[i] * sgate[i];
+            t[i] = a[i] / (1.f + expf(-gx));
+        }
+        float wsum[8];
+        for (int w = 0; w < 8; ++w) {
+            float lane_ss[32];
+            for (int l = 0; l < 32; ++l) {
+                const int tid = w * 32 + l;
+                float ss = 0.f;
+                for (int b = 0; b < nb; ++b) {
+                    const float* e = t + 4 * (tid + 256 * b);
+                    const float p = fmaf(e[0], e[0], e[1] * e[1]);
+                    const float q = fmaf(e[2], e[2], e[3] * e[3]);
+                    ss += p + q;
+                }
+                lane_ss[l] = ss;
+            }
+            wsum[w] = gn_tree_down(lane_ss, 32);
+        }
+        const float ss = gn_tree_down(wsum, 8);
+        const float k = (1.0f / sqrtf(ss / (float)n + 1e-6f / (float)n)) * (1.0f / sqrtf((float)n));
+        for (int grp = 0; grp < n / 32; ++grp) {
+            float v[32], amax = 0.f;
+            for (int i = 0; i < 32; ++i) {
+                v[i] = t[grp * 32 + i] * k;
+                if (dst) dst[(size_t)m * n + grp * 32 + i] = v[i];
+                amax = fmaxf(amax, fabsf(v[i]));
+            }
+            const float d = amax * (1.f / 127.f);
+            const float id = d > 0.f ? 1.f / d : 0.f;
+            int s = 0;
+            for (int i = 0; i < 32; ++i) {
+                int q = (int)nearbyintf(v[i] * id);
+                q = q > 127 ? 127 : (q < -127 ? -127 : q);
+                xq[(size_t)m * n + grp * 32 + i] = (int8_t)q;
+                s += q;
+            }
+            xd[(size_t)m * (n / 32) + grp] = d;
+            xsum[(size_t)m * (n / 32) + grp] = s;
+        }
+    }
+    free(t);
+    return 0;
+}

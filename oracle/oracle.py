@@ -87,6 +87,8 @@ def lib():
         L.oracle_qkv_prep.restype = C.c_int
         L.oracle_qkv_prep.argtypes = ([C.POINTER(_Geom)] + [C.c_void_p] * 6 + [C.c_int] + [C.c_void_p] * 5 +
                                       [C.c_int] * 3)
+        L.oracle_gate_norm.restype = C.c_int
+        L.oracle_gate_norm.argtypes = [C.c_int, C.c_int] + [C.c_void_p] * 7
         L.oracle_attend.restype = C.c_int
         L.oracle_attend.argtypes = [C.POINTER(_Geom)] + [C.c_void_p] * 8 + [C.c_int] * 6
         L.oracle_attend_f32.restype = C.c_int
@@ -161,6 +163,23 @@ def rope_tables(head_dim: int, positions) -> tuple:
     cs = np.concatenate([np.cos(th1), np.cos(th2)], axis=1).astype(np.float32)
     sn = np.concatenate([np.sin(th1), np.sin(th2)], axis=1).astype(np.float32)
     return cs, sn
+
+
+def gate_norm(aout, gate, sgate):
+    """k_gate_norm_vec4 (bruce.cu:1526) restated: aout, gate float32 [rows][n], sgate [n] ->
+    (dst float32 [rows][n], xq int8 [rows][n], xd float32 [rows][n/32], xsum int32 [rows][n/32])."""
+    aout = np.ascontiguousarray(aout, dtype=np.float32)
+    gate = np.ascontiguousarray(gate, dtype=np.float32)
+    sgate = np.ascontiguousarray(sgate, dtype=np.float32)
+    rows, n = aout.shape
+    dst = np.zeros((rows, n), np.float32)
+    xq = np.zeros((rows, n), np.int8)
+    xd = np.zeros((rows, n // 32), np.float32)
+    xsum = np.zeros((rows, n // 32), np.int32)
+    rc = lib().oracle_gate_norm(n, rows, _p(aout), _p(gate), _p(sgate), _p(dst), _p(xq), _p(xd), _p(xsum))
+    if rc:
+        raise ValueError(f"oracle_gate_norm failed: {rc}")
+    return dst, xq, xd, xsum
 
 
 def attend(g: Geom, q, kvk, kvv, pos, kslot=None, act=None, rows=1, is_swa=False,

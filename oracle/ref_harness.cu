@@ -72,6 +72,14 @@ int ref_attn_exact(float* out, const float* q, const uint8_t* kvk, const uint8_t
     return ref_sync_status();
 }
 
+// The reference's gate-norm step after attention, k_gate_norm_vec4 (bruce.cu:1526): sigmoid gate, L2 norm over the
+// token's N_HEAD*HD values, q8 activation copy.  dst may be null.
+int ref_gate_norm(float* dst, const float* aout, const float* gate, const float* sg, int8_t* xq, float* xd, int* xs,
+                  int rows) {
+    k_gate_norm_vec4<<<rows, 256>>>(dst, aout, gate, sg, N_HEAD * HD, xq, xd, xs);
+    return ref_sync_status();
+}
+
 // The reference's shipping dispatch, launch_attn_m (bruce.cu:3942) + k_attn_combine_rows: tensor-core
 // kernels with fp16 accumulation.  Returns the elapsed milliseconds of `reps` back-to-back calls in *ms.
 int ref_attn_shipping(float* out, const float* q, const uint8_t* kvk, const uint8_t* kvv, const int* d_pos,
