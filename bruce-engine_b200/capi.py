@@ -39,6 +39,7 @@ SIGNATURES = {
     "battn_call_workspace_bytes": (_I, [C.POINTER(CGeom), _I, _I, _I, _SZP]),
     "battn_exact_workspace_bytes": (_I, [_P, _I, _I, _I, _SZP]),
     "battn_kv_append": (_I, [_P] * 8 + [_I, _I, _I, _P]),
+    "battn_kv_copy_prefix": (_I, [_P, _P, _P, _I, _I, _I, _I, _P]),
     "battn_qkv_prep": (_I, [_P] * 8 + [_I] + [_P] * 5 + [_I, _I, _I, _P]),
     "battn_rope_tables": (_I, [_P] * 4 + [_I, _I, _P]),
     "battn_decode": (_I, [_P] * 9 + [_I, _I, _P]),

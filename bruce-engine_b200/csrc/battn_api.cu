@@ -2,6 +2,7 @@
 // No allocation, synchronisation or host read of device state happens inside the per-step entry
 // points, so they can be recorded into CUDA graphs like the reference's launches
 // (engine/src/bruce.cu:7877-7900, 8046-8055).
+#include <algorithm>
 #include <cstring>
 #include <new>
 
@@ -454,6 +455,24 @@ int battn_kv_append(battn_handle* h, const float* k, const float* v, uint8_t* kv
     cudaError_t e;
     if (g.HD == 128) e = launch_pdl(k_kv_append<128>, dim3(blocks), dim3(256), 0, st, P);
     else             e = launch_pdl(k_kv_append<256>, dim3(blocks), dim3(256), 0, st, P);
+    h->launches += 1;
+    if (e == cudaSuccess) e = cudaGetLastError();
+    return e == cudaSuccess ? BATTN_OK : cuda_fail(h, e);
+}
+
+int battn_kv_copy_prefix(battn_handle* h, uint8_t* kvk, uint8_t* kvv, int src_slot, int dst_slot, int n_pos, int is_swa,
+                         void* stream) {
+    if (!h || !kvk || !kvv || ((((uintptr_t)kvk | (uintptr_t)kvv)) & 15)) return BATTN_ERR_ARG;
+    const Geom& g = h->g;
+    if (src_slot < 0 || dst_slot < 0 || src_slot >= g.n_slots || dst_slot >= g.n_slots || src_slot == dst_slot) return BATTN_ERR_ARG;
+    if (n_pos < 0 || (!is_swa && n_pos > g.slot_ctx)) return BATTN_ERR_CAPACITY;
+    if (n_pos == 0) return BATTN_OK;
+    CopyParams P;
+    P.kvk = kvk; P.kvv = kvv; P.src = src_slot; P.dst = dst_slot; P.n_pos = n_pos; P.Hkv = g.Hkv; P.rec = g.rec;
+    P.pstride = is_swa ? g.ring : g.slot_ctx; P.ring = is_swa ? g.ring : 0;
+    const int copied = is_swa && n_pos > g.ring ? g.ring : n_pos;
+    const int bx = (int)std::min<size_t>(64, ((size_t)copied * g.rec / 16 + 255) / 256 + 1);
+    cudaError_t e = launch_pdl(k_kv_copy_prefix, dim3(bx, g.Hkv, 2), dim3(256), 0, (cudaStream_t)stream, P);
     h->launches += 1;
     if (e == cudaSuccess) e = cudaGetLastError();
     return e == cudaSuccess ? BATTN_OK : cuda_fail(h, e);

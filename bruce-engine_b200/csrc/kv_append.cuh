@@ -72,4 +72,42 @@ __global__ void __launch_bounds__(256) k_kv_append(const AppendParams P) {
     }
 }
 
+// Prefix sharing between slots: the first n_pos cached positions of slot `src` copied into slot `dst` of the same
+// layer buffer, K and V, every kv head (a request whose prompt starts like another slot's cache skips that part of
+// its prompt).  Records are position-contiguous per kv head, so this is n_kv contiguous runs per tensor, moved
+// with 16-byte loads.  Full-attention layers copy [0, n_pos); a sliding-window layer copies the ring slots of
+// the last min(n_pos, 2W) positions (p & (2W - 1) is the same slot in both partitions).
+struct CopyParams {
+    uint8_t* kvk;
+    uint8_t* kvv;
+    int src, dst, n_pos, Hkv, rec, pstride, ring;      // ring = 2W on a sliding-window layer, else 0
+};
+
+__global__ void __launch_bounds__(256) k_kv_copy_prefix(const CopyParams P) {
+    pdl_wait();
+    pdl_trigger();
+    const int first = P.ring ? max(0, P.n_pos - P.ring) : 0;                   // first position to copy
+    const size_t run = (size_t)(P.n_pos - first) * P.rec;                      // bytes per kv head when contiguous
+    const int kvh = blockIdx.y;
+    uint8_t* base = blockIdx.z ? P.kvv : P.kvk;
+    const size_t so = ((size_t)P.src * P.Hkv + kvh) * P.pstride * (size_t)P.rec;
+    const size_t dof = ((size_t)P.dst * P.Hkv + kvh) * P.pstride * (size_t)P.rec;
+    if (!P.ring) {
+        // [0, n_pos) is one run: 16-byte chunks (the partition base is 16-byte aligned), then the odd tail bytes
+        const size_t n16 = run >> 4;
+        for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (size_t)gridDim.x * blockDim.x)
+            reinterpret_cast<uint4*>(base + dof)[i] = reinterpret_cast<const uint4*>(base + so)[i];
+        if (blockIdx.x == 0 && threadIdx.x < (int)(run & 15)) base[dof + (n16 << 4) + threadIdx.x] = base[so + (n16 << 4) + threadIdx.x];
+    } else {
+        // ring slots of positions [first, n_pos): 8-byte words (a record is a multiple of 8 bytes)
+        const int w8 = P.rec >> 3;
+        const size_t total = (size_t)(P.n_pos - first) * w8;
+        for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+            const int p = first + (int)(i / w8), wi = (int)(i % w8);
+            const size_t off = (size_t)(p & (P.ring - 1)) * P.rec + (size_t)wi * 8;
+            *reinterpret_cast<uint2*>(base + dof + off) = *reinterpret_cast<const uint2*>(base + so + off);
+        }
+    }
+}
+
 }  // namespace battn

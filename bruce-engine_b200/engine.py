@@ -97,6 +97,11 @@ class AttnEngine:
             self.h, _ptr(k), _ptr(v), _ptr(kvk), _ptr(kvv), _ptr(pos), _ptr(kslot), _ptr(act),
             n_seq, rows, int(is_swa), self._stream()))
 
+    def kv_copy_prefix(self, kvk, kvv, src_slot: int, dst_slot: int, n_pos: int, is_swa: bool = False):
+        """Prefix sharing between slots: the first n_pos cached positions of src_slot copied into dst_slot."""
+        self._check("battn_kv_copy_prefix", self.lib.battn_kv_copy_prefix(
+            self.h, _ptr(kvk), _ptr(kvv), src_slot, dst_slot, n_pos, int(is_swa), self._stream()))
+
     def qkv_prep(self, q_out, q, k, v, sqk, cs, sn, kvk, kvv, pos, kslot=None, act=None, rows: int = 1,
                  is_swa: bool = False, theta_sel: int = 1):
         """The whole k_qkv_prep_fast / k_qkv_prep_fast_ms step (bruce.cu:1732-1812, 1835-1918): L2 scale + RoPE

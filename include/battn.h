@@ -117,6 +117,16 @@ int battn_kv_append(battn_handle* h, const float* k, const float* v, uint8_t* kv
                     const int* pos, const int* kslot, const int* act,
                     int n_seq, int rows_per_seq, int is_swa, void* stream);
 
+/* Prefix sharing between slots: copies the cache of the first n_pos positions of partition src_slot into partition
+ * dst_slot of the same layer (K and V, every kv head), so that a request whose prompt begins like another slot's
+ * cached conversation starts its prompt at n_pos.  The reference reuses a prefix only inside ONE slot
+ * (Session::cache_hit, engine/src/session.h:337-346, with the slot chosen by affinity, server.h:376-396); with its
+ * contiguous per-slot partitions (bruce.cu:5471-5503) sharing across slots is a copy, and this is that copy.
+ * kvk, kvv: the LAYER base pointers.  On a sliding-window layer the ring slots of the last min(n_pos, 2*window)
+ * positions are copied.  Bytes are copied verbatim: the destination's records equal the source's. */
+int battn_kv_copy_prefix(battn_handle* h, uint8_t* kvk, uint8_t* kvv, int src_slot, int dst_slot, int n_pos, int is_swa,
+                         void* stream);
+
 /* QKV prologue fused with the append, one launch: everything k_qkv_prep (bruce.cu:645-710),
  * k_qkv_prep_rows (:1656-1725), k_qkv_prep_fast (:1732-1812) and k_qkv_prep_fast_ms (:1835-1918) do.
  * Per row m = i*rows_per_seq + r (sequence i, row r, position pos[i] + r) and per head:
