@@ -105,6 +105,20 @@ static inline void launch_attn_ms(float* out, const float* q, const uint8_t* kvk
     BATTN_CK(battn_decode(g_battn, out, q, kvk, kvv, pos, kslot, act, part, rows, is_swa, st));
 }
 
+/* k_gate_norm_vec4 as launched at bruce.cu:7746-7755 and :7975 (the host's ns == 1 branch, which this library's
+ * normalised outputs always take): sigmoid gate, L2 norm, q8 copy of `rows` attention rows; dst may be null */
+static inline void gate_norm_rows(float* dst, const float* aout, const float* gate, const float* sgate, int8_t* xq,
+                                  float* xd, int* xsum, int rows, cudaStream_t st) {
+    BATTN_CK(battn_gate_norm(g_battn, dst, aout, gate, sgate, xq, xd, xsum, rows, st));
+}
+/* launch_attn_m(rows > 8) followed by k_combine_gate_norm_rows_opt<16> (bruce.cu:7729-7743) in one call: the
+ * prompt chunk's attention output never goes to memory */
+static inline void attn_gate_norm_rows(const float* q, const uint8_t* kvk, const uint8_t* kvv, const int* pos, float* part,
+                                       const float* gate, const float* sgate, int8_t* xq, float* xd, int* xsum, int rows,
+                                       int is_swa, cudaStream_t st) {
+    BATTN_CK(battn_prefill_gate_norm(g_battn, nullptr, q, kvk, kvv, pos, part, gate, sgate, xq, xd, xsum, rows, is_swa, st));
+}
+
 /* --prefill-tc 0 / BRUCE_ATTN_M1PATH=0: the exact fp32 path, k_attn_rows + k_attn_combine_rows
  * (bruce.cu:7735, 7753) */
 static inline void launch_attn_exact(float* out, const float* q, const uint8_t* kvk, const uint8_t* kvv,

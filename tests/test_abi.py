@@ -80,7 +80,9 @@ def test_reference_shim_header_compiles():
                     "void use(float* o, const float* q, const uint8_t* k, const uint8_t* v, const int* p, float* part,\n"
                     "         cudaStream_t st) { launch_attn_m(o, q, k, v, p, part, 1, 56, 0, st);\n"
                     "  launch_attn_ms(o, q, k, v, p, p, p, part, 8, 7, 1, st); launch_attn_exact(o, q, k, v, p, part, 4, 8, 0, st);\n"
-                    "  launch_attn_m(o, q, k, v, p, part, 8, 28, 0, st); launch_attn_m(o, q, k, v, p, part, 512, 2, 1, st); }\n")
+                    "  launch_attn_m(o, q, k, v, p, part, 8, 28, 0, st); launch_attn_m(o, q, k, v, p, part, 512, 2, 1, st);\n"
+                    "  gate_norm_rows(nullptr, o, q, q, (int8_t*)o, o, (int*)o, 4, st);\n"
+                    "  attn_gate_norm_rows(q, k, v, p, part, q, q, (int8_t*)o, o, (int*)o, 512, 0, st); }\n")
         r = subprocess.run([nvcc, "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-I",
                             os.path.join(ROOT, "include"), "-c", src, "-o", os.path.join(d, "shim_check.o")],
                            capture_output=True, text=True)

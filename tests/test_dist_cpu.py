@@ -104,3 +104,73 @@ def test_sequence_split_decode_over_gloo_ranks(world):
             p.join(timeout=60)
             assert p.exitcode == 0
         assert np.abs(got - want).max() < 1e-5
+
+
+# ---- the exchange protocol of the sequence split (epoch flags, parity buffers, bounded wait) among CPU ranks ----------
+def _xchg_worker(rank, world, port, ret):
+    """Four steps of a 3-rank group.  Step 2: the last rank sits out (its peers time out, it catches up with
+    advance = 2).  Step 3: rank 0's push to rank 1 is dropped (only rank 1 times out).  Steps 1 and 4: everybody
+    merges the same records."""
+    store = dist.TCPStore("127.0.0.1", port, world, is_master=(rank == 0), timeout=__import__("datetime").timedelta(seconds=30))
+    x = bd.HostExchange(store, rank, world, wait_s=0.4)
+    store.set(f"ready/{rank}", "1")
+    store.wait([f"ready/{r}" for r in range(world)])
+    H, HD = 4, 8
+    log = []
+
+    def record(step):
+        rng = np.random.default_rng(1000 * step + rank)
+        rec = rng.standard_normal((1, H, HD + 2)).astype(np.float32)
+        rec[..., HD + 1] = np.abs(rec[..., HD + 1]) + 0.5          # l > 0
+        return rec
+
+    def fix_l(a):
+        a = a.copy(); a[..., HD + 1] = np.abs(a[..., HD + 1]) + 0.5; return a
+
+    def want(step):
+        return O.merge(np.stack([fix_l(np.random.default_rng(1000 * step + r).standard_normal((1, H, HD + 2)).astype(np.float32))
+                                 for r in range(world)]))
+
+    def barrier(tag):
+        store.set(f"bar/{tag}/{rank}", "1")
+        store.wait([f"bar/{tag}/{r}" for r in range(world)])
+
+    # step 1: ordinary
+    x.push(record(1)); out = x.wait_merge((1, H, HD + 2)); log.append(out is not bd.HostExchange.TIMEOUT and np.allclose(out, want(1), atol=1e-6))
+    barrier(1)
+    # step 2: the last rank sits out; the others find a STALE flag (step 1) from it and must not accept it
+    if rank != world - 1:
+        x.push(record(2)); out = x.wait_merge((1, H, HD + 2)); log.append(out is bd.HostExchange.TIMEOUT)
+    else:
+        log.append(True)
+    barrier(2)
+    # step 3: everybody takes part again (the absentee advances by two); rank 0's copy for rank 1 is dropped
+    adv = 2 if rank == world - 1 else 1
+    x.push(record(3), advance=adv, drop_to=(1,) if rank == 0 else ())
+    out = x.wait_merge((1, H, HD + 2))
+    if rank == 1:
+        log.append(out is bd.HostExchange.TIMEOUT)              # sees rank 0's flag of step 2 only
+    else:
+        log.append(out is not bd.HostExchange.TIMEOUT and np.allclose(out, want(3), atol=1e-6))
+    barrier(3)
+    # step 4: ordinary again, and in the parity buffer that step 2 used: nothing stale may leak in
+    x.push(record(4)); out = x.wait_merge((1, H, HD + 2)); log.append(out is not bd.HostExchange.TIMEOUT and np.allclose(out, want(4), atol=1e-6))
+    barrier(4)
+    assert x.epoch == 4
+    ret.put((rank, log))
+
+
+def test_exchange_protocol_stale_flag_dropped_push_and_absent_rank():
+    world = 3
+    ctx = mp.get_context("spawn")
+    ret = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_xchg_worker, args=(r, world, port, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = dict(ret.get(timeout=120) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for r in range(world):
+        assert got[r] == [True, True, True, True], f"rank {r}: {got[r]}"
