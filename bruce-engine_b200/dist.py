@@ -160,8 +160,8 @@ class HostExchange:
 
 class SeqSplitDecoder:
     """Decode attention over one sequence whose KV cache is split by position range across the ranks of a process
-    group (full-causal layers).  Sliding-window layers read only the last `window` keys: they are not split --
-    `owner_of(p0, ...)` names the rank that holds the tail and serves them alone (`decode_window`).
+    group (full-causal layers: `decode`).  Sliding-window layers read only the last `window` keys: they are not
+    split -- the rank that owns the tail serves them alone (`decode_window`).
 
     Two exchanges of the per-shard (o, m, l) records:
       * "push" (default on CUDA): the decode kernel's merge epilogue stores the records straight into every peer's
@@ -194,6 +194,8 @@ class SeqSplitDecoder:
         self._pos = torch.zeros(R, dtype=torch.int32, device=dev)
         self._act = torch.ones(R, dtype=torch.int32, device=dev)
         self._epoch = torch.zeros(1, dtype=torch.int32, device=dev)
+        self._wpos = torch.zeros(1, dtype=torch.int32, device=dev)      # position of a window-layer call (global)
+        self._wpos_host = 0
         self._cur = (0, 1)                                   # (position, activity) currently held on the device
         self._behind = 0                                     # steps of the group this rank sat out
         self._kslot = torch.zeros(R, dtype=torch.int32, device=dev)
@@ -243,6 +245,22 @@ class SeqSplitDecoder:
             flat = self._recs.view(-1)[:self.world * rec.numel()]
             dist.all_gather_into_tensor(flat, rec.reshape(-1), group=self.group)
             eng.attn_combine(out, flat.view(self.world, rows, g.n_head, g.head_dim + 2), self.world, rows)
+
+    def decode_window(self, out, q, kvk_swa, kvv_swa, p0: int, rows: int = 1):
+        """A sliding-window layer of the split sequence: it reads only the last `window` keys, so it is not split --
+        the rank that owns position p0 keeps the layer's ring (under GLOBAL positions, p & (2W - 1)) and serves the
+        rows alone; the others receive the result (one small broadcast).  Appends to this layer go to that rank only
+        (`owner_of`)."""
+        owner = owner_of(p0, self.n_total, self.world)
+        if self.rank == owner:
+            if self._wpos_host != p0:
+                self._wpos.fill_(p0)
+                self._wpos_host = p0
+            self.eng.launch_attn_m(out.view((1,) + tuple(out.shape)), q.view((1,) + tuple(q.shape)), kvk_swa, kvv_swa,
+                                   self._wpos, self.part, rows, True)
+        if self.world > 1:
+            dist.broadcast(out, src=owner if self.group is None else dist.get_global_rank(self.group, owner), group=self.group)
+        return out
 
     def skip_step(self):
         """This rank sits out one step of the group (it neither pushes nor merges).  Its peers' merge of that step

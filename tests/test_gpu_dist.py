@@ -83,6 +83,74 @@ def _worker(rank, world, port, n_total, cases, q_all, k, v, exchange, skip_case,
         dist.destroy_process_group()
 
 
+def _window_worker(rank, world, port, n_total, W, q, k, v, ret):
+    import torch.distributed as dist
+
+    from bruce_engine_b200 import dist as bd
+    from bruce_engine_b200.engine import AttnEngine
+    from bruce_engine_b200.layout import G_B
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        sh = bd.shard_of(n_total, rank, world)
+        g = G_B.with_(slot_ctx=max(2, sh.capacity), window=W)
+        eng = AttnEngine(g, rank)
+        dec = bd.SeqSplitDecoder(eng, n_total, exchange="nccl")
+        kvk, kvv = eng.alloc_kv_layer(True, fill=0)                 # the ring of the window layer (2W slots)
+        p0 = n_total - 1
+        owner = bd.owner_of(p0, n_total, world)
+        if rank == owner:                                           # only the tail's owner holds the layer
+            kd, vd = torch.from_numpy(k).cuda(), torch.from_numpy(v).cuda()
+            first = max(0, n_total - 2 * W)
+            for a in range(first, n_total, 64):
+                b = min(n_total, a + 64)
+                eng.qkv_prep_store(kd[None, a:b], vd[None, a:b], kvk, kvv, torch.tensor([a], dtype=torch.int32, device="cuda"),
+                                   rows=b - a, is_swa=True)
+        qd = torch.from_numpy(q).cuda().half().contiguous()
+        out = torch.full((1, g.n_head, g.head_dim), float("nan"), dtype=torch.float16, device="cuda")
+        dec.decode_window(out, qd, kvk, kvv, p0, 1)
+        torch.cuda.synchronize()
+        assert eng.device_status() == 0
+        ret.put((rank, out.float().cpu().numpy()))
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_window_layer_of_a_split_sequence_is_served_by_the_owner_of_the_tail():
+    import torch.multiprocessing as mp
+
+    from oracle import oracle as O
+    from tests.util import assert_close
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least 2 GPUs")
+    n_total, W = 3000, 256
+    g = O.Geom(n_head=32, n_kv=8, head_dim=128, window=W, slot_ctx=n_total)
+    rng = np.random.default_rng(53)
+    k = rng.standard_normal((n_total, g.n_kv, g.head_dim), dtype=np.float32)
+    v = rng.standard_normal((n_total, g.n_kv, g.head_dim), dtype=np.float32)
+    q = rng.standard_normal((1, g.n_head, g.head_dim), dtype=np.float32).astype(np.float16).astype(np.float32)
+    kvk, kvv = O.new_cache(g, True), O.new_cache(g, True)
+    first = max(0, n_total - 2 * W)
+    O.kv_append(g, k[None, first:], v[None, first:], kvk, kvv, [first], rows=n_total - first, is_swa=True)
+    want = O.attend(g, q[None], kvk, kvv, [n_total - 1], rows=1, is_swa=True)[0]
+    ctx = mp.get_context("spawn")
+    ret = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_window_worker, args=(r, world, port, n_total, W, q, k, v, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    outs = dict(ret.get(timeout=300) for _ in range(world))
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    for r in range(world):
+        assert_close(outs[r], want, f"window layer of the split sequence on rank {r}")
+
+
 def _run(n_total, cases, exchange, skip_case=None, seed=31):
     import torch.multiprocessing as mp
 
