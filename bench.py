@@ -500,6 +500,46 @@ def bench_verify(torch, AttnEngine, G_B, device, reps: int):
     return res
 
 
+def bench_paged(torch, AttnEngine, G_B, device, reps: int, ctx: int = 262144, page_len: int = 256):
+    """Decode at context `ctx` over a paged cache (pages of `page_len` positions, table = a random permutation of the
+    pool) next to the same call on a contiguous partition holding the same records; the outputs must be equal."""
+    g = G_B.with_(slot_ctx=ctx + page_len, window=WINDOW, n_slots=1)
+    eng = AttnEngine(g, device)
+    dev = eng.device
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(77)
+    n_pages = (ctx + page_len) // page_len
+    table = torch.randperm(n_pages, generator=gen, device=dev).to(torch.int32).reshape(1, n_pages).contiguous()
+    pages, pool_k, pool_v = eng.alloc_pages(n_pages, page_len, table)
+    kvk, kvv = eng.alloc_kv_layer(False)
+    kb = torch.randn((1, 512, g.n_kv, g.head_dim), generator=gen, device=dev)
+    vb = torch.randn((1, 512, g.n_kv, g.head_dim), generator=gen, device=dev)
+    pos1 = torch.zeros(1, dtype=torch.int32, device=dev)
+    for a in range(0, ctx + 1, 512):
+        pos1.fill_(a)
+        n = min(512, ctx + 1 - a)
+        eng.qkv_prep_store(kb, vb, kvk, kvv, pos1, rows=n)
+        eng.kv_append_paged(pages, kb, vb, pos1, rows=n)
+    q = torch.randn((1, 1, g.n_head, g.head_dim), generator=gen, device=dev).half()
+    out_c, out_p = torch.zeros_like(q), torch.zeros_like(q)
+    pos = torch.full((1,), ctx, dtype=torch.int32, device=dev)
+    part = eng.alloc_part(1, 1)
+    res = {"ctx": ctx, "page_len": page_len, "n_pages": n_pages}
+    for name, step in (("contiguous", lambda: eng.launch_attn_m(out_c, q, kvk, kvv, pos, part, 1)),
+                       ("paged", lambda: eng.attn_paged(out_p, q, pages, pos, part, rows=1))):
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize()
+        eng.profile_start(reps)
+        for _ in range(reps):
+            step()
+        t = statistics.mean(eng.profile_stop()) * 1e-3
+        res[name] = {"kernel_us": t * 1e6, "TBps": (ctx + 1) * POS_BYTES / t / 1e12}
+    res["outputs_equal"] = bool(torch.equal(out_c, out_p))
+    assert eng.device_status() == 0
+    return res
+
+
 def fill_positions(torch, eng, kvk, kvv, seed: int, start: int, end: int, kslot=None, local_start: int = 0):
     """Appends deterministic N(0,1) K/V rows for global positions [start, end) of one sequence: the rows of every
     512-position block come from a generator seeded by (seed, block index), so the data at a position does not
@@ -796,7 +836,8 @@ def run_gpu(args):
     ctxs = [args.only_ctx] if args.only_ctx else CTXS
     if args.case == "verify":
         print(json.dumps({"verify": bench_verify(torch, AttnEngine, G_B, local, max(1, args.steps)),
-                          "qkv_prep": bench_qkv_prep(torch, AttnEngine, G_B, local, 50)}))
+                          "qkv_prep": bench_qkv_prep(torch, AttnEngine, G_B, local, 50),
+                          "paged_decode_256k": bench_paged(torch, AttnEngine, G_B, local, max(1, args.steps))}))
         return 0
     if args.case == "prefill":                      # light run for profiling the prompt-chunk kernel
         from bruce_engine_b200.layout import G_R
@@ -973,6 +1014,7 @@ def run_gpu(args):
     prefill = bench_prefill(torch, AttnEngine, G_B, local, 2) if rank == 0 else None
     verify = bench_verify(torch, AttnEngine, G_B, local, 20) if rank == 0 else None
     qkv_prep = bench_qkv_prep(torch, AttnEngine, G_B, local, 50) if rank == 0 else None
+    paged = bench_paged(torch, AttnEngine, G_B, local, 20) if rank == 0 else None
     legacy = bench_legacy_reference_kernels(torch, AttnEngine) if rank == 0 and world == 1 else None
     if prefill is not None:
         bf16_peak = None
@@ -1023,7 +1065,7 @@ def run_gpu(args):
                                  "workloads and their efficiency are in scaling_detail"},
             "e2e": {"value": e2e_value, "unit": "TB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": ms_e2e / K},
-            "gpu_launches": launches, "roofline": roofline, "sweep": sweep, "prefill": prefill, "verify_8rows_64k": verify, "qkv_prep": qkv_prep, "serving_mix_64_slots": serving, "seq_split_1m": seqsplit,
+            "gpu_launches": launches, "roofline": roofline, "sweep": sweep, "prefill": prefill, "verify_8rows_64k": verify, "qkv_prep": qkv_prep, "paged_decode_256k": paged, "serving_mix_64_slots": serving, "seq_split_1m": seqsplit,
             "clocks": clocks,
             "device_status": status,
             "parity": parity,

@@ -27,7 +27,14 @@ class CGeom(C.Structure):
                 ("out_dtype", C.c_int), ("softmax_scale", C.c_float)]
 
 
+class CPages(C.Structure):
+    """battn_pages: a paged cache of one full-causal layer (pool pointers, the device-resident page table)."""
+    _fields_ = [("pool_k", C.c_void_p), ("pool_v", C.c_void_p), ("table", C.c_void_p),
+                ("n_pages", C.c_int), ("n_tables", C.c_int), ("max_pages", C.c_int), ("page_len", C.c_int)]
+
+
 _P, _I, _SZP = C.c_void_p, C.c_int, C.POINTER(C.c_size_t)
+_PG = C.POINTER(CPages)
 
 # name -> (restype, argtypes); exactly the symbols include/battn.h declares
 SIGNATURES = {
@@ -51,6 +58,13 @@ SIGNATURES = {
     "battn_attend_exact": (_I, [_P] * 9 + [_I, _I, _I, _I, _P]),
     "battn_partials": (_I, [_P] * 9 + [_I, _I, _I, _P]),
     "battn_merge": (_I, [_P, _P, _P, _I, _I, _P]),
+    "battn_pages_pool_bytes": (_I, [_P, _I, _I, _SZP]),
+    "battn_pages_copy": (_I, [_P, _PG, _I, _I, _P]),
+    "battn_kv_append_paged": (_I, [_P, _PG] + [_P] * 5 + [_I, _I, _P]),
+    "battn_decode_paged": (_I, [_P, _P, _P, _PG] + [_P] * 4 + [_I, _P]),
+    "battn_verify_paged": (_I, [_P, _P, _P, _PG] + [_P] * 4 + [_I, _I, _P]),
+    "battn_prefill_paged": (_I, [_P, _P, _P, _PG, _I, _P, _P, _I, _P]),
+    "battn_attend_exact_paged": (_I, [_P, _P, _P, _PG] + [_P] * 4 + [_I, _I, _I, _P]),
     "battn_xchg_create": (_I, [_P, _I, _I, _I, C.POINTER(_P), _P]),
     "battn_xchg_connect": (_I, [_P, _P]),
     "battn_xchg_area": (_I, [_P, C.POINTER(_P), _SZP]),

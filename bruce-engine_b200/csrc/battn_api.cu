@@ -166,9 +166,34 @@ struct ProfScope {
     ~ProfScope() { if (idx >= 0) cudaEventRecord(h->prof_ev[2 * idx + 1], st); }
 };
 
+// a caller's paged cache, validated: the device-side view plus what replaces the contiguous geometry
+struct PagedView {
+    Paging pg;
+    int n_tables, capacity;          // table rows; positions one row can hold
+};
+int paged_view(const battn_pages* pages, PagedView& v) {
+    if (!pages || !pages->pool_k || !pages->pool_v || !pages->table) return BATTN_ERR_ARG;
+    if ((((uintptr_t)pages->pool_k | (uintptr_t)pages->pool_v) & 15) || ((uintptr_t)pages->table & 3)) return BATTN_ERR_ARG;
+    const int L = pages->page_len;
+    if (L < 128 || L > 65536 || (L & (L - 1))) return BATTN_ERR_ARG;        // whole 128-key tiles per page
+    if (pages->n_pages < 1 || pages->n_tables < 1 || pages->max_pages < 1) return BATTN_ERR_ARG;
+    if ((long long)pages->max_pages * L > 0x7fffffffLL) return BATTN_ERR_CAPACITY;
+    int shift = 0;
+    while ((1 << shift) < L) ++shift;
+    v.pg.table = pages->table; v.pg.max_pages = pages->max_pages; v.pg.shift = shift; v.pg.n_pages = pages->n_pages;
+    v.n_tables = pages->n_tables; v.capacity = pages->max_pages * L;
+    return BATTN_OK;
+}
+// overrides the contiguous-partition fields of a kernel's parameters with the paged view
+template <typename P_>
+void apply_paging(P_& P, const PagedView* pv) {
+    if (!pv) return;
+    P.pg = pv->pg; P.pstride = pv->capacity; P.ring_mask = -1; P.slot_ctx = pv->capacity;
+}
+
 int launch_exact(battn_handle* h, void* out, float* rec_out, const void* q, const uint8_t* kvk, const uint8_t* kvv,
                  const int* pos, const int* kslot, const int* act, void* ws, int n_seq, int rows, int nsplit,
-                 int is_swa, cudaStream_t st) {
+                 int is_swa, cudaStream_t st, const PagedView* pv = nullptr) {
     const Geom& g = h->g;
     ExactParams P;
     P.q = q; P.kvk = kvk; P.kvv = kvv; P.pos = pos; P.kslot = kslot; P.act = act;
@@ -177,6 +202,8 @@ int launch_exact(battn_handle* h, void* out, float* rec_out, const void* q, cons
     P.W = g.W; P.pstride = is_swa ? g.ring : g.slot_ctx; P.ring_mask = is_swa ? g.ring - 1 : -1;
     P.slot_ctx = g.slot_ctx; P.n_slots = g.n_slots; P.is_swa = is_swa; P.q_f16 = g.q_f16;
     P.scale = g.scale; P.status = h->d_status;
+    apply_paging(P, pv);
+    if (pv) P.n_slots = pv->n_tables;
     const dim3 grid(n_seq * g.Hkv, nsplit, rows), block(32 * g.G);
     {
         ProfScope prof(h, st);
@@ -187,8 +214,8 @@ int launch_exact(battn_handle* h, void* out, float* rec_out, const void* q, cons
     M.mode = MERGE_REGULAR; M.part = P.part; M.out = out; M.rec_out = rec_out;
     M.n_rows = n_seq * rows; M.rows = rows; M.Hq = g.Hq; M.Hkv = g.Hkv; M.G = g.G;
     M.count = nsplit; M.log2_domain = 0; M.out_f16 = g.out_f16;
-    M.pos = pos; M.kslot = kslot; M.act = act; M.is_swa = is_swa; M.W = g.W; M.slot_ctx = g.slot_ctx;
-    M.n_slots = g.n_slots; M.status = h->d_status; M.hdr = nullptr;
+    M.pos = pos; M.kslot = kslot; M.act = act; M.is_swa = is_swa; M.W = g.W; M.slot_ctx = P.slot_ctx;
+    M.n_slots = P.n_slots; M.status = h->d_status; M.hdr = nullptr;
     if (g.HD == 128) k_merge<128><<<n_seq * rows * g.Hq, MERGE_THREADS, 0, st>>>(M);
     else             k_merge<256><<<n_seq * rows * g.Hq, MERGE_THREADS, 0, st>>>(M);
     h->launches += 2;
@@ -204,7 +231,8 @@ cudaError_t launch_fd_kernel(const fd::Params& P, int grid, size_t smem, cudaStr
 // decode / verify / multi-slot decode through the flash-decode kernel and the balanced merge
 int launch_flash(battn_handle* h, void* out, float* rec_out, const void* q, const uint8_t* kvk, const uint8_t* kvv,
                  const int* pos, const int* kslot, const int* act, void* ws, int n_seq, int rows, int is_swa,
-                 cudaStream_t st, const XchgView* xv = nullptr, int* epoch_ptr = nullptr, int epoch_advance = 0) {
+                 cudaStream_t st, const XchgView* xv = nullptr, int* epoch_ptr = nullptr, int epoch_advance = 0,
+                 const PagedView* pv = nullptr) {
     const Geom& g = h->g;
     const int RG = rows * g.G;
     if (RG > 32) return BATTN_ERR_CAPACITY;
@@ -219,6 +247,8 @@ int launch_flash(battn_handle* h, void* out, float* rec_out, const void* q, cons
     P.slot_ctx = g.slot_ctx; P.n_slots = g.n_slots; P.is_swa = is_swa; P.q_f16 = g.q_f16;
     P.scale_log2 = g.scale * LOG2E; P.status = h->d_status;
     P.epoch_ptr = epoch_ptr; P.epoch_advance = epoch_advance;
+    apply_paging(P, pv);
+    if (pv) P.n_slots = pv->n_tables;
 
     cudaError_t e;
     if (RG > 16 && g.HD == 128 && g.W >= 64 && vt::smem_bytes(n_seq) <= SMEM_MAX) {
@@ -265,7 +295,8 @@ int launch_flash(battn_handle* h, void* out, float* rec_out, const void* q, cons
 
 // prompt chunk on the tcgen05 kernel: one CTA per (128-row M tile, kv head), normalised output
 int launch_prefill(battn_handle* h, void* out, const void* q, const uint8_t* kvk, const uint8_t* kvv, const int* pos,
-                   void* ws, int rows, int is_swa, cudaStream_t st, const GateNormParams* gn = nullptr) {
+                   void* ws, int rows, int is_swa, cudaStream_t st, const GateNormParams* gn = nullptr,
+                   const PagedView* pv = nullptr, int table_row = 0) {
     const Geom& g = h->g;
     if (128 % g.G) return BATTN_ERR_ARG;
     pf::Params P;
@@ -274,6 +305,8 @@ int launch_prefill(battn_handle* h, void* out, const void* q, const uint8_t* kvk
     P.W = g.W; P.pstride = is_swa ? g.ring : g.slot_ctx; P.ring_mask = is_swa ? g.ring - 1 : -1;
     P.slot_ctx = g.slot_ctx; P.is_swa = is_swa; P.q_f16 = g.q_f16; P.out_f16 = g.out_f16;
     P.scale_log2 = g.scale * LOG2E; P.status = h->d_status;
+    apply_paging(P, pv);
+    if (pv) P.slot = table_row;
     const int MR = 128 / g.G;
     P.nsplit = prefill_splits(h, rows, is_swa);
     P.recs = (P.nsplit > 1 || gn) ? reinterpret_cast<float*>(ws) : nullptr;
@@ -436,8 +469,9 @@ int battn_exact_workspace_bytes(const battn_handle* h, int n_seq, int rows_per_s
     return BATTN_OK;
 }
 
-int battn_kv_append(battn_handle* h, const float* k, const float* v, uint8_t* kvk, uint8_t* kvv, const int* pos,
-                    const int* kslot, const int* act, int n_seq, int rows_per_seq, int is_swa, void* stream) {
+static int kv_append_impl(battn_handle* h, const float* k, const float* v, uint8_t* kvk, uint8_t* kvv, const int* pos,
+                          const int* kslot, const int* act, int n_seq, int rows_per_seq, int is_swa, void* stream,
+                          const PagedView* pv) {
     const int rc = check_seq_args(h, k, v, kvk, kvv, pos, kslot, n_seq, rows_per_seq, MAX_PREFILL);
     if (rc) return rc;
     const Geom& g = h->g;
@@ -449,6 +483,7 @@ int battn_kv_append(battn_handle* h, const float* k, const float* v, uint8_t* kv
     P.n_seq = n_seq; P.rows = rows_per_seq; P.Hkv = g.Hkv;
     P.pstride = is_swa ? g.ring : g.slot_ctx; P.ring_mask = is_swa ? g.ring - 1 : -1;
     P.n_slots = g.n_slots; P.status = h->d_status;
+    if (pv) { P.pg = pv->pg; P.pstride = pv->capacity; P.ring_mask = -1; P.n_slots = pv->n_tables; }
     const long long warps = (long long)n_seq * rows_per_seq * g.Hkv * 2;
     const int blocks = (int)((warps + 7) / 8);
     cudaStream_t st = (cudaStream_t)stream;
@@ -458,6 +493,11 @@ int battn_kv_append(battn_handle* h, const float* k, const float* v, uint8_t* kv
     h->launches += 1;
     if (e == cudaSuccess) e = cudaGetLastError();
     return e == cudaSuccess ? BATTN_OK : cuda_fail(h, e);
+}
+
+int battn_kv_append(battn_handle* h, const float* k, const float* v, uint8_t* kvk, uint8_t* kvv, const int* pos,
+                    const int* kslot, const int* act, int n_seq, int rows_per_seq, int is_swa, void* stream) {
+    return kv_append_impl(h, k, v, kvk, kvv, pos, kslot, act, n_seq, rows_per_seq, is_swa, stream, nullptr);
 }
 
 int battn_kv_copy_prefix(battn_handle* h, uint8_t* kvk, uint8_t* kvv, int src_slot, int dst_slot, int n_pos, int is_swa,
@@ -608,6 +648,87 @@ int battn_attend_exact(battn_handle* h, void* out, const void* q, const uint8_t*
     if (!ws || ((uintptr_t)ws & 15) || nsplit < 1 || nsplit > MAX_SPLITS) return BATTN_ERR_ARG;
     return launch_exact(h, out, nullptr, q, kvk, kvv, pos, kslot, act, ws, n_seq, rows_per_seq, nsplit, is_swa,
                         (cudaStream_t)stream);
+}
+
+// ---- paged cache (full-causal layers) -----------------------------------------------------------------------
+int battn_pages_pool_bytes(const battn_handle* h, int n_pages, int page_len, size_t* out_bytes) {
+    if (!h || !out_bytes || n_pages < 1 || page_len < 128 || (page_len & (page_len - 1))) return BATTN_ERR_ARG;
+    *out_bytes = (size_t)n_pages * h->g.Hkv * (size_t)page_len * h->g.rec;
+    return BATTN_OK;
+}
+
+int battn_pages_copy(battn_handle* h, const battn_pages* pages, int from_page, int to_page, void* stream) {
+    PagedView pv;
+    const int rc = paged_view(pages, pv);
+    if (rc) return rc;
+    if (!h || from_page < 0 || to_page < 0 || from_page >= pages->n_pages || to_page >= pages->n_pages) return BATTN_ERR_ARG;
+    if (from_page == to_page) return BATTN_OK;
+    const size_t page_bytes = (size_t)h->g.Hkv * pages->page_len * h->g.rec;
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e = cudaMemcpyAsync(pages->pool_k + to_page * page_bytes, pages->pool_k + from_page * page_bytes, page_bytes,
+                                    cudaMemcpyDeviceToDevice, st);
+    if (e == cudaSuccess)
+        e = cudaMemcpyAsync(pages->pool_v + to_page * page_bytes, pages->pool_v + from_page * page_bytes, page_bytes,
+                            cudaMemcpyDeviceToDevice, st);
+    return e == cudaSuccess ? BATTN_OK : cuda_fail(h, e);
+}
+
+int battn_kv_append_paged(battn_handle* h, const battn_pages* pages, const float* k, const float* v, const int* pos,
+                          const int* ktab, const int* act, int n_seq, int rows_per_seq, void* stream) {
+    PagedView pv;
+    const int rc = paged_view(pages, pv);
+    if (rc) return rc;
+    return kv_append_impl(h, k, v, pages->pool_k, pages->pool_v, pos, ktab, act, n_seq, rows_per_seq, 0, stream, &pv);
+}
+
+int battn_decode_paged(battn_handle* h, void* out, const void* q, const battn_pages* pages, const int* pos,
+                       const int* ktab, const int* act, void* ws, int n_seq, void* stream) {
+    PagedView pv;
+    int rc = paged_view(pages, pv);
+    if (rc) return rc;
+    rc = check_seq_args(h, out, q, pages->pool_k, pages->pool_v, pos, ktab, n_seq, 1, 1);
+    if (rc) return rc;
+    if (!ws || ((uintptr_t)ws & 15)) return BATTN_ERR_ARG;
+    return launch_flash(h, out, nullptr, q, pages->pool_k, pages->pool_v, pos, ktab, act, ws, n_seq, 1, 0,
+                        (cudaStream_t)stream, nullptr, nullptr, 0, &pv);
+}
+
+int battn_verify_paged(battn_handle* h, void* out, const void* q, const battn_pages* pages, const int* pos,
+                       const int* ktab, const int* act, void* ws, int rows, int batch, void* stream) {
+    PagedView pv;
+    int rc = paged_view(pages, pv);
+    if (rc) return rc;
+    rc = check_seq_args(h, out, q, pages->pool_k, pages->pool_v, pos, ktab, batch, rows, MAX_VERIFY);
+    if (rc) return rc;
+    if (!ws || ((uintptr_t)ws & 15)) return BATTN_ERR_ARG;
+    return launch_flash(h, out, nullptr, q, pages->pool_k, pages->pool_v, pos, ktab, act, ws, batch, rows, 0,
+                        (cudaStream_t)stream, nullptr, nullptr, 0, &pv);
+}
+
+int battn_prefill_paged(battn_handle* h, void* out, const void* q, const battn_pages* pages, int table_row,
+                        const int* pos, void* ws, int rows, void* stream) {
+    PagedView pv;
+    int rc = paged_view(pages, pv);
+    if (rc) return rc;
+    rc = check_seq_args(h, out, q, pages->pool_k, pages->pool_v, pos, nullptr, 1, rows, MAX_PREFILL);
+    if (rc) return rc;
+    if (!ws || ((uintptr_t)ws & 15) || table_row < 0 || table_row >= pages->n_tables) return BATTN_ERR_ARG;
+    if (rows * h->g.G <= 32) return BATTN_ERR_ARG;       // short calls: battn_decode_paged / battn_verify_paged
+    return launch_prefill(h, out, q, pages->pool_k, pages->pool_v, pos, ws, rows, 0, (cudaStream_t)stream, nullptr, &pv,
+                          table_row);
+}
+
+int battn_attend_exact_paged(battn_handle* h, void* out, const void* q, const battn_pages* pages, const int* pos,
+                             const int* ktab, const int* act, void* ws, int n_seq, int rows_per_seq, int nsplit,
+                             void* stream) {
+    PagedView pv;
+    int rc = paged_view(pages, pv);
+    if (rc) return rc;
+    rc = check_seq_args(h, out, q, pages->pool_k, pages->pool_v, pos, ktab, n_seq, rows_per_seq, MAX_PREFILL);
+    if (rc) return rc;
+    if (!ws || ((uintptr_t)ws & 15) || nsplit < 1 || nsplit > MAX_SPLITS) return BATTN_ERR_ARG;
+    return launch_exact(h, out, nullptr, q, pages->pool_k, pages->pool_v, pos, ktab, act, ws, n_seq, rows_per_seq, nsplit,
+                        0, (cudaStream_t)stream, &pv);
 }
 
 int battn_xchg_create(battn_handle* h, int rank, int world, int max_rows, battn_xchg** out_x, void* ipc_handle_out) {

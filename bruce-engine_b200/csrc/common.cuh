@@ -174,6 +174,30 @@ __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
+// ---- paged cache ------------------------------------------------------------------------------------
+// A full-causal layer's cache can be a pool of pages instead of one contiguous partition per slot (the reference
+// carves contiguous ctx/N partitions, bruce.cu:5471-5503): a page holds 2^shift consecutive positions of every kv
+// head, laid out [kv head][position][record], so a 64- or 128-key tile of one head is still one contiguous run.
+// Row `slot` of the device-resident table maps logical page (pos >> shift) to a physical page.  Sequences that
+// share a prefix point at the same physical pages.  table == nullptr: the contiguous partitions.
+struct Paging {
+    const int* table = nullptr;
+    int max_pages = 0, shift = 0, n_pages = 0;
+};
+// index, in records, of position `sp` (already reduced modulo the ring on a window layer) of (slot, kv head)
+__device__ __forceinline__ size_t kv_rec_index_page(const Paging& pg, int page, int kvh, int Hkv, int sp, int* status) {
+    if ((unsigned)page >= (unsigned)pg.n_pages) {          // a table entry outside the pool: flag it, stay in bounds
+        atomicOr(status, BATTN_DEV_BAD_POSITION);
+        page = 0;
+    }
+    return ((((size_t)page * Hkv + kvh) << pg.shift) | (size_t)(sp & ((1 << pg.shift) - 1)));
+}
+__device__ __forceinline__ size_t kv_rec_index(const Paging& pg, int slot, int kvh, int Hkv, int pstride, int sp,
+                                               int* status) {
+    if (!pg.table) return ((size_t)slot * Hkv + kvh) * pstride + sp;
+    return kv_rec_index_page(pg, pg.table[(size_t)slot * pg.max_pages + (sp >> pg.shift)], kvh, Hkv, sp, status);
+}
+
 // ---- per-sequence key range ---------------------------------------------------------------------
 // Sequence i with `rows` query rows at p0 .. p0+rows-1: union of the rows' visible keys is
 // [lo, hi), lo = is_swa ? max(0, p0 + 1 - W) : 0, hi = p0 + rows  (bruce.cu:724-727, 3670-3675).

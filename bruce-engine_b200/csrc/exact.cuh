@@ -27,6 +27,7 @@ struct ExactParams {
     int q_f16;
     float scale;
     int* status;
+    Paging pg;
 };
 
 template <int HD>
@@ -53,7 +54,7 @@ __global__ void __launch_bounds__(256) k_attn_exact(const ExactParams P) {
                         : reinterpret_cast<const float*>(P.q)[qi];
     }
     const int blk = (lane * DPL) >> 5;
-    const size_t hb = ((size_t)sr.slot * P.Hkv + kvh) * P.pstride * (size_t)REC;
+    const size_t hb = P.pg.table ? 0 : ((size_t)sr.slot * P.Hkv + kvh) * P.pstride * (size_t)REC;
     const uint8_t* kb = P.kvk + hb;
     const uint8_t* vb = P.kvv + hb;
     const int off = 2 * NBLK + lane * DPL;
@@ -63,7 +64,8 @@ __global__ void __launch_bounds__(256) k_attn_exact(const ExactParams P) {
     for (int j = 0; j < DPL; ++j) o[j] = 0.f;
 
     for (int key = a0; key < a1; ++key) {
-        const size_t ro = (size_t)(key & P.ring_mask) * REC;           // ring slot (bruce.cu:740)
+        const size_t ro = (P.pg.table ? kv_rec_index(P.pg, sr.slot, kvh, P.Hkv, P.pstride, key, P.status)
+                                      : (size_t)(key & P.ring_mask)) * REC;   // ring slot (bruce.cu:740)
         const uint8_t* kk = kb + ro;
         const uint8_t* vv = vb + ro;
         const float d = __half2float(reinterpret_cast<const __half*>(kk)[blk]);

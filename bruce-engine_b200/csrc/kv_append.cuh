@@ -20,6 +20,7 @@ struct AppendParams {
     int ring_mask;      // 2*W-1 for a sliding-window layer, -1 (all ones) otherwise
     int n_slots;
     int* status;
+    Paging pg;          // table != nullptr: paged cache (pstride = positions a table row can hold)
 };
 
 template <int HD>
@@ -49,7 +50,7 @@ __global__ void __launch_bounds__(256) k_kv_append(const AppendParams P) {
     }
     const int pp = p & P.ring_mask;                   // ring slot (bruce.cu:691); identity when -1
     const float* src = (which ? P.v : P.k) + (((size_t)i * P.rows + r) * P.Hkv + kvh) * HD;
-    uint8_t* dst = (which ? P.kvv : P.kvk) + (((size_t)slot * P.Hkv + kvh) * P.pstride + pp) * (size_t)REC;
+    uint8_t* dst = (which ? P.kvv : P.kvk) + kv_rec_index(P.pg, slot, kvh, P.Hkv, P.pstride, pp, P.status) * (size_t)REC;
 
 #pragma unroll
     for (int it = 0; it < HD / 128; ++it) {

@@ -69,6 +69,8 @@ struct Params {
     // merge + gate-norm epilogue)
     int nsplit;
     float* recs;
+    Paging pg;       // table != nullptr: paged cache of a full-causal layer; `slot` is the table row of the sequence
+    int slot = 0;
 };
 
 template <int HD, int BN>
@@ -442,12 +444,15 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill(const Params P) {
                 const int b = j % C::RAW_STAGES;
                 if (j >= C::RAW_STAGES) wait(B_RAW_FREE0 + b, (j / C::RAW_STAGES - 1) & 1);   // both dequant groups left it
                 const int sp = ((tile_first + j) * BN) & P.ring_mask;
-                const int nk = min(BN, P.pstride - sp);
+                const int nk = P.pg.table ? BN : min(BN, P.pstride - sp);
                 const uint32_t bytes = (uint32_t)nk * REC;
+                // (a paged look-up here is hidden by the ring: the loader runs RAW_STAGES tiles ahead of the dequant warps)
+                const size_t off = P.pg.table ? kv_rec_index(P.pg, P.slot, kvh, P.Hkv, P.pstride, sp, P.status) * (size_t)REC
+                                              : hb + (size_t)sp * REC;
                 uint8_t* dst = RAW + b * 2 * C::RAW_BYTES;
                 mbar_expect_tx(&bars[B_RAW_FULL0 + b], 2 * bytes);
-                bulk_g2s(dst, P.kvk + hb + (size_t)sp * REC, bytes, &bars[B_RAW_FULL0 + b]);
-                bulk_g2s(dst + C::RAW_BYTES, P.kvv + hb + (size_t)sp * REC, bytes, &bars[B_RAW_FULL0 + b]);
+                bulk_g2s(dst, P.kvk + off, bytes, &bars[B_RAW_FULL0 + b]);
+                bulk_g2s(dst + C::RAW_BYTES, P.kvv + off, bytes, &bars[B_RAW_FULL0 + b]);
             }
         }
     } else if (warp > (NSOFT + 2 * NDEQ) / 32 + 2) {

@@ -248,16 +248,19 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill_hd128(const Params P) {
         } else if ((warp == W_LDK || warp == W_LDV) && lane == 0) {
             // ======================= loaders: raw K (or V) tiles into their ring with bulk copies =======
             const bool isv = warp == W_LDV;
-            const uint8_t* src = (isv ? P.kvv : P.kvk) + hb;
+            const uint8_t* src = isv ? P.kvv : P.kvk;
             uint8_t* ring = smem + (isv ? OFF_RAWV : OFF_RAWK);
             const int full = isv ? B_VRAW_FULL : B_KRAW_FULL, free_ = isv ? B_VRAW_FREE : B_KRAW_FREE;
             for (int j = 0; j < n_tiles; ++j) {
                 if (j >= NB) wait(free_ + slot(j), phase(j - NB), 200);         // the dequant group left it (no hurry: the ring is three deep)
                 const int sp = ((tile_first + j) * BN) & P.ring_mask;
-                const int nk = min(BN, P.pstride - sp);
+                const int nk = P.pg.table ? BN : min(BN, P.pstride - sp);
                 const uint32_t bytes = (uint32_t)nk * REC;
+                // (a paged look-up here is hidden by the ring: the loader runs three tiles ahead of the dequant warps)
+                const size_t off = P.pg.table ? kv_rec_index(P.pg, P.slot, kvh, P.Hkv, P.pstride, sp, P.status) * (size_t)REC
+                                              : hb + (size_t)sp * REC;
                 mbar_expect_tx(&bars[full + slot(j)], bytes);
-                bulk_g2s(ring + slot(j) * RAW_BYTES, src + (size_t)sp * REC, bytes, &bars[full + slot(j)]);
+                bulk_g2s(ring + slot(j) * RAW_BYTES, src + off, bytes, &bars[full + slot(j)]);
             }
         }
     } else if (warp >= W_VDQ) {

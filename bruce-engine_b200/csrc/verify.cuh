@@ -117,8 +117,13 @@ __global__ void __launch_bounds__(NTHREADS, HD == 128 ? 3 : 1) k_verify_wide(con
                                               P.n_slots, P.status);
                 const size_t hb = ((size_t)sr.slot * P.Hkv + pc.kvh) * P.pstride * (size_t)REC;
                 const int tile0 = sr.lo / TILE + pc.tl;
+                // paged cache: the table entry of the next tile is fetched one tile ahead of its use
+                const int* trow = P.pg.table ? P.pg.table + (size_t)sr.slot * P.pg.max_pages : nullptr;
+                int page_nx = trow ? trow[(tile0 * TILE) >> P.pg.shift] : 0;
                 for (int t = 0; t < pc.n; ++t, ++cnt) {
                     const int s = cnt % STAGES, use = cnt / STAGES;
+                    const int page = page_nx;
+                    if (trow && t + 1 < pc.n) page_nx = trow[((tile0 + t + 1) * TILE) >> P.pg.shift];
                     if (use > 0 && !*(volatile int*)&s_abort) {
                         if (!mbar_wait_bounded(&empty[s], (use - 1) & 1)) {
                             atomicOr(P.status, BATTN_DEV_WAIT_TIMEOUT);
@@ -127,12 +132,14 @@ __global__ void __launch_bounds__(NTHREADS, HD == 128 ? 3 : 1) k_verify_wide(con
                     }
                     if (*(volatile int*)&s_abort) continue;
                     const int sp = ((tile0 + t) * TILE) & P.ring_mask;
-                    const int nk = min(TILE, P.pstride - sp);
+                    const int nk = trow ? TILE : min(TILE, P.pstride - sp);
                     const uint32_t bytes = (uint32_t)nk * REC;
+                    const size_t src = trow ? kv_rec_index_page(P.pg, page, pc.kvh, P.Hkv, sp, P.status) * (size_t)REC
+                                            : hb + (size_t)sp * REC;
                     uint8_t* dstk = stages + (size_t)s * 2 * TILE_BYTES;
                     mbar_expect_tx(&full[s], 2 * bytes);
-                    bulk_g2s(dstk, P.kvk + hb + (size_t)sp * REC, bytes, &full[s]);
-                    bulk_g2s(dstk + TILE_BYTES, P.kvv + hb + (size_t)sp * REC, bytes, &full[s]);
+                    bulk_g2s(dstk, P.kvk + src, bytes, &full[s]);
+                    bulk_g2s(dstk + TILE_BYTES, P.kvv + src, bytes, &full[s]);
                 }
                 g += pc.n;
             }

@@ -299,17 +299,24 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_verify_tc(const fd::Params P) {
                 const SeqRange sr = seq_range(P.pos, P.kslot, P.act, pc.i, P.rows, P.is_swa, P.W, P.slot_ctx, P.n_slots,
                                               P.status);
                 const size_t hb = ((size_t)sr.slot * P.Hkv + pc.kvh) * P.pstride * (size_t)REC;
-                const uint8_t* src = (isv ? P.kvv : P.kvk) + hb;
+                const uint8_t* src = isv ? P.kvv : P.kvk;
                 const int tile0 = sr.lo / BK + pc.tl;
+                // paged cache: the table entry of the next tile is fetched one tile ahead of its use
+                const int* trow = P.pg.table ? P.pg.table + (size_t)sr.slot * P.pg.max_pages : nullptr;
+                int page_nx = trow ? trow[(tile0 * BK) >> P.pg.shift] : 0;
                 for (int t = 0; t < pc.n; ++t, ++cnt) {
+                    const int page = page_nx;
+                    if (trow && t + 1 < pc.n) page_nx = trow[((tile0 + t + 1) * BK) >> P.pg.shift];
                     if (cnt >= NB) wait(free_ + slot(cnt), phase(cnt - NB), 100);
                     if (misc[1]) continue;
                     VT_TRACE(isv ? 3 : 2, cnt, 0);
                     const int sp = ((tile0 + t) * BK) & P.ring_mask;
-                    const int nk = min(BK, P.pstride - sp);
+                    const int nk = trow ? BK : min(BK, P.pstride - sp);
                     const uint32_t bytes = (uint32_t)nk * REC;
+                    const size_t off = trow ? kv_rec_index_page(P.pg, page, pc.kvh, P.Hkv, sp, P.status) * (size_t)REC
+                                            : hb + (size_t)sp * REC;
                     mbar_expect_tx(&bars[full + slot(cnt)], bytes);
-                    bulk_g2s(ring + slot(cnt) * RAW_BYTES, src + (size_t)sp * REC, bytes, &bars[full + slot(cnt)]);
+                    bulk_g2s(ring + slot(cnt) * RAW_BYTES, src + off, bytes, &bars[full + slot(cnt)]);
                 }
                 g += pc.n;
             }

@@ -174,6 +174,54 @@ class AttnEngine:
         rc = self.lib.battn_merge(self.h, _ptr(out), _ptr(parts), n_parts, n_rows, self._stream())
         self._check("battn_merge", rc)
 
+    # ---- paged cache of a full-causal layer ------------------------------------------------------------
+    def alloc_pages(self, n_pages: int, page_len: int, table: torch.Tensor, fill: int | None = None):
+        """A pool of `n_pages` pages of `page_len` positions (K and V) and its `battn_pages` descriptor; `table` is
+        the int32 device tensor [n_tables][max_pages] the kernels read the page numbers from (the host may edit it
+        between launches).  Returns (descriptor, pool_k, pool_v); keep the tensors alive with the descriptor."""
+        n = C.c_size_t()
+        self._check("battn_pages_pool_bytes", self.lib.battn_pages_pool_bytes(self.h, n_pages, page_len, C.byref(n)))
+        mk = (lambda: torch.empty(n.value, dtype=torch.uint8, device=self.device)) if fill is None else \
+             (lambda: torch.full((n.value,), fill, dtype=torch.uint8, device=self.device))
+        pk, pv = mk(), mk()
+        assert table.dtype == torch.int32 and table.dim() == 2 and table.is_contiguous()
+        desc = capi.CPages(pk.data_ptr(), pv.data_ptr(), table.data_ptr(), n_pages, table.shape[0], table.shape[1],
+                           page_len)
+        return desc, pk, pv
+
+    def pages_copy(self, pages, from_page: int, to_page: int):
+        """Copy on write: one physical page's K and V records into another page."""
+        self._check("battn_pages_copy", self.lib.battn_pages_copy(self.h, C.byref(pages), from_page, to_page,
+                                                                  self._stream()))
+
+    def kv_append_paged(self, pages, k, v, pos, ktab=None, act=None, rows: int = 1):
+        self._check("battn_kv_append_paged", self.lib.battn_kv_append_paged(
+            self.h, C.byref(pages), _ptr(k), _ptr(v), _ptr(pos), _ptr(ktab), _ptr(act), pos.numel(), rows,
+            self._stream()))
+
+    def attn_paged(self, out, q, pages, pos, part, rows: int = 1, ktab=None, act=None, table_row: int = 0):
+        """Attention over a paged cache: one row per sequence (decode), 2..8 rows (verify) or a prompt chunk of the
+        sequence with table row `table_row`; the dispatch of launch_attn_m / launch_attn_ms."""
+        st = self._stream()
+        n_seq = pos.numel()
+        if rows == 1:
+            rc = self.lib.battn_decode_paged(self.h, _ptr(out), _ptr(q), C.byref(pages), _ptr(pos), _ptr(ktab),
+                                             _ptr(act), _ptr(part), n_seq, st)
+            self._check("battn_decode_paged", rc)
+        elif rows * self.geom.group <= 32:
+            rc = self.lib.battn_verify_paged(self.h, _ptr(out), _ptr(q), C.byref(pages), _ptr(pos), _ptr(ktab),
+                                             _ptr(act), _ptr(part), rows, n_seq, st)
+            self._check("battn_verify_paged", rc)
+        else:
+            rc = self.lib.battn_prefill_paged(self.h, _ptr(out), _ptr(q), C.byref(pages), table_row, _ptr(pos),
+                                              _ptr(part), rows, st)
+            self._check("battn_prefill_paged", rc)
+
+    def attn_exact_paged(self, out, q, pages, pos, part, n_seq: int, rows: int, nsplit: int, ktab=None, act=None):
+        rc = self.lib.battn_attend_exact_paged(self.h, _ptr(out), _ptr(q), C.byref(pages), _ptr(pos), _ptr(ktab),
+                                               _ptr(act), _ptr(part), n_seq, rows, nsplit, self._stream())
+        self._check("battn_attend_exact_paged", rc)
+
     # ---- the step after attention ------------------------------------------------------------------------
     def gate_norm(self, dst, aout, gate, sgate, xq, xd, xsum, rows: int):
         """k_gate_norm_vec4 (bruce.cu:1526): sigmoid gate, L2 norm, q8 activation copy; dst may be None."""

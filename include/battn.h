@@ -38,7 +38,7 @@
 extern "C" {
 #endif
 
-#define BATTN_VERSION 2
+#define BATTN_VERSION 3
 
 /* status codes */
 enum {
@@ -253,6 +253,46 @@ int battn_partials(battn_handle* h, float* rec, const void* q, const uint8_t* kv
  *   out = sum_s o_s e^(m_s-M) / sum_s l_s e^(m_s-M), M = max_s m_s; empty records contribute 0. */
 int battn_merge(battn_handle* h, void* out, const float* parts, int n_parts, int n_rows,
                 void* stream);
+
+/* ---- Paged cache of a full-causal layer -----------------------------------------------------------------------
+ * The reference gives every slot one contiguous partition of ctx/N positions (alloc_buffers, bruce.cu:5471-5503),
+ * so a short conversation reserves as much memory as the longest one may use, and two slots whose prompts share a
+ * prefix each hold their own copy (prefix reuse is per slot, engine/src/session.h:337-346).  With a paged cache
+ * the layer is a pool of pages; a page holds page_len consecutive positions of every kv head,
+ *     page p, kv head h, position-in-page j  ->  pool + ((p * n_kv + h) * page_len + j) * record bytes,
+ * records exactly as in the contiguous layout, so a key tile of one head is still one contiguous run and every
+ * kernel streams it the same way.  `table` (device memory, int32 [n_tables][max_pages]) maps logical page
+ * pos / page_len of a sequence to a physical page; it is read by the kernels, so a host may edit it between
+ * launches without re-capturing graphs.  Sequences that share a prefix point at the same physical pages (the
+ * host un-shares the page a sequence is about to append into).  `ktab[i]` is the table row of sequence i, in
+ * place of the partition number `kslot[i]` of the contiguous calls; ktab == NULL means one sequence using row 0.
+ * A table entry outside [0, n_pages) sets BATTN_DEV_BAD_POSITION (the access is redirected to page 0, in bounds).
+ * Sliding-window layers keep their 2*window ring per slot (a bounded allocation already) and use the contiguous
+ * calls.  Results equal those of the contiguous calls on the same records, bit for bit. */
+typedef struct battn_pages {
+    uint8_t* pool_k;     /* n_pages pages of n_kv * page_len records (battn_pages_pool_bytes), 16-byte aligned */
+    uint8_t* pool_v;
+    const int* table;    /* device, [n_tables][max_pages] */
+    int n_pages, n_tables, max_pages;
+    int page_len;        /* positions per page: a power of two, 128 .. 65536 */
+} battn_pages;
+int battn_pages_pool_bytes(const battn_handle* h, int n_pages, int page_len, size_t* out_bytes);
+/* Copy on write: the K and V records of physical page from_page copied into to_page (two device-to-device copies on
+ * `stream`), for a sequence that is about to append into a page it shares with another one. */
+int battn_pages_copy(battn_handle* h, const battn_pages* pages, int from_page, int to_page, void* stream);
+/* as battn_kv_append / battn_decode / battn_verify / battn_prefill (more than 32 / group rows; one sequence, table row
+ * `table_row`) / battn_attend_exact, is_swa = 0 */
+int battn_kv_append_paged(battn_handle* h, const battn_pages* pages, const float* k, const float* v, const int* pos,
+                          const int* ktab, const int* act, int n_seq, int rows_per_seq, void* stream);
+int battn_decode_paged(battn_handle* h, void* out, const void* q, const battn_pages* pages, const int* pos,
+                       const int* ktab, const int* act, void* ws, int n_seq, void* stream);
+int battn_verify_paged(battn_handle* h, void* out, const void* q, const battn_pages* pages, const int* pos,
+                       const int* ktab, const int* act, void* ws, int rows, int batch, void* stream);
+int battn_prefill_paged(battn_handle* h, void* out, const void* q, const battn_pages* pages, int table_row,
+                        const int* pos, void* ws, int rows, void* stream);
+int battn_attend_exact_paged(battn_handle* h, void* out, const void* q, const battn_pages* pages, const int* pos,
+                             const int* ktab, const int* act, void* ws, int n_seq, int rows_per_seq, int nsplit,
+                             void* stream);
 
 /* ---- One sequence split by position range across several devices (no counterpart in the reference, which is
  * single-GPU; built on its split record and merge, bruce.cu:781-783, 992-1007) ------------------------------------

@@ -104,6 +104,91 @@ private:
     bool stop_ = false;
 };
 
+/* ---- page allocator of a paged cache, with prefix sharing between table rows ---------------------------------------
+ * Host-side owner of the page table that battn_*_paged calls read (include/battn.h): hands out pages on demand
+ * instead of the reference's fixed ctx/N partition per slot (bruce.cu:5471-5503), lets a new request start from the
+ * pages that already hold another row's prefix (the reference reuses a prefix inside one slot only,
+ * session.h:337-346), and tells the caller which page to copy before a row appends into a page it shares.
+ * Not thread-safe: the scheduler thread owns it.  The caller uploads table() (or the rows marked dirty) to the
+ * device before the next launch. */
+class PagePool {
+public:
+    PagePool(int n_pages, int page_len, int n_rows, int max_pages)
+        : page_len_(page_len), max_pages_(max_pages), table_((size_t)n_rows * max_pages, -1), used_(n_rows, 0),
+          ref_(n_pages, 0), dirty_(n_rows, 0) {
+        for (int p = n_pages - 1; p >= 0; --p) free_.push_back(p);
+    }
+    /* Row `row` can hold positions [0, n_pos) afterwards.  False (and nothing changed) when the pool or the row's
+     * table is too small. */
+    bool reserve(int row, int n_pos) {
+        const int need = (n_pos + page_len_ - 1) / page_len_;
+        int& have = used_[(size_t)row];
+        if (need > max_pages_ || need - have > (int)free_.size()) return false;
+        for (; have < need; ++have) {
+            const int p = free_.back();
+            free_.pop_back();
+            ref_[(size_t)p] = 1;
+            at(row, have) = p;
+            dirty_[(size_t)row] = 1;
+        }
+        return true;
+    }
+    /* The empty row `dst` starts with the pages that hold the first n_pos positions of `src`; only whole pages are
+     * shared.  Returns the number of positions dst now holds (a multiple of the page length). */
+    int share_prefix(int src, int dst, int n_pos) {
+        if (used_[(size_t)dst] != 0) return 0;
+        const int n = std::min(n_pos / page_len_, used_[(size_t)src]);
+        for (int i = 0; i < n; ++i) {
+            at(dst, i) = at(src, i);
+            ++ref_[(size_t)at(src, i)];
+        }
+        used_[(size_t)dst] = n;
+        if (n) dirty_[(size_t)dst] = 1;
+        return n * page_len_;
+    }
+    /* Call before appending at `pos` of `row` (the page must be reserved).  If the page is shared with another row,
+     * the row gets a private page and *from / *to name the physical pages whose records the caller must copy
+     * (battn_pages_copy) before the append; otherwise both are -1.  False when no page is free. */
+    bool make_writable(int row, int pos, int* from, int* to) {
+        *from = *to = -1;
+        int& p = at(row, pos / page_len_);
+        if (ref_[(size_t)p] <= 1) return true;
+        if (free_.empty()) return false;
+        const int q = free_.back();
+        free_.pop_back();
+        --ref_[(size_t)p];
+        ref_[(size_t)q] = 1;
+        *from = p; *to = q;
+        p = q;
+        dirty_[(size_t)row] = 1;
+        return true;
+    }
+    /* Drops the row's pages; a page returns to the pool when its last row lets go of it. */
+    void release(int row) {
+        for (int i = 0; i < used_[(size_t)row]; ++i) {
+            int& p = at(row, i);
+            if (--ref_[(size_t)p] == 0) free_.push_back(p);
+            p = -1;
+        }
+        used_[(size_t)row] = 0;
+        dirty_[(size_t)row] = 1;
+    }
+    const int* table() const { return table_.data(); }                  /* [n_rows][max_pages], -1 = unmapped */
+    const int* row(int r) const { return table_.data() + (size_t)r * max_pages_; }
+    int pages_of(int r) const { return used_[(size_t)r]; }
+    int capacity_of(int r) const { return used_[(size_t)r] * page_len_; }
+    int free_pages() const { return (int)free_.size(); }
+    int refcount(int page) const { return ref_[(size_t)page]; }
+    bool take_dirty(int r) { const bool d = dirty_[(size_t)r] != 0; dirty_[(size_t)r] = 0; return d; }
+
+private:
+    int& at(int r, int i) { return table_[(size_t)r * max_pages_ + i]; }
+    int page_len_, max_pages_;
+    std::vector<int> table_, used_, ref_;
+    std::vector<char> dirty_;
+    std::vector<int> free_;
+};
+
 /* ---- the step scheduler ----------------------------------------------------------------------------------------- */
 struct SchedConfig {
     int max_rows = 64;          /* decode rows fused into one step (the reference stops at 8, bruce.cu:94)          */

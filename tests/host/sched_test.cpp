@@ -132,6 +132,42 @@ static void test_slot_pool() {
     CHECK(got == -1);
 }
 
+static void test_page_pool() {
+    PagePool pool(/*n_pages*/ 10, /*page_len*/ 256, /*rows*/ 3, /*max_pages*/ 6);
+    CHECK(pool.free_pages() == 10);
+    CHECK(pool.reserve(0, 700) && pool.pages_of(0) == 3 && pool.capacity_of(0) == 768 && pool.free_pages() == 7);
+    CHECK(pool.reserve(0, 700) && pool.pages_of(0) == 3);                    // already there
+    CHECK(!pool.reserve(0, 6 * 256 + 1));                                    // beyond the row's table
+    CHECK(pool.take_dirty(0) && !pool.take_dirty(0));
+    // a second request shares the first 600 positions: two whole pages
+    CHECK(pool.share_prefix(0, 1, 600) == 512 && pool.pages_of(1) == 2);
+    CHECK(pool.row(1)[0] == pool.row(0)[0] && pool.row(1)[1] == pool.row(0)[1]);
+    CHECK(pool.refcount(pool.row(0)[0]) == 2 && pool.free_pages() == 7);
+    CHECK(pool.share_prefix(0, 1, 600) == 0);                                // only an empty row may adopt a prefix
+    CHECK(pool.reserve(1, 900) && pool.pages_of(1) == 4 && pool.free_pages() == 5);
+    int from, to;
+    CHECK(pool.make_writable(1, 800, &from, &to) && from == -1 && to == -1); // its own page
+    // row 1 rewrites position 300, which lives in a shared page: copy on write
+    const int shared = pool.row(0)[1];
+    CHECK(pool.make_writable(1, 300, &from, &to) && from == shared && to >= 0 && to != shared);
+    CHECK(pool.row(1)[1] == to && pool.row(0)[1] == shared && pool.refcount(shared) == 1 && pool.refcount(to) == 1);
+    CHECK(pool.free_pages() == 4);
+    // releasing the first row keeps the page the second still uses
+    const int kept = pool.row(0)[0];
+    pool.release(0);
+    CHECK(pool.pages_of(0) == 0 && pool.refcount(kept) == 1 && pool.free_pages() == 6 && pool.row(0)[0] == -1);
+    CHECK(!pool.reserve(2, 7 * 256));                                        // more than the pool holds (and the table)
+    CHECK(pool.reserve(2, 6 * 256) && pool.free_pages() == 0);
+    CHECK(!pool.reserve(0, 1));                                              // exhausted: nothing changes
+    CHECK(pool.share_prefix(1, 0, 256) == 256);                              // sharing needs no free page
+    CHECK(!pool.make_writable(0, 10, &from, &to));                           // but un-sharing does
+    pool.release(2);
+    CHECK(pool.make_writable(0, 10, &from, &to) && from == kept);
+    pool.release(0); pool.release(1);
+    CHECK(pool.free_pages() == 10);
+    for (int p = 0; p < 10; ++p) CHECK(pool.refcount(p) == 0);
+}
+
 static void test_chunk_policy() {
     SchedConfig c;
     CHECK(StepScheduler::next_chunk(c, 1, 0, 5000) == 512);          // one request, ingesting: nobody else -> solo... (pending 1)
@@ -257,6 +293,7 @@ int main() {
     test_drafter();
     test_spec_round();
     test_slot_pool();
+    test_page_pool();
     test_chunk_policy();
     test_row_graphs();
     test_spec_generation_matches_plain_decoding();
