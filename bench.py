@@ -253,6 +253,9 @@ class Layer:
         self.out = torch.zeros((1, 1, g.n_head, g.head_dim), dtype=torch.float16, device=dev)
         self.part = self.eng.alloc_part(1, 1)
         self.bytes = visible(ctx, is_swa) * POS_BYTES
+        # positions reach the device by a copy at the start of a step and the kernel before an attention call is the
+        # append of that call's row (or the previous call's merge): the order early KV streaming asks for
+        self.eng.set_early_kv_stream(True)
 
     # ---- end-to-end path: this layer's inputs and output are views into one staging buffer per step ----
     E2E_Q, E2E_K, E2E_V, E2E_POS = 0, 8192, 8192 + 4096, 8192 + 2 * 4096       # byte offsets inside a slot
@@ -1061,6 +1064,7 @@ def run_gpu(args):
                        "timed_region": f"{repeats} x the block of K = {K} steps (repeated until >= {MIN_TIMED_S} s); "
                                        "ms_per_step and value are per step of one block",
                        "block_repeats": repeats,
+                       "early_kv_stream": True,
                        "n_gt_1": "value at N > 1 = N replicas of this sweep (one sequence set per GPU); the sharded "
                                  "workloads and their efficiency are in scaling_detail"},
             "e2e": {"value": e2e_value, "unit": "TB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,

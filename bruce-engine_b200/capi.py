@@ -58,6 +58,7 @@ SIGNATURES = {
     "battn_attend_exact": (_I, [_P] * 9 + [_I, _I, _I, _I, _P]),
     "battn_partials": (_I, [_P] * 9 + [_I, _I, _I, _P]),
     "battn_merge": (_I, [_P, _P, _P, _I, _I, _P]),
+    "battn_set_early_kv_stream": (_I, [_P, _I]),
     "battn_pages_pool_bytes": (_I, [_P, _I, _I, _SZP]),
     "battn_pages_copy": (_I, [_P, _PG, _I, _I, _P]),
     "battn_kv_append_paged": (_I, [_P, _PG] + [_P] * 5 + [_I, _I, _P]),

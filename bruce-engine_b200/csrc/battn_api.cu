@@ -204,6 +204,7 @@ int launch_exact(battn_handle* h, void* out, float* rec_out, const void* q, cons
     P.scale = g.scale; P.status = h->d_status;
     apply_paging(P, pv);
     if (pv) P.n_slots = pv->n_tables;
+    h->kvw_kind = 0;
     const dim3 grid(n_seq * g.Hkv, nsplit, rows), block(32 * g.G);
     {
         ProfScope prof(h, st);
@@ -249,6 +250,10 @@ int launch_flash(battn_handle* h, void* out, float* rec_out, const void* q, cons
     P.epoch_ptr = epoch_ptr; P.epoch_advance = epoch_advance;
     apply_paging(P, pv);
     if (pv) P.n_slots = pv->n_tables;
+    // early KV streaming: only when the last launch on this handle wrote no cache rows but this call's own
+    P.early = h->early_stream && (h->kvw_kind == 0 || (h->kvw_kind == 1 && h->kvw_pos == pos && h->kvw_nseq == n_seq &&
+                                                       h->kvw_rows == rows));
+    h->kvw_kind = 0;
 
     cudaError_t e;
     if (RG > 16 && g.HD == 128 && g.W >= 64 && vt::smem_bytes(n_seq) <= SMEM_MAX) {
@@ -307,6 +312,7 @@ int launch_prefill(battn_handle* h, void* out, const void* q, const uint8_t* kvk
     P.scale_log2 = g.scale * LOG2E; P.status = h->d_status;
     apply_paging(P, pv);
     if (pv) P.slot = table_row;
+    h->kvw_kind = 0;
     const int MR = 128 / g.G;
     P.nsplit = prefill_splits(h, rows, is_swa);
     P.recs = (P.nsplit > 1 || gn) ? reinterpret_cast<float*>(ws) : nullptr;
@@ -398,6 +404,7 @@ int battn_init(const battn_geom* geom, int device, battn_handle** out_handle) {
     g = g0;
     h->device = device; h->last_cuda_error = 0; h->launches = 0; h->d_status = nullptr;
     h->prof_ev = nullptr; h->prof_cap = 0; h->prof_n = 0;
+    h->early_stream = 0; h->kvw_kind = 0; h->kvw_nseq = 0; h->kvw_rows = 0; h->kvw_pos = nullptr;
 
     cudaError_t e = cudaSetDevice(device);
     cudaDeviceProp prop;
@@ -484,6 +491,7 @@ static int kv_append_impl(battn_handle* h, const float* k, const float* v, uint8
     P.pstride = is_swa ? g.ring : g.slot_ctx; P.ring_mask = is_swa ? g.ring - 1 : -1;
     P.n_slots = g.n_slots; P.status = h->d_status;
     if (pv) { P.pg = pv->pg; P.pstride = pv->capacity; P.ring_mask = -1; P.n_slots = pv->n_tables; }
+    h->kvw_kind = 1; h->kvw_pos = pos; h->kvw_nseq = n_seq; h->kvw_rows = rows_per_seq;
     const long long warps = (long long)n_seq * rows_per_seq * g.Hkv * 2;
     const int blocks = (int)((warps + 7) / 8);
     cudaStream_t st = (cudaStream_t)stream;
@@ -507,6 +515,7 @@ int battn_kv_copy_prefix(battn_handle* h, uint8_t* kvk, uint8_t* kvv, int src_sl
     if (src_slot < 0 || dst_slot < 0 || src_slot >= g.n_slots || dst_slot >= g.n_slots || src_slot == dst_slot) return BATTN_ERR_ARG;
     if (n_pos < 0 || (!is_swa && n_pos > g.slot_ctx)) return BATTN_ERR_CAPACITY;
     if (n_pos == 0) return BATTN_OK;
+    h->kvw_kind = 2;
     CopyParams P;
     P.kvk = kvk; P.kvv = kvv; P.src = src_slot; P.dst = dst_slot; P.n_pos = n_pos; P.Hkv = g.Hkv; P.rec = g.rec;
     P.pstride = is_swa ? g.ring : g.slot_ctx; P.ring = is_swa ? g.ring : 0;
@@ -533,6 +542,7 @@ int battn_qkv_prep(battn_handle* h, void* q_out, const float* q, const float* k,
     P.table_off = theta_sel == 2 ? g.HD / 2 : 0; P.q_out_f16 = g.q_f16;
     P.pstride = is_swa ? g.ring : g.slot_ctx; P.ring_mask = is_swa ? g.ring - 1 : -1;
     P.n_slots = g.n_slots; P.status = h->d_status;
+    h->kvw_kind = 1; h->kvw_pos = pos; h->kvw_nseq = n_seq; h->kvw_rows = rows_per_seq;
     cudaStream_t st = (cudaStream_t)stream;
     cudaError_t e;
     const dim3 grid(n_seq * rows_per_seq, (g.Hq + g.Hkv + 7) / 8);
@@ -663,6 +673,7 @@ int battn_pages_copy(battn_handle* h, const battn_pages* pages, int from_page, i
     if (rc) return rc;
     if (!h || from_page < 0 || to_page < 0 || from_page >= pages->n_pages || to_page >= pages->n_pages) return BATTN_ERR_ARG;
     if (from_page == to_page) return BATTN_OK;
+    h->kvw_kind = 2;
     const size_t page_bytes = (size_t)h->g.Hkv * pages->page_len * h->g.rec;
     cudaStream_t st = (cudaStream_t)stream;
     cudaError_t e = cudaMemcpyAsync(pages->pool_k + to_page * page_bytes, pages->pool_k + from_page * page_bytes, page_bytes,
@@ -851,6 +862,12 @@ int battn_merge(battn_handle* h, void* out, const float* parts, int n_parts, int
     h->launches += 1;
     const cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? BATTN_OK : cuda_fail(h, e);
+}
+
+int battn_set_early_kv_stream(battn_handle* h, int enable) {
+    if (!h) return BATTN_ERR_ARG;
+    h->early_stream = enable != 0;
+    return BATTN_OK;
 }
 
 int battn_device_status(battn_handle* h, int* out_bits, int clear) {

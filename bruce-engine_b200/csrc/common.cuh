@@ -40,6 +40,12 @@ struct battn_handle {
     int vw_ctas_per_sm;      // resident CTAs per SM of the wide verify kernel
     int fd_ctas_per_sm[3];   // resident CTAs per SM of the flash-decode kernel, per NT in {1,2}
     int fd_smem[3];
+    // Early KV streaming of the decode kernels (see fd::Params::early): allowed for a call when the last launch on
+    // this handle wrote no cache rows other than the call's own (kvw_kind 0: none, 1: rows_per_seq rows at kvw_pos of
+    // n_seq sequences, 2: anything else).
+    int early_stream;
+    int kvw_kind, kvw_nseq, kvw_rows;
+    const int* kvw_pos;
 };
 
 // Receive area of one device in a sequence split (see XchgView in exact.cuh) and its mappings of the peers' areas.

@@ -308,25 +308,31 @@ __global__ void __launch_bounds__(MERGE_THREADS) k_merge(const MergeParams P) {
 }
 
 // The merge behind the flash-decode kernels (their work-balanced records only).  Those records are padded to
-// HD + 4 floats so that every record is 16-byte aligned: 1024 threads = HD/4 float4 lanes x 32 (or 16)
-// record groups, so the ~74..592 records of a (row, head) are read in one or two rounds of independent
-// 16-byte loads instead of a long latency chain.
+// HD + 4 floats so that every record is 16-byte aligned.  The kernel is one latency chain (header -> records ->
+// output) behind every decode call, so it is built to have as few dependent steps as possible: warp w owns the
+// float4 lanes w, w + 32, ... of the output and lane s of every warp owns records s, s + 32, ...; each warp
+// reads the (m, l) pairs itself, so the maximum, the weights, the denominator and the weighted sum are all
+// butterfly shuffles inside a warp -- one round of independent loads (up to 128 records), no block barrier, no
+// shared memory.  More records take further rounds with the running (M, L, acc) rescaled, in a fixed order.
+// (Eight warps with four float4 lanes each would fit on an SM beside the next call's decode CTAs, but measured
+// 1 us slower per call: the chain of loads and shuffles per lane is what counts here.)
 constexpr int MERGE_B_THREADS = 1024;
+constexpr int MERGE_B_KEEP = 4;           // records per lane and round
 
 template <int HD>
 __global__ void __launch_bounds__(MERGE_B_THREADS) k_merge_balanced(const MergeParams P) {
     constexpr int RS = HD + 4;                                   // floats per internal record
-    constexpr int NDQ = HD / 4, NG = MERGE_B_THREADS / NDQ;
-    __shared__ float s_m[MERGE_MAX_COUNT];
-    __shared__ float s_l[MERGE_MAX_COUNT];
-    __shared__ float s_red[MERGE_B_THREADS / 32];
-    __shared__ float4 s_acc[MERGE_B_THREADS];
+    constexpr int NWARP = MERGE_B_THREADS / 32, DPW = (HD / 4) / NWARP;   // float4 lanes per warp: 1 or 2
+    static_assert(DPW >= 1 && DPW * NWARP * 4 == HD, "one float4 lane per warp and step");
     const int hq = blockIdx.x % P.Hq, rowidx = blockIdx.x / P.Hq;
     const int i = rowidx / P.rows, r = rowidx % P.rows;
     const int kvh = hq / P.G, h = hq % P.G;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    pdl_wait();
+    // The successor may start at once: it is either a kernel of this library, which touches nothing this kernel
+    // or its predecessors write before its own griddepcontrol.wait, or a launch without the programmatic attribute,
+    // which waits for this grid to complete anyway.  The next decode call uses the head start to stream cache tiles.
     pdl_trigger();
+    pdl_wait();
     const int per = P.hdr[0];
     const int c0 = P.hdr[2 + i], c1 = P.hdr[3 + i];
     const int nt = c1 - c0;
@@ -341,69 +347,80 @@ __global__ void __launch_bounds__(MERGE_B_THREADS) k_merge_balanced(const MergeP
     const float* base = P.part + ((size_t)(clo + item) * RG + r * P.G + h) * (size_t)RS;
     const size_t stride = (size_t)RG * RS;
 
-    float mx = NEG_BIG;
-    for (int s = tid; s < count; s += MERGE_B_THREADS) {
-        const float2 ml = *reinterpret_cast<const float2*>(base + s * stride + HD);
-        s_m[s] = ml.x; s_l[s] = ml.y;
-        mx = fmaxf(mx, ml.x);
-    }
+    float M = NEG_BIG, L = 0.f;
+    float4 acc[DPW];
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    if (lane == 0) s_red[warp] = mx;
-    __syncthreads();
-    float M = s_red[lane];
+    for (int j = 0; j < DPW; ++j) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s0 = 0; s0 < count; s0 += 32 * MERGE_B_KEEP) {
+        float2 ml[MERGE_B_KEEP];
+        float4 o[MERGE_B_KEEP][DPW];
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
-    __syncthreads();
-    float ls = 0.f;
-    for (int s = tid; s < count; s += MERGE_B_THREADS) {
-        const float w = fast_exp2(s_m[s] - M);                   // records carry m in log2 units
-        s_m[s] = w;
-        ls = fmaf(s_l[s], w, ls);
-    }
+        for (int k = 0; k < MERGE_B_KEEP; ++k) {                 // every load of the round is in flight at once
+            const int s = s0 + 32 * k + lane;
+            ml[k] = make_float2(NEG_BIG, 0.f);
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) ls += __shfl_xor_sync(0xffffffffu, ls, o);
-    if (lane == 0) s_red[warp] = ls;
-    __syncthreads();
-    float L = s_red[lane];
+            for (int j = 0; j < DPW; ++j) o[k][j] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (s < count) {
+                const float* rp = base + s * stride;
+                ml[k] = *reinterpret_cast<const float2*>(rp + HD);
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
-
-    const int dq = tid % NDQ, grp = tid / NDQ;
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 8
-    for (int s = grp; s < count; s += NG) {
-        const float4 o = *reinterpret_cast<const float4*>(base + s * stride + 4 * dq);
-        const float w = s_m[s];
-        acc.x = fmaf(o.x, w, acc.x); acc.y = fmaf(o.y, w, acc.y);
-        acc.z = fmaf(o.z, w, acc.z); acc.w = fmaf(o.w, w, acc.w);
-    }
-    s_acc[tid] = acc;
-    __syncthreads();
-#pragma unroll
-    for (int st = NG / 2; st > 0; st >>= 1) {                    // fixed-order tree over the record groups
-        if (grp < st) {
-            const float4 o = s_acc[(grp + st) * NDQ + dq];
-            acc.x += o.x; acc.y += o.y; acc.z += o.z; acc.w += o.w;
-            s_acc[tid] = acc;
+                for (int j = 0; j < DPW; ++j) o[k][j] = *reinterpret_cast<const float4*>(rp + 4 * (warp + NWARP * j));
+            }
         }
-        __syncthreads();
+        float mk = ml[0].x;
+#pragma unroll
+        for (int k = 1; k < MERGE_B_KEEP; ++k) mk = fmaxf(mk, ml[k].x);
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) mk = fmaxf(mk, __shfl_xor_sync(0xffffffffu, mk, d));
+        const float Mn = fmaxf(M, mk);
+        const float sc = fast_exp2(M - Mn);                      // records carry m in log2 units
+        float ls = 0.f;
+        float4 a[DPW];
+#pragma unroll
+        for (int j = 0; j < DPW; ++j) a[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int k = 0; k < MERGE_B_KEEP; ++k) {
+            const float w = fast_exp2(ml[k].x - Mn);
+            ls = fmaf(ml[k].y, w, ls);
+#pragma unroll
+            for (int j = 0; j < DPW; ++j) {
+                a[j].x = fmaf(o[k][j].x, w, a[j].x); a[j].y = fmaf(o[k][j].y, w, a[j].y);
+                a[j].z = fmaf(o[k][j].z, w, a[j].z); a[j].w = fmaf(o[k][j].w, w, a[j].w);
+            }
+        }
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) {                       // fixed-order butterfly: every lane ends with the sums
+            ls += __shfl_xor_sync(0xffffffffu, ls, d);
+#pragma unroll
+            for (int j = 0; j < DPW; ++j) {
+                a[j].x += __shfl_xor_sync(0xffffffffu, a[j].x, d); a[j].y += __shfl_xor_sync(0xffffffffu, a[j].y, d);
+                a[j].z += __shfl_xor_sync(0xffffffffu, a[j].z, d); a[j].w += __shfl_xor_sync(0xffffffffu, a[j].w, d);
+            }
+        }
+        L = fmaf(L, sc, ls);
+#pragma unroll
+        for (int j = 0; j < DPW; ++j) {
+            acc[j].x = fmaf(acc[j].x, sc, a[j].x); acc[j].y = fmaf(acc[j].y, sc, a[j].y);
+            acc[j].z = fmaf(acc[j].z, sc, a[j].z); acc[j].w = fmaf(acc[j].w, sc, a[j].w);
+        }
+        M = Mn;
     }
-    const int d4 = 4 * dq;
-    const size_t oi = ((size_t)rowidx * P.Hq + hq) * HD + d4;
+
+    const size_t obase = ((size_t)rowidx * P.Hq + hq) * HD;
     if (xq) {
         // ---- sequence split: push this device's record to every peer, then merge what the peers pushed ----
         const XchgView& X = P.xchg;
         const int xitem = rowidx * P.Hq + hq;
         const int epoch = *X.epoch_ptr;
-        if (X.push && grp == 0) {
+        if (X.push && lane == 0) {
             const size_t slot = (((size_t)(epoch & 1) * X.world + X.rank) * X.max_items + xitem) * RS;
 #pragma unroll
             for (int d = 0; d < XCHG_MAX_WORLD; ++d)
                 if (d < X.world) {
                     float* dst = X.rec[d] + slot;                // plain stores into the peer's memory
-                    *reinterpret_cast<float4*>(dst + d4) = acc;
-                    if (dq == 0) *reinterpret_cast<float2*>(dst + HD) = make_float2(M, L);
+#pragma unroll
+                    for (int j = 0; j < DPW; ++j) *reinterpret_cast<float4*>(dst + 4 * (warp + NWARP * j)) = acc[j];
+                    if (warp == 0) *reinterpret_cast<float2*>(dst + HD) = make_float2(M, L);
                 }
             __threadfence_system();
         }
@@ -412,28 +429,39 @@ __global__ void __launch_bounds__(MERGE_B_THREADS) k_merge_balanced(const MergeP
             st_release_sys(X.flag[tid] + (size_t)X.rank * X.max_items + xitem, epoch);
         if (!X.wait || !P.out) return;
         if (!xchg_wait<HD, MERGE_B_THREADS>(X, epoch, xitem, P.status)) return;
-        if (grp == 0) xchg_merge_store<HD>(X, epoch, xitem, dq, P.out, P.out_f16, oi);
+        if (lane == 0) {
+#pragma unroll
+            for (int j = 0; j < DPW; ++j) {
+                const int dq = warp + NWARP * j;
+                xchg_merge_store<HD>(X, epoch, xitem, dq, P.out, P.out_f16, obase + 4 * dq);
+            }
+        }
         return;
     }
-    if (grp != 0) return;
-    if (P.out) {
-        const float il = L > 0.f ? 1.f / L : 0.f;
-        if (P.out_f16) {
-            const __half2 a = __floats2half2_rn(acc.x * il, acc.y * il), b = __floats2half2_rn(acc.z * il, acc.w * il);
-            *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(P.out) + oi) =
-                make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
-        } else {
-            *reinterpret_cast<float4*>(reinterpret_cast<float*>(P.out) + oi) =
-                make_float4(acc.x * il, acc.y * il, acc.z * il, acc.w * il);
+    if (lane != 0) return;
+#pragma unroll
+    for (int j = 0; j < DPW; ++j) {
+        const int d4 = 4 * (warp + NWARP * j);
+        const size_t oi = obase + d4;
+        if (P.out) {
+            const float il = L > 0.f ? 1.f / L : 0.f;
+            if (P.out_f16) {
+                const __half2 a = __floats2half2_rn(acc[j].x * il, acc[j].y * il), b = __floats2half2_rn(acc[j].z * il, acc[j].w * il);
+                *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(P.out) + oi) =
+                    make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
+            } else {
+                *reinterpret_cast<float4*>(reinterpret_cast<float*>(P.out) + oi) =
+                    make_float4(acc[j].x * il, acc[j].y * il, acc[j].z * il, acc[j].w * il);
+            }
         }
-    }
-    if (P.rec_out) {                                             // public record: HD + 2 floats, natural-log m
-        float* ro = P.rec_out + ((size_t)rowidx * P.Hq + hq) * (size_t)(HD + 2);
-        *reinterpret_cast<float2*>(ro + d4) = make_float2(acc.x, acc.y);
-        *reinterpret_cast<float2*>(ro + d4 + 2) = make_float2(acc.z, acc.w);
-        if (dq == 0) {
-            ro[HD] = M > -1e29f ? M * LN2 : M;
-            ro[HD + 1] = L;
+        if (P.rec_out) {                                         // public record: HD + 2 floats, natural-log m
+            float* ro = P.rec_out + ((size_t)rowidx * P.Hq + hq) * (size_t)(HD + 2);
+            *reinterpret_cast<float2*>(ro + d4) = make_float2(acc[j].x, acc[j].y);
+            *reinterpret_cast<float2*>(ro + d4 + 2) = make_float2(acc[j].z, acc[j].w);
+            if (d4 == 0) {
+                ro[HD] = M > -1e29f ? M * LN2 : M;
+                ro[HD + 1] = L;
+            }
         }
     }
 }

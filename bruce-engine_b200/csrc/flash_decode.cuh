@@ -56,6 +56,14 @@ struct Params {
     int* epoch_ptr;
     int epoch_advance;
     Paging pg;       // table != nullptr: paged cache of a full-causal layer (pages hold whole tiles)
+    // Early KV streaming.  The kernel is launched with programmatic stream serialisation, so its CTAs may start while
+    // the previous kernel of the stream (normally the append of this step's rows) is still running.  With early != 0
+    // the positions are read and the bulk copies of every tile that lies entirely below the step's first row are
+    // issued BEFORE griddepcontrol.wait -- those cache rows were written by earlier steps, and everything older than
+    // the immediate predecessor has completed by the time this grid starts -- so the first stages are in shared
+    // memory when the predecessor finishes.  Q, the tile that holds the step's own rows, and every write (header,
+    // records, epoch) come after the wait.  The host sets early only when the predecessor wrote no other cache rows.
+    int early;
 };
 
 template <int HD>
@@ -121,9 +129,11 @@ k_flash_decode(const Params P) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], NW); }
         mbar_fence_init();
     }
-    pdl_wait();          // nothing above reads or writes global memory
-    pdl_trigger();
-    if (P.epoch_ptr && blockIdx.x == 0 && tid == 0) *P.epoch_ptr += P.epoch_advance;
+    const bool early = P.early != 0;
+    if (!early) {
+        pdl_wait();      // nothing above reads or writes global memory
+        pdl_trigger();
+    }
     if (P.n_seq == 1) {
         // one sequence (decode / verify of a single stream): no prefix sum, one barrier
         if (tid == 0) {
@@ -159,6 +169,9 @@ k_flash_decode(const Params P) {
     const int total = P.Hkv * cum[P.n_seq];
     const int per = max(1, (total + (int)gridDim.x - 1) / (int)gridDim.x);
     if (blockIdx.x == 0) {
+        // the header and the step counter are read by the previous call's merge: written after the wait
+        if (early) { pdl_wait(); pdl_trigger(); }
+        if (P.epoch_ptr && tid == 0) *P.epoch_ptr += P.epoch_advance;
         if (tid == 0) { P.hdr[0] = per; P.hdr[1] = total; }
         for (int i = tid; i <= P.n_seq; i += NTHREADS) P.hdr[2 + i] = cum[i];
     }
@@ -170,6 +183,7 @@ k_flash_decode(const Params P) {
         // =========================== producer: one thread issues the bulk copies ===================
         if (lane == 0) {
             int cnt = 0;
+            bool waited = !early || blockIdx.x == 0;
             for (int g = g0; g < g1;) {
                 const Piece pc = locate(g, g1, cum, P.n_seq, P.Hkv);
                 const SeqRange sr = seq_range(P.pos, P.kslot, P.act, pc.i, P.rows, P.is_swa, P.W, P.slot_ctx,
@@ -184,6 +198,13 @@ k_flash_decode(const Params P) {
                     const int s = cnt % STAGES, use = cnt / STAGES;
                     const int page = page_nx;
                     if (trow && t + 1 < pc.n) page_nx = trow[((tile0 + t + 1) * TILE) >> P.pg.shift];
+                    // early streaming stops at the tile that holds this step's own rows, and before the first stage
+                    // that needs the consumers (they do not start before the predecessor has finished)
+                    if (!waited && ((tile0 + t + 1) * TILE > sr.p0 || use > 0)) {
+                        pdl_wait();
+                        pdl_trigger();
+                        waited = true;
+                    }
                     if (use > 0 && !*(volatile int*)&s_abort) {
                         if (!mbar_wait_bounded(&empty[s], (use - 1) & 1)) {
                             atomicOr(P.status, BATTN_DEV_WAIT_TIMEOUT);
@@ -203,9 +224,11 @@ k_flash_decode(const Params P) {
                 }
                 g += pc.n;
             }
+            if (!waited) { pdl_wait(); pdl_trigger(); }
         }
     } else {
         // =========================== consumers ======================================================
+        if (early && blockIdx.x != 0) { pdl_wait(); pdl_trigger(); }      // Q and the records come after the predecessor
         const int gid = lane >> 2, t4 = lane & 3;
         const int ctid = tid;                                     // 0..127
         // local key (within the 64-key tile) of MMA row kappa for this warp

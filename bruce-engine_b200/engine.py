@@ -148,6 +148,12 @@ class AttnEngine:
                                        _ptr(act), _ptr(part), rows_per_seq, rows, int(is_swa), st)
             self._check("battn_verify", rc)
 
+    def set_early_kv_stream(self, enable: bool):
+        """Whether decode calls stream the cache tiles below their first position before the preceding kernel of
+        the stream has finished (battn_set_early_kv_stream; off by default: the host must not let a kernel that
+        writes positions or older cache rows directly precede an attention call)."""
+        self._check("battn_set_early_kv_stream", self.lib.battn_set_early_kv_stream(self.h, int(enable)))
+
     def decode_noalloc(self, out, q, kvk, kvv, pos, kslot=None, act=None, is_swa: bool = False):
         """Decode attention without a caller-provided `part` buffer: the scratch is a fixed array
         inside the library (for hosts that cannot allocate device memory while serving)."""

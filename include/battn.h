@@ -248,6 +248,19 @@ int battn_partials(battn_handle* h, float* rec, const void* q, const uint8_t* kv
                    const uint8_t* kvv, const int* pos, const int* kslot, const int* act, void* ws,
                    int rows, int batch, int is_swa, void* stream);
 
+/* Early KV streaming (off by default; battn_set_early_kv_stream(h, 1) turns it on for the handle).  The decode and
+ * 2..4-row verify kernels are launched so that they may start while the previous kernel of the stream is still
+ * running; with this option they read pos / kslot / act and begin to stream the cache tiles that lie entirely below
+ * the call's first position before that kernel has finished, while Q, the tile holding the call's own rows and every
+ * write wait for it (about 0.8 us less per call).  The host promises that the kernel which precedes the call in the
+ * stream writes neither pos / kslot / act nor cache rows other than the call's own (pos[i] .. pos[i]+rows-1) --
+ * the reference's step order: positions uploaded by a copy at the start of the step (bruce.cu:8043, 8259),
+ * k_qkv_prep* right before the attention launch (:7667-7732).  Copies and graph launches order fully and are always
+ * safe predecessors.  The library additionally checks what it can see: a call streams early only if the last launch
+ * on this handle was not a cache write, or was the append / prologue of exactly these rows (same pos pointer,
+ * sequence and row counts). */
+int battn_set_early_kv_stream(battn_handle* h, int enable);
+
 /* Log-sum-exp merge of n_parts records per (row, head): k_attn_combine (bruce.cu:992-1007).
  *   parts fp32 [n_parts][n_rows][n_head][head_dim + 2]; out [n_rows][n_head][head_dim] out_dtype.
  *   out = sum_s o_s e^(m_s-M) / sum_s l_s e^(m_s-M), M = max_s m_s; empty records contribute 0. */

@@ -24,8 +24,12 @@ def _geom(name, **kw):
 
 
 def _engine(g):
+    """Early KV streaming on: positions reach the device by copies and the kernel before an attention call is this
+    library's append or merge, the order the option asks for; every case below therefore also checks that path."""
     from bruce_engine_b200.engine import AttnEngine
-    return AttnEngine(g)
+    eng = AttnEngine(g)
+    eng.set_early_kv_stream(True)
+    return eng
 
 
 class Case:

@@ -20,6 +20,7 @@ def test_decode_step_graph_replays_at_new_positions():
     n_seq, steps = 4, 7
     g = G_B.with_(slot_ctx=512, window=64, n_slots=n_seq)
     eng, og = AttnEngine(g), oracle_geom(g)
+    eng.set_early_kv_stream(True)          # append -> attention inside the graph: the order the option asks for
     HD = g.head_dim
     rng = np.random.default_rng(17)
     start = np.array([130, 0, 255, 61], dtype=np.int32)           # ragged; slot 3 crosses the window edge

@@ -108,3 +108,39 @@ def test_prefix_copied_between_slots_is_identical_and_attends_alike(is_swa):
     want = O.attend(og, q, okvk, okvv, [n_total - 1], kslot=[2], rows=1, is_swa=is_swa)
     assert_close(to_np(out), want, f"decode on a copied prefix, swa={is_swa}")
     assert eng.device_status() == 0
+
+
+def test_early_kv_streaming_waits_when_the_previous_launch_wrote_other_rows():
+    """With early KV streaming on, a decode that directly follows a prefix copy into its slot, or the append of a
+    300-row chunk, must still see those rows: the library streams early only behind the append of the call's own rows."""
+    g, eng = _engine(slot_ctx=2048, window=256, n_slots=2)
+    eng.set_early_kv_stream(True)
+    og = oracle_geom(g)
+    n0, n1 = 1500, 1800
+    _, k, v = draw_qkv(g, n1, 1, seed=33)
+    kvk, kvv = eng.alloc_kv_layer(False, fill=0)
+    gpu_fill(eng, k[:n0], v[:n0], kvk, kvv, False, slot=0)
+    okvk, okvv = oracle_fill(og, k[:n0], v[:n0], False, slot=0)
+    rng = np.random.default_rng(3)
+    q = rng.standard_normal((1, 1, g.n_head, g.head_dim), dtype=np.float32).astype(np.float16).astype(np.float32)
+    qd, part = dev_q(eng, q), eng.alloc_part(1, 1)
+    want = O.attend(og, q, okvk, okvv, [n0 - 1], kslot=[0], rows=1)
+    per_slot = g.layer_bytes(False) // g.n_slots
+    pos, one = dev_i32([n0 - 1], "cuda"), dev_i32([1], "cuda")
+    for trial in range(4):
+        kvk[per_slot:].zero_()
+        kvv[per_slot:].zero_()
+        out = new_out(eng, 1, 1, g.n_head, g.head_dim)
+        eng.kv_copy_prefix(kvk, kvv, 0, 1, n0)                       # no synchronisation before the decode
+        eng.launch_attn_ms(out, qd, kvk, kvv, pos, one, None, part, 1)
+        torch.cuda.synchronize()
+        assert_close(to_np(out), want, f"decode right behind a prefix copy, trial {trial}")
+    # a 300-row chunk appended at n0, then a decode at the chunk's last row through another position buffer
+    kd, vd = torch.from_numpy(k[n0:]).cuda(), torch.from_numpy(v[n0:]).cuda()
+    out = new_out(eng, 1, 1, g.n_head, g.head_dim)
+    eng.qkv_prep_store(kd, vd, kvk, kvv, dev_i32([n0], "cuda"), kslot=dev_i32([0], "cuda"), rows=n1 - n0)
+    eng.launch_attn_ms(out, qd, kvk, kvv, dev_i32([n1 - 1], "cuda"), dev_i32([0], "cuda"), None, part, 1)
+    torch.cuda.synchronize()
+    okvk, okvv = oracle_fill(og, k, v, False, slot=0)
+    assert_close(to_np(out), O.attend(og, q, okvk, okvv, [n1 - 1], kslot=[0], rows=1), "decode right behind a chunk append")
+    assert eng.device_status() == 0
