@@ -256,6 +256,7 @@ int launch_flash(battn_handle* h, void* out, float* rec_out, const void* q, cons
     h->kvw_kind = 0;
 
     cudaError_t e;
+    int fd_grid = 0;                                   // grid of the flash-decode kernel, when that one runs
     if (RG > 16 && g.HD == 128 && g.W >= 64 && vt::smem_bytes(n_seq) <= SMEM_MAX) {
         // 5..8 rows at head_dim 128: the tensor-memory verify kernel, one CTA per SM (128-key tiles must not wrap the
         // ring, hence the window bound; very large batches exceed its shared memory and take the kernel below)
@@ -281,6 +282,7 @@ int launch_flash(battn_handle* h, void* out, float* rec_out, const void* q, cons
         if (per_sm > h->fd_ctas_per_sm[idx]) per_sm = h->fd_ctas_per_sm[idx];
         if (per_sm < 1) per_sm = 1;
         const int grid = h->num_sms * per_sm;
+        fd_grid = grid;
         ProfScope prof(h, st);
         if (g.HD == 128) e = idx == 0 ? launch_fd_kernel<128, 1>(P, grid, smem, st) : launch_fd_kernel<128, 2>(P, grid, smem, st);
         else             e = idx == 0 ? launch_fd_kernel<256, 1>(P, grid, smem, st) : launch_fd_kernel<256, 2>(P, grid, smem, st);
@@ -290,6 +292,11 @@ int launch_flash(battn_handle* h, void* out, float* rec_out, const void* q, cons
     M.mode = 0; M.part = P.part; M.out = out; M.rec_out = rec_out;
     M.n_rows = n_seq * rows; M.rows = rows; M.Hq = g.Hq; M.Hkv = g.Hkv; M.G = g.G;
     M.count = 0; M.log2_domain = 1; M.out_f16 = g.out_f16; M.hdr = P.hdr; M.status = h->d_status;
+    if (P.early && fd_grid > 0 && n_seq == 1) {
+        // the merge recomputes the cut from the positions while it waits for the decode kernel
+        M.pre_grid = fd_grid; M.pre_tile = fd::TILE;
+        M.pos = pos; M.kslot = kslot; M.act = act; M.is_swa = is_swa; M.W = g.W; M.slot_ctx = P.slot_ctx; M.n_slots = P.n_slots;
+    }
     if (xv) M.xchg = *xv;
     if (g.HD == 128) e = launch_pdl(k_merge_balanced<128>, dim3(n_seq * rows * g.Hq), dim3(MERGE_B_THREADS), 0, st, M);
     else             e = launch_pdl(k_merge_balanced<256>, dim3(n_seq * rows * g.Hq), dim3(MERGE_B_THREADS), 0, st, M);

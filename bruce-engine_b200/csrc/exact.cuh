@@ -209,6 +209,9 @@ struct MergeParams {
     int* status;
     // k_merge_balanced only: header written by the flash-decode kernel: {tiles_per_cta, total, cum[n_seq+1]}
     const int* hdr;
+    // k_merge_balanced, single sequence behind an early-streaming decode kernel: the work cut is recomputed from the
+    // positions before the wait (pre_grid CTAs, pre_tile keys per tile) instead of read from the header after it
+    int pre_grid, pre_tile;
     // sequence split across devices (k_merge_balanced as the pushing epilogue, k_merge_wait): see XchgView
     XchgView xchg;
 };
@@ -332,9 +335,20 @@ __global__ void __launch_bounds__(MERGE_B_THREADS) k_merge_balanced(const MergeP
     // or its predecessors write before its own griddepcontrol.wait, or a launch without the programmatic attribute,
     // which waits for this grid to complete anyway.  The next decode call uses the head start to stream cache tiles.
     pdl_trigger();
+    int per = 1, c0 = 0, c1 = 0;
+    const bool pre = P.pre_grid > 0;
+    if (pre) {
+        // what the decode kernel derives from the same positions (flash_decode.cuh): one L2 round trip less behind the wait
+        const SeqRange sr = seq_range(P.pos, P.kslot, P.act, 0, P.rows, P.is_swa, P.W, P.slot_ctx, P.n_slots, P.status);
+        c1 = sr.active ? ((sr.hi + P.pre_tile - 1) / P.pre_tile - sr.lo / P.pre_tile) : 0;
+        per = max(1, (P.Hkv * c1 + P.pre_grid - 1) / P.pre_grid);
+    }
     pdl_wait();
-    const int per = P.hdr[0];
-    const int c0 = P.hdr[2 + i], c1 = P.hdr[3 + i];
+    if (!pre) {
+        per = P.hdr[0];
+        c0 = P.hdr[2 + i];
+        c1 = P.hdr[3 + i];
+    }
     const int nt = c1 - c0;
     const bool xq = P.xchg.world > 0;                            // this launch feeds a cross-device exchange
     if (nt <= 0 && !xq) return;                                  // inactive sequence: no output
