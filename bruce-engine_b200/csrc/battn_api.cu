@@ -19,6 +19,10 @@
 
 using namespace battn;
 
+#ifndef BATTN_PF_PAIR
+#define BATTN_PF_PAIR 1
+#endif
+
 namespace {
 
 // The wait self-test: thread 0 waits on an mbarrier that has one pending arrival nobody will make.
@@ -83,7 +87,11 @@ cudaError_t fd_prepare_all(battn_handle* h) {
         e = cudaFuncSetAttribute((const void*)vt::k_verify_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX);
         if (e != cudaSuccess) return e;
     }
-    if (HD == 128) e = cudaFuncSetAttribute((const void*)pf128::k_prefill_hd128, cudaFuncAttributeMaxDynamicSharedMemorySize, pf128::TOTAL);
+    if (HD == 128) {
+        e = cudaFuncSetAttribute((const void*)pf128::k_prefill_hd128<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, pf128::TOTAL);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute((const void*)pf128::k_prefill_hd128<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, pf128::TOTAL_PAIR);
+    }
     else           e = cudaFuncSetAttribute((const void*)pf::k_prefill<256, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, pf::Cfg<256, 64>::TOTAL);
     if (e != cudaSuccess) return e;
     if ((e = fd_prepare<HD, 1>(h, 0)) != cudaSuccess) return e;
@@ -326,7 +334,19 @@ int launch_prefill(battn_handle* h, void* out, const void* q, const uint8_t* kvk
     const dim3 grid((rows + MR - 1) / MR, g.Hkv, P.nsplit);
     {
         ProfScope prof(h, st);
-        if (g.HD == 128) pf128::k_prefill_hd128<<<grid, pf128::NTHREADS, pf128::TOTAL, st>>>(P);
+        if (g.HD == 128 && BATTN_PF_PAIR && grid.x >= 2) {
+            // two M tiles per cluster of two CTAs (tcgen05.mma.cta_group::2): each CTA converts half of every operand
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3((grid.x + 1) & ~1u, grid.y, grid.z); cfg.blockDim = dim3(pf128::NTHREADS);
+            cfg.dynamicSmemBytes = pf128::TOTAL_PAIR; cfg.stream = st;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+            cfg.attrs = attr; cfg.numAttrs = 1;
+            cudaLaunchKernelEx(&cfg, pf128::k_prefill_hd128<true>, P);
+        } else if (g.HD == 128) {
+            pf128::k_prefill_hd128<false><<<grid, pf128::NTHREADS, pf128::TOTAL, st>>>(P);
+        }
         else             pf::k_prefill<256, 64><<<grid, pf::NTHREADS, pf::Cfg<256, 64>::TOTAL, st>>>(P);
     }
     h->launches += 1;

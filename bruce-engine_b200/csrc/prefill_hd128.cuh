@@ -5,14 +5,22 @@
 // Behaviour replaced: k_attn_tc_rs_opt<NW,...> for rows > 8 and its dispatch
 // (engine/src/bruce.cu:2750-3131, 4021-4078); masks as bruce.cu:2799-2805, 3012-3029.
 //
-// One CTA per (128-row M tile, kv head); the keys stream through in tiles of 64.  Twenty warps, each
-// warpgroup resized with setmaxnreg for its role:
+// One CTA per (128-row M tile, kv head); the keys stream through in tiles of 64.  Chunks of more than one M tile
+// run as clusters of two CTAs (template parameter PAIR): 256 rows per pair with tcgen05.mma.cta_group::2, issued
+// by the first CTA of the cluster.  Every CTA keeps its own 128 rows of Q, S, P and O in its tensor memory, but
+// the B operands are split between the two: a CTA converts and holds only 32 of a tile's 64 keys of the K operand
+// and 64 of the 128 head dimensions (plus a block of ones) of the V^T operand, so the int8 -> fp16 conversion per
+// attended row is halved; "my share is ready" is a plain remote mbarrier arrive on the issuing CTA's barrier (a
+// cluster-scope release there stalled every dequant warp on a memory barrier and cost 20 %), completion comes back
+// through tcgen05.commit with a two-CTA multicast.  In that mode the S products are issued for two key tiles at a
+// time (N = 128): a 64-column product runs at about half the tensor rate.
+// Twenty warps, each warpgroup resized with setmaxnreg for its role:
 //   warps 0-3   softmax group A (even key tiles), one thread per accumulator row
 //   warps 4-7   softmax group B (odd key tiles), one thread per accumulator row
 //   warps 8-11  K dequant: raw q8_0 records -> fp16 K operand [key][dim], scale folded in
 //   warps 12-15 V dequant: raw q8_0 records -> fp16 V^T operand [dim][key], scale folded in
 //   warp 16     issues the S MMAs, warp 19 the P.V MMAs;  warps 17/18 stream raw K / V tiles with bulk copies
-// Data flow per key tile j (every ring below is three deep and indexed j mod 3):
+// Data flow per key tile j (every ring below is three deep -- four in a pair -- and indexed j mod the depth):
 //   loader -> raw K/V tile (shared memory) -> dequant -> fp16 operand (128-byte-swizzled shared memory)
 //   K operand         two fp16 parts per value: hi = fp16(d*x) and lo = d*x - hi (exact: the product of an int8
 //                     and an fp16 scale has 19 significant bits, fp16 keeps 11, the rest fits the second part),
@@ -44,45 +52,116 @@ namespace pf128 {
 
 using namespace pf;
 
-#ifndef BATTN_PF_NB
-#define BATTN_PF_NB 3
-#endif
-#ifndef BATTN_PF_KLO
-#define BATTN_PF_KLO 1
-#endif
-constexpr int HD = 128, BN = 64, NB = BATTN_PF_NB;     // NB: depth of every ring (raw tiles, operands, S/P)
-constexpr bool KLO = BATTN_PF_KLO != 0;
+constexpr int HD = 128, BN = 64;
 constexpr int NBLK = HD / 32, REC = HD + 2 * NBLK;
 constexpr int NTHREADS = 640;
 constexpr int W_KDQ = 8, W_VDQ = 12, W_MMA = 16, W_LDK = 17, W_LDV = 18, W_PV = 19;
 constexpr int REGS_LAUNCH = 96, REGS_SOFT = 144, REGS_DEQ = 72, REGS_CTL = 40;
 static_assert(2 * REGS_SOFT + 2 * REGS_DEQ + REGS_CTL <= 5 * REGS_LAUNCH, "register budget per scheduler");
 
-constexpr int VROWS = HD + 16;                         // V^T operand rows: head_dim + the block of ones
-constexpr int K_BYTES = BN * HD * 2;                   // two 64-dim sub-tiles of [64 keys][128 B]
-constexpr int V_BYTES = VROWS * 128;                   // [144 rows][64 keys] fp16
 constexpr int RAW_BYTES = BN * REC;
-constexpr int OFF_K = 0;                                // K operand, high part: fp16(d * x)
-constexpr int OFF_KLO = OFF_K + NB * K_BYTES;           // K operand, low part: fp16(d * x - high part), exact
-constexpr int OFF_V = OFF_KLO + (KLO ? NB * K_BYTES : 0);
-constexpr int OFF_RAWK = OFF_V + NB * V_BYTES;
-constexpr int OFF_RAWV = OFF_RAWK + NB * RAW_BYTES;
-constexpr int OFF_BAR = OFF_RAWV + NB * RAW_BYTES;
 enum { B_KRAW_FULL = 0, B_KRAW_FREE = 4, B_VRAW_FULL = 8, B_VRAW_FREE = 12, B_KF = 16, B_S = 20, B_P = 24, B_PV = 28,
-       N_BARS = 32 };
-constexpr int OFF_MISC = OFF_BAR + N_BARS * 8;          // [0] tmem base, [1] abort flag, [4..7] decision sequence
-constexpr int OFF_MREF = OFF_MISC + 32;                 // [128] row references
-constexpr int TOTAL = OFF_MREF + 128 * 4 + 1024;        // + slack to align the base to 1024
-static_assert(TOTAL <= 226 * 1024, "shared memory budget");
-static_assert(K_BYTES % 1024 == 0 && V_BYTES % 1024 == 0 && RAW_BYTES % 16 == 0, "operand alignment");
+       B_Q = 32, N_BARS = 33 };
 
-constexpr int T_O = 0;                                  // tensor-memory columns
-constexpr int T_L = HD;                                 // 16 columns, each = sum of P
-constexpr int T_S = HD + 32;                            // NB S/P buffers of BN columns
-constexpr int T_Q = T_S + NB * BN;                      // HD/2 columns of fp16 pairs
-static_assert(T_Q + HD / 2 <= TMEM_COLS, "tensor memory budget");
+// Shared- and tensor-memory layout.  PAIR = false: one CTA per 128-row M tile.  PAIR = true: two CTAs of a cluster
+// work on 256 rows with tcgen05.mma.cta_group::2 -- every CTA keeps its own 128 rows of Q, S, P and O, but the B
+// operands are split between them: each CTA converts and holds only 32 of a tile's 64 keys of the K operand and
+// 64 of the 128 head dimensions (plus its own block of ones) of the V^T operand, so the conversion work per
+// attended row is halved.
+template <bool PAIR>
+struct Lay {
+    // depth of every ring (raw tiles, operands, S/P); PAIR: four, because the S products are issued for two tiles at
+    // a time (N = 128: a 64-column S product runs at about half the tensor rate, measured) and the two tiles'
+    // K operands and S buffers are neighbours in their rings
+    static constexpr int NB = PAIR ? 4 : 3;
+    static constexpr bool S2 = PAIR;
+    static constexpr int KROWS = PAIR ? BN / 2 : BN;        // K operand rows (keys) this CTA holds per tile
+    static constexpr int K_SUB = KROWS * 128;                // one 64-dim sub-tile [KROWS][128 B]
+    static constexpr int K_BYTES = 2 * K_SUB;
+    static constexpr int VDIMS = PAIR ? HD / 2 : HD;         // head dimensions of the V^T operand this CTA holds
+    static constexpr int VROWS = VDIMS + 16;                 // + the block of ones
+    static constexpr int V_BYTES = VROWS * 128;              // [VROWS][64 keys] fp16
+    static constexpr int N_PV = PAIR ? 2 * VROWS : VROWS;    // N of the P.V product: 160 or 144
+    static constexpr int OFF_K = 0;                          // K operand, high part: fp16(d * x)
+    static constexpr int OFF_KLO = OFF_K + NB * K_BYTES;     // K operand, low part: fp16(d * x - high part), exact
+    static constexpr int OFF_V = OFF_KLO + NB * K_BYTES;
+    static constexpr int OFF_RAWK = OFF_V + NB * V_BYTES;
+    static constexpr int OFF_RAWV = OFF_RAWK + NB * RAW_BYTES;
+    static constexpr int OFF_BAR = OFF_RAWV + NB * RAW_BYTES;
+    static constexpr int OFF_MISC = OFF_BAR + N_BARS * 8 + 8;   // [0] tmem base, [1] abort flag, [4..7] decision sequence
+    static constexpr int OFF_MREF = OFF_MISC + 32;           // [128] row references
+    static constexpr int TOTAL = OFF_MREF + 128 * 4 + 1024;  // + slack to align the base to 1024
+    static_assert(TOTAL <= 226 * 1024, "shared memory budget");
+    static_assert(K_SUB % 1024 == 0 && V_BYTES % 1024 == 0 && RAW_BYTES % 16 == 0, "operand alignment");
+    // tensor-memory columns.  PAIR: the P.V product has N = 160 = [dims 0-63 | ones | dims 64-127 | ones], so the
+    // two halves of O sit at columns 0 and 80 and the denominator at column 64.
+    static constexpr int T_O = 0;
+    static constexpr int T_OHI = PAIR ? VROWS : HD / 2;      // column of dims 64..127
+    static constexpr int T_L = PAIR ? HD / 2 : HD;           // 16 columns, each = sum of P
+    static constexpr int T_S = HD + 32;                      // NB S/P buffers of BN columns
+    static constexpr int T_Q = T_S + NB * BN;                // HD/2 columns of fp16 pairs
+    static_assert(N_PV <= T_S && T_Q + HD / 2 <= TMEM_COLS, "tensor memory budget");
+    __device__ static constexpr int ocol(int c) { return c < 2 ? c * 32 : T_OHI + (c - 2) * 32; }   // 32-column chunk c of O
+    // byte offset of sub-tile `sub` of the K operand in ring slot `sl`.  S2: slots 2p and 2p+1 interleave, so that
+    // the rows of both tiles are consecutive 8-row groups of one operand with N = 128.
+    __device__ static constexpr int koff(int sl, int sub) {
+        return S2 ? (sl >> 1) * (2 * K_BYTES) + sub * (2 * K_SUB) + (sl & 1) * K_SUB : sl * K_BYTES + sub * K_SUB;
+    }
+    // S2, cta_group::2: columns of the pair's 128-column S product are [tile 2p keys 0-31 | tile 2p+1 keys 0-31 |
+    // tile 2p keys 32-63 | tile 2p+1 keys 32-63] (each CTA supplies its rows of both tiles); a last tile without a
+    // partner is an ordinary 64-column product in the first half.  First 32-column chunk of the tile in slot sl, and
+    // distance to its second chunk:
+    __device__ static constexpr int scol(int sl) { return S2 ? (sl >> 1) * (2 * BN) + (sl & 1) * 32 : sl * BN; }
+    __device__ static constexpr int schunk(bool paired) { return S2 && paired ? 64 : 32; }
+};
+constexpr int TOTAL = Lay<false>::TOTAL, TOTAL_PAIR = Lay<true>::TOTAL;
 
+// ---- cluster helpers (PAIR) -------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_rank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// arrive on the barrier at the same shared-memory offset in CTA `cta` of the cluster
+__device__ __forceinline__ void mbar_arrive_remote(uint64_t* bar, uint32_t cta) {
+    uint32_t ra;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(smem_u32(bar)), "r"(cta));
+#ifdef BATTN_PF_ARRIVE_CLUSTER_RELEASE
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(ra) : "memory");
+#else
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(ra) : "memory");
+#endif
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// the two-CTA forms of the MMA (A in tensor memory) and of its completion signal, which arrives on the barrier at
+// the same offset in both CTAs of the pair
+__device__ __forceinline__ void umma2_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(acc)
+        : "memory");
+}
+__device__ __forceinline__ void umma2_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(smem_u32(bar)), "h"((uint16_t)3) : "memory");
+}
+
+template <bool PAIR>
 __global__ void __maxnreg__(REGS_LAUNCH) k_prefill_hd128(const Params P) {
+    using L = Lay<PAIR>;
+    constexpr int NB = L::NB;
+    constexpr int OFF_K = L::OFF_K, OFF_KLO = L::OFF_KLO, OFF_V = L::OFF_V, OFF_RAWK = L::OFF_RAWK, OFF_RAWV = L::OFF_RAWV;
+    constexpr int OFF_BAR = L::OFF_BAR, OFF_MISC = L::OFF_MISC, OFF_MREF = L::OFF_MREF;
+    constexpr int K_SUB = L::K_SUB, V_BYTES = L::V_BYTES, VDIMS = L::VDIMS;
+    constexpr int T_O = L::T_O, T_L = L::T_L, T_S = L::T_S, T_Q = L::T_Q;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);      // 1024-byte aligned
     uint8_t* Ksm = smem + OFF_K;
@@ -95,19 +174,27 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill_hd128(const Params P) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = P.G, MR = 128 / G;                        // query positions per M tile
     const int n_mt = (P.rows + MR - 1) / MR;
-    const int mt = n_mt - 1 - (int)blockIdx.x;              // longest key ranges first (bruce.cu:2770)
+    // PAIR: CTA 0 of a cluster (the one that issues the MMAs) takes the later M tile of its pair, CTA 1 the one
+    // before it; with an odd number of M tiles the last pair's second CTA has no rows of its own (mt = -1) and
+    // only contributes its halves of the operands.
+    const int crank = PAIR ? (int)cluster_rank() : 0;
+    const bool leader = crank == 0;
+    const int mt_pair = n_mt - 1 - (PAIR ? (int)blockIdx.x & ~1 : (int)blockIdx.x);    // longest key ranges first (bruce.cu:2770)
+    const int mt = mt_pair - crank;
     const int kvh = blockIdx.y;
     const int p0 = P.pos[0];
     if (p0 < 0 || (!P.is_swa && p0 + P.rows > P.slot_ctx)) {
         if (tid == 0) atomicOr(P.status, BATTN_DEV_BAD_POSITION);
         return;
     }
-    const int rbase = mt * MR;
-    const int rows_eff = min(MR, P.rows - rbase);
+    const int rbase = max(mt, 0) * MR;
+    const int rows_eff = mt < 0 ? 0 : min(MR, P.rows - rbase);
     const int p_first = p0 + rbase, p_last = p_first + rows_eff - 1;
-    const int lo_cta = P.is_swa ? max(0, p_first + 1 - P.W) : 0;       // bruce.cu:2801
-    const int hi_cta = p_last + 1;
     const int full_lo = P.is_swa ? max(0, p_last + 1 - P.W) : 0;
+    // key range of the CTA, or of the pair (both CTAs walk the same tiles)
+    const int rbase_lo = PAIR ? max(mt_pair - 1, 0) * MR : rbase;
+    const int lo_cta = P.is_swa ? max(0, p0 + rbase_lo + 1 - P.W) : 0;       // bruce.cu:2801
+    const int hi_cta = p0 + min(P.rows, (mt_pair + 1) * MR);
     // key split: gridDim.z CTAs share this (M tile, kv head), each takes a contiguous share of the key tiles
     const int tile_lo = lo_cta / BN;
     const int n_all = (hi_cta + BN - 1) / BN - tile_lo;
@@ -129,29 +216,40 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill_hd128(const Params P) {
         for (int b = 0; b < NB; ++b) {
             mbar_init(&bars[B_KRAW_FULL + b], 1); mbar_init(&bars[B_VRAW_FULL + b], 1);
             mbar_init(&bars[B_KRAW_FREE + b], 4); mbar_init(&bars[B_VRAW_FREE + b], 4);
-            mbar_init(&bars[B_KF + b], 4);
             mbar_init(&bars[B_S + b], 1); mbar_init(&bars[B_PV + b], 1);
-            mbar_init(&bars[B_P + b], 8);                      // 4 softmax warps (P written) + 4 V dequant warps (operand ready)
+            // K operand ready: 4 dequant warps; P written and V operand ready: 4 softmax + 4 dequant warps --
+            // PAIR: of both CTAs, counted on the issuing CTA's barriers
+            mbar_init(&bars[B_KF + b], PAIR ? 8 : 4);
+            mbar_init(&bars[B_P + b], PAIR ? 16 : 8);
         }
+        mbar_init(&bars[B_Q], 1);
         misc[1] = 0;
         misc[4] = misc[5] = misc[6] = misc[7] = 0;
         mbar_fence_init();
     }
     if (tid < 128) mref[tid] = NEG_BIG;
     if (warp == W_MMA) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
-                         smem_u32(const_cast<uint32_t*>(&misc[0]))), "r"(TMEM_COLS) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if (PAIR) {
+            // the same warp of both CTAs of the pair allocates the same columns in both tensor memories
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                             smem_u32(const_cast<uint32_t*>(&misc[0]))), "r"(TMEM_COLS) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                             smem_u32(const_cast<uint32_t*>(&misc[0]))), "r"(TMEM_COLS) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
-    // rows HD .. HD+15 of every V^T operand buffer: ones (the denominator columns of the P.V MMA)
+    // the last sixteen rows of every V^T operand buffer: ones (the denominator columns of the P.V MMA)
     for (int idx = tid; idx < NB * 16 * 8; idx += NTHREADS) {
         const int b = idx / (16 * 8), rem = idx - b * (16 * 8);
-        reinterpret_cast<uint4*>(Vsm + b * V_BYTES + HD * 128)[rem] =
+        reinterpret_cast<uint4*>(Vsm + b * V_BYTES + VDIMS * 128)[rem] =
             make_uint4(0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u);
     }
     proxy_fence();
     tc_fence_before();
     __syncthreads();
+    if (PAIR) cluster_sync_all();          // both CTAs' barriers are initialised before either arrives on the other's
     tc_fence_after();
     const uint32_t tmem = misc[0];
     // Q into tensor memory: lane = row m = (position m / G, head m % G) (the reference's pair packing,
@@ -189,16 +287,40 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill_hd128(const Params P) {
         tc_fence_before();
         named_bar_sync(3, 9 * 32);
         tc_fence_after();
+        // PAIR: the issuing CTA's S MMA reads Q from both tensor memories
+        if (PAIR && !leader && warp == W_MMA && lane == 0) mbar_arrive_remote(&bars[B_Q], 0);
     }
 
     // bounded wait that degrades to "do not wait" once any wait has run out
     auto wait = [&](int b, uint32_t parity, uint32_t sleep_ns) {
         if (mbar_try_wait(&bars[b], parity)) return;               // the common case costs one poll
         if (misc[1]) return;
+#ifdef BATTN_PF_SLEEP_DIV
+        sleep_ns = sleep_ns / BATTN_PF_SLEEP_DIV;
+#endif
         if (!mbar_wait_backoff(&bars[b], parity, sleep_ns)) {
             atomicOr(P.status, BATTN_DEV_WAIT_TIMEOUT);
             misc[1] = 1;
         }
+    };
+    // the same for a barrier the other CTA of the pair arrives on (acquire at cluster scope)
+    auto wait_pair = [&](int b, uint32_t parity, uint32_t sleep_ns) {
+#ifndef BATTN_PF_WAIT_CLUSTER_ACQUIRE
+        wait(b, parity, sleep_ns);
+        return;
+#endif
+        if (!PAIR) { wait(b, parity, sleep_ns); return; }
+        if (misc[1]) return;
+        for (uint32_t i = 0; i < (1u << 22); ++i) {
+            if (mbar_try_wait_cluster(&bars[b], parity)) return;
+            __nanosleep(sleep_ns);
+        }
+        atomicOr(P.status, BATTN_DEV_WAIT_TIMEOUT);
+        misc[1] = 1;
+    };
+    // "this CTA's share of tile j is ready": on the own barrier, or on the issuing CTA's
+    auto arrive_issuer = [&](int b) {
+        if (PAIR) mbar_arrive_remote(&bars[b], 0); else mbar_arrive(&bars[b]);
     };
     // ring slot and phase parity of tile j
     auto slot = [](int j) { return j % NB; };
@@ -208,42 +330,66 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill_hd128(const Params P) {
 
     if (warp >= W_MMA) {
         regs_shrink<REGS_CTL>();                                   // the whole last warpgroup
-        if (warp == W_MMA && lane == 0) {
+        if (warp == W_MMA && lane == 0 && leader) {
             // ======================= S = Q K^T for every tile ===========================================
             // Runs ahead of the P.V issuer as far as the rings allow: S of tile j refills the buffer whose P
             // the P.V MMA of tile j-NB has consumed.
-            const uint32_t idS = umma_idesc(128, BN);
+            const uint32_t idS = umma_idesc(PAIR ? 256 : 128, BN);
             const uint64_t kd0 = umma_desc(smem_u32(Ksm)), kl0 = umma_desc(smem_u32(Klo));
-            for (int j = 0; j < n_tiles; ++j) {
-                wait(B_KF + slot(j), phase(j), 20);
-                if (j >= NB) wait(B_PV + slot(j), phase(j - NB), 20);
+            if (PAIR) wait_pair(B_Q, 0, 20);                               // the other CTA's Q is in its tensor memory
+            const int step = L::S2 ? 2 : 1;
+            for (int j = 0; j < n_tiles; j += step) {
+                const bool two = L::S2 && j + 1 < n_tiles;                 // tiles j and j+1 in one product
+                const int jl = two ? j + 1 : j;
+                wait_pair(B_KF + slot(j), phase(j), 20);
+                if (two) wait_pair(B_KF + slot(jl), phase(jl), 20);
+                // the S buffers are free once the P.V products that read them are complete (products complete in
+                // order).  S2: always both buffers of the ring pair -- a last tile without a partner is a 64-column
+                // product that spills over the partner buffer's first chunk.
+                const int jw = L::S2 ? j + 1 : j;
+                if (jw >= NB) wait(B_PV + slot(jw), phase(jw - NB), 20);
                 tc_fence_after();
-                const uint32_t d = tmem + T_S + slot(j) * BN;
-                const uint64_t kd = kd0 + (uint64_t)(slot(j) * (K_BYTES >> 4));
-                const uint64_t kl = kl0 + (uint64_t)(slot(j) * (K_BYTES >> 4));
+                const uint32_t d = tmem + T_S + L::scol(slot(j));
+                const uint32_t id = two ? umma_idesc(256, 2 * BN) : idS;
+                const uint32_t sub_step = (uint32_t)((L::S2 ? 2 * K_SUB : K_SUB) >> 4);
+                const uint64_t kd = kd0 + (uint64_t)(L::koff(slot(j), 0) >> 4);
+                const uint64_t kl = kl0 + (uint64_t)(L::koff(slot(j), 0) >> 4);
                 // S = Q K_hi^T + Q K_lo^T: the two fp16 parts add up to the exact product d * x of every cached
                 // value, so the scores carry no rounding of the K operand
 #pragma unroll
-                for (int ks = 0; ks < HD / 16; ++ks)
-                    umma_f16_ts(d, tmem + T_Q + 8 * ks, kd + (uint64_t)((ks >> 2) * ((BN * 128) >> 4) + 2 * (ks & 3)), idS, ks > 0);
+                for (int ks = 0; ks < HD / 16; ++ks) {
+                    const uint64_t off = (uint64_t)((ks >> 2) * sub_step + 2 * (ks & 3));
+                    if (PAIR) umma2_f16_ts(d, tmem + T_Q + 8 * ks, kd + off, id, ks > 0);
+                    else      umma_f16_ts(d, tmem + T_Q + 8 * ks, kd + off, id, ks > 0);
+                }
 #pragma unroll
-                for (int ks = 0; KLO && ks < HD / 16; ++ks)
-                    umma_f16_ts(d, tmem + T_Q + 8 * ks, kl + (uint64_t)((ks >> 2) * ((BN * 128) >> 4) + 2 * (ks & 3)), idS, 1u);
-                umma_commit(&bars[B_S + slot(j)]);
+                for (int ks = 0; ks < HD / 16; ++ks) {
+                    const uint64_t off = (uint64_t)((ks >> 2) * sub_step + 2 * (ks & 3));
+                    if (PAIR) umma2_f16_ts(d, tmem + T_Q + 8 * ks, kl + off, id, 1u);
+                    else      umma_f16_ts(d, tmem + T_Q + 8 * ks, kl + off, id, 1u);
+                }
+                if (PAIR) {
+                    umma2_commit(&bars[B_S + slot(j)]);
+                    if (two) umma2_commit(&bars[B_S + slot(jl)]);
+                } else {
+                    umma_commit(&bars[B_S + slot(j)]);
+                }
             }
-        } else if (warp == W_PV && lane == 0) {
+        } else if (warp == W_PV && lane == 0 && leader) {
             // ======================= O += P [V | 1] for every tile ======================================
-            const uint32_t idO = umma_idesc(128, VROWS);
+            const uint32_t idO = umma_idesc(PAIR ? 256 : 128, L::N_PV);
             const uint64_t vd0 = umma_desc(smem_u32(Vsm));
             for (int j = 0; j < n_tiles; ++j) {
-                wait(B_P + slot(j), phase(j), 20);                         // P written and the V operand ready
+                wait_pair(B_P + slot(j), phase(j), 20);                    // P written and the V operand ready
                 tc_fence_after();
-                const uint32_t tP = tmem + T_S + slot(j) * BN;                // P overwrote the S tile
+                const uint32_t tP = tmem + T_S + L::scol(slot(j));            // P overwrote the first chunk of the S tile
                 const uint64_t vd = vd0 + (uint64_t)(slot(j) * (V_BYTES >> 4));
 #pragma unroll
-                for (int ks = 0; ks < BN / 16; ++ks)
-                    umma_f16_ts(tmem + T_O, tP + 8 * ks, vd + (uint64_t)(2 * ks), idO, (j > 0 || ks > 0) ? 1u : 0u);
-                umma_commit(&bars[B_PV + slot(j)]);
+                for (int ks = 0; ks < BN / 16; ++ks) {
+                    if (PAIR) umma2_f16_ts(tmem + T_O, tP + 8 * ks, vd + (uint64_t)(2 * ks), idO, (j > 0 || ks > 0) ? 1u : 0u);
+                    else      umma_f16_ts(tmem + T_O, tP + 8 * ks, vd + (uint64_t)(2 * ks), idO, (j > 0 || ks > 0) ? 1u : 0u);
+                }
+                if (PAIR) umma2_commit(&bars[B_PV + slot(j)]); else umma_commit(&bars[B_PV + slot(j)]);
             }
         } else if ((warp == W_LDK || warp == W_LDV) && lane == 0) {
             // ======================= loaders: raw K (or V) tiles into their ring with bulk copies =======
@@ -267,8 +413,10 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill_hd128(const Params P) {
         // ======================= V dequant warps: V^T operand, [dim][key] ================================
         regs_shrink<REGS_DEQ>();
         const int t = tid - W_VDQ * 32, wq = t >> 5;
-        constexpr int NWG = HD / 16;                            // groups of four dim-words
-        constexpr int UPT = (HD / 4) * (BN / 8) / 128;          // micro-tiles (4 dims x 8 keys) per thread
+        constexpr int NWG = VDIMS / 16;                         // groups of four dim-words this CTA converts
+        constexpr int UPT = (VDIMS / 4) * (BN / 8) / 128;       // micro-tiles (4 dims x 8 keys) per thread: 2, PAIR: 1
+        constexpr int WBASE = 0;
+        const int wfirst = PAIR ? crank * (VDIMS / 4) : WBASE;  // first dim word of this CTA's half of the head
         const int cc = lane & 7, wl = lane >> 3;                // key chunk (8 keys), fixed per thread
         int vkey[8];
 #pragma unroll
@@ -290,9 +438,10 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill_hd128(const Params P) {
 #pragma unroll
             for (int it = 0; it < UPT; ++it) {
                 const int u = UPT * wq + it;
-                const int w = 4 * (u % NWG) + wl;                       // dim word: dims 4w .. 4w+3
-                if ((it & 1) == 0) {                                    // two consecutive micro-tiles share a block
-                    const int vblk = (u % NWG) >> 1;
+                const int wloc = 4 * (u % NWG) + wl;                    // dim word inside this CTA's operand
+                const int w = wfirst + wloc;                            // dim word of the head: dims 4w .. 4w+3
+                if (UPT == 1 || (it & 1) == 0) {                        // two consecutive micro-tiles share a block
+                    const int vblk = w >> 3;
 #pragma unroll
                     for (int pr = 0; pr < 4; ++pr) {
                         const uint32_t sa = kok[2 * pr] ? reinterpret_cast<const uint16_t*>(Vraw + vkey[2 * pr] * REC)[vblk] : 0u;
@@ -316,30 +465,36 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill_hd128(const Params P) {
                 }
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const int d = 4 * w + i;
+                    const int d = 4 * wloc + i;                         // operand row
                     *reinterpret_cast<uint4*>(Vdst + sw128(d, cc)) = make_uint4(chunk[i][0], chunk[i][1], chunk[i][2], chunk[i][3]);
                 }
             }
             proxy_fence();
             __syncwarp();
-            if (lane == 0) { mbar_arrive(&bars[B_P + slot(j)]); mbar_arrive(&bars[B_VRAW_FREE + slot(j)]); }
+            if (lane == 0) { arrive_issuer(B_P + slot(j)); mbar_arrive(&bars[B_VRAW_FREE + slot(j)]); }
         }
     } else if (warp >= W_KDQ) {
         // ======================= K dequant warps: K operand, [key][dim] ==================================
         regs_shrink<REGS_DEQ>();
         const int t = tid - W_KDQ * 32;
-        const int krow = t & (BN - 1);                          // each thread converts one 64-dim half of one row
-        const int sub = t / BN;                                 // which 64-dim sub-tile
-        const int kkey = kappa(krow);
+        // a thread converts NBT 32-dim blocks of one operand row: a 64-dim half of one of 64 rows, or (PAIR) one
+        // block of one of this CTA's 32 rows
+        constexpr int KROWS = L::KROWS, NBT = PAIR ? 1 : 2;
+        const int krow = t & (KROWS - 1);
+        const int part = t / KROWS;                             // 0..1, PAIR: 0..3
+        const int sub = PAIR ? part >> 1 : part;                // which 64-dim sub-tile
+        const int blk0 = PAIR ? part & 1 : 0;                   // first block inside the sub-tile
+        const int kkey = kappa(crank * KROWS + krow);           // S column = operand row of the pair's tile
         for (int j = 0; j < n_tiles; ++j) {
             const uint8_t* src = smem + OFF_RAWK + slot(j) * RAW_BYTES + kkey * REC;
             wait(B_KRAW_FULL + slot(j), phase(j), 50);
             // the S MMA that last read this K buffer (tile j - NB) must be complete
             if (j >= NB) wait(B_S + slot(j), phase(j - NB), 50);
-            uint8_t* Kdst = Ksm + slot(j) * K_BYTES + sub * (BN * 128);
-            uint8_t* Ldst = Klo + slot(j) * K_BYTES + sub * (BN * 128);
+            uint8_t* Kdst = Ksm + L::koff(slot(j), sub);
+            uint8_t* Ldst = Klo + L::koff(slot(j), sub);
 #pragma unroll
-            for (int blk = 0; blk < 2; ++blk) {
+            for (int bb = 0; bb < NBT; ++bb) {
+                const int blk = blk0 + bb;
                 const __half sc = reinterpret_cast<const __half*>(src)[2 * sub + blk];
                 const __half2 s2 = __half2half2(sc);
                 const uint32_t su = *reinterpret_cast<const uint32_t*>(&s2);
@@ -356,12 +511,12 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill_hd128(const Params P) {
                     o.z = hmul2_u32(i2, su); r.z = hfma2_residual(i2, su, o.z);
                     o.w = hmul2_u32(i3, su); r.w = hfma2_residual(i3, su, o.w);
                     *reinterpret_cast<uint4*>(Kdst + sw128(krow, ch)) = o;
-                    if (KLO) *reinterpret_cast<uint4*>(Ldst + sw128(krow, ch)) = r;
+                    *reinterpret_cast<uint4*>(Ldst + sw128(krow, ch)) = r;
                 }
             }
             proxy_fence();
             __syncwarp();
-            if (lane == 0) { mbar_arrive(&bars[B_KF + slot(j)]); mbar_arrive(&bars[B_KRAW_FREE + slot(j)]); }
+            if (lane == 0) { arrive_issuer(B_KF + slot(j)); mbar_arrive(&bars[B_KRAW_FREE + slot(j)]); }
         }
     } else {
         // ======================= softmax warps: one thread per accumulator row, groups alternate tiles ====
@@ -380,7 +535,8 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill_hd128(const Params P) {
 
         for (int j = grp; j < n_tiles; j += 2) {
             const int t0 = (tile_first + j) * BN;
-            const uint32_t tS = tmem + lane_base + T_S + slot(j) * BN;
+            const uint32_t tS = tmem + lane_base + T_S + L::scol(slot(j));
+            const int ch2 = L::schunk((j ^ 1) < n_tiles);          // the tile's second 32 columns (see Lay::scol)
             // tiles every row of the CTA sees completely skip the mask code (bruce.cu:2927-2928)
             // (rows past the end of a ragged M tile hold zero queries: whatever they compute is finite and never stored)
             const bool masked = !(t0 >= full_lo && t0 + BN - 1 <= p_first);
@@ -388,7 +544,7 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill_hd128(const Params P) {
             tc_fence_after();
             uint32_t v[2][32];
             tmem_ld32_nowait(tS, v[0]);
-            tmem_ld32_nowait(tS + 32, v[1]);
+            tmem_ld32_nowait(tS + ch2, v[1]);
             tmem_ld_wait();
             if (masked) {
                 // Tiles that some row of the CTA sees only partly (the causal diagonal, the window edge, a
@@ -455,7 +611,7 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill_hd128(const Params P) {
 #pragma unroll 1
                     for (int c = 0; c < HD / 32; ++c) {
                         uint32_t o[32];
-                        const uint32_t ta = tmem + lane_base + T_O + c * 32;
+                        const uint32_t ta = tmem + lane_base + T_O + L::ocol(c);
                         tmem_ld32(ta, o);
 #pragma unroll
                         for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
@@ -492,7 +648,7 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill_hd128(const Params P) {
             tmem_st_wait();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&bars[B_P + slot(j)]);
+            if (lane == 0) arrive_issuer(B_P + slot(j));
         }
         // ---- epilogue: O / sum(P) -> global; each of the two threads of a row writes half of it ----------
         // A parity wait on phase k of a barrier is only meaningful once phase k-1 is known to be complete (before
@@ -519,7 +675,7 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill_hd128(const Params P) {
 #pragma unroll 1
         for (int c = 0; c < HD / 64; ++c) {
             uint32_t o[32];
-            tmem_ld32(tmem + lane_base + T_O + grp * (HD / 2) + c * 32, o);
+            tmem_ld32(tmem + lane_base + T_O + L::ocol(2 * grp + c), o);
             if (row_ok) {
                 if (rec) {
                     float2* dst = reinterpret_cast<float2*>(rec + grp * (HD / 2) + c * 32);     // records are 8-byte aligned
@@ -548,9 +704,11 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill_hd128(const Params P) {
         tc_fence_before();
     }
     __syncthreads();
+    if (PAIR) cluster_sync_all();          // neither CTA leaves (or frees tensor memory) while the other may still use it
     if (warp == W_MMA) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+        if (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+        else      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
     }
 }
 
