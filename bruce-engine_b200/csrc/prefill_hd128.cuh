@@ -89,8 +89,8 @@ struct Lay {
     static constexpr int OFF_RAWV = OFF_RAWK + NB * RAW_BYTES;
     static constexpr int OFF_BAR = OFF_RAWV + NB * RAW_BYTES;
     static constexpr int OFF_MISC = OFF_BAR + N_BARS * 8 + 8;   // [0] tmem base, [1] abort flag, [4..7] decision sequence
-    static constexpr int OFF_MREF = OFF_MISC + 32;           // [128] row references
-    static constexpr int TOTAL = OFF_MREF + 128 * 4 + 1024;  // + slack to align the base to 1024
+    static constexpr int OFF_MREF = OFF_MISC + 32;           // [tile parity][column half][128 rows] row maxima
+    static constexpr int TOTAL = OFF_MREF + 2 * 2 * 128 * 4 + 1024;  // + slack to align the base to 1024
     static_assert(TOTAL <= 226 * 1024, "shared memory budget");
     static_assert(K_SUB % 1024 == 0 && V_BYTES % 1024 == 0 && RAW_BYTES % 16 == 0, "operand alignment");
     // tensor-memory columns.  PAIR: the P.V product has N = 160 = [dims 0-63 | ones | dims 64-127 | ones], so the
@@ -217,17 +217,15 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill_hd128(const Params P) {
             mbar_init(&bars[B_KRAW_FULL + b], 1); mbar_init(&bars[B_VRAW_FULL + b], 1);
             mbar_init(&bars[B_KRAW_FREE + b], 4); mbar_init(&bars[B_VRAW_FREE + b], 4);
             mbar_init(&bars[B_S + b], 1); mbar_init(&bars[B_PV + b], 1);
-            // K operand ready: 4 dequant warps; P written and V operand ready: 4 softmax + 4 dequant warps --
+            // K operand ready: 4 dequant warps; P written and V operand ready: 8 softmax + 4 dequant warps --
             // PAIR: of both CTAs, counted on the issuing CTA's barriers
             mbar_init(&bars[B_KF + b], PAIR ? 8 : 4);
-            mbar_init(&bars[B_P + b], PAIR ? 16 : 8);
+            mbar_init(&bars[B_P + b], PAIR ? 24 : 12);
         }
         mbar_init(&bars[B_Q], 1);
         misc[1] = 0;
-        misc[4] = misc[5] = misc[6] = misc[7] = 0;
         mbar_fence_init();
     }
-    if (tid < 128) mref[tid] = NEG_BIG;
     if (warp == W_MMA) {
         if (PAIR) {
             // the same warp of both CTAs of the pair allocates the same columns in both tensor memories
@@ -522,7 +520,7 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill_hd128(const Params P) {
         // ======================= softmax warps: one thread per accumulator row, groups alternate tiles ====
         regs_grow<REGS_SOFT>();
         const int m = tid & 127;                               // row = TMEM lane
-        const int grp = tid >> 7;                              // 0: even tiles, 1: odd tiles
+        const int grp = tid >> 7;                              // which 32 of a tile's 64 columns this thread owns
         const int qtr = warp & 3;
         const uint32_t lane_base = (uint32_t)(qtr * 32) << 16;
         const int r = m / G, h = m - r * G;
@@ -532,75 +530,60 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill_hd128(const Params P) {
         const float c2 = P.scale_log2;
         const float thr = RESCALE_THRESHOLD / c2;              // threshold in raw-score units
         const uint64_t c2p = pack_f2(c2, c2);
+        // the two threads of a row keep the row reference in a register each: they see the same maxima and take
+        // the same decisions
+        float m_ref = NEG_BIG;
 
-        for (int j = grp; j < n_tiles; j += 2) {
+        for (int j = 0; j < n_tiles; ++j) {
             const int t0 = (tile_first + j) * BN;
-            const uint32_t tS = tmem + lane_base + T_S + L::scol(slot(j));
             const int ch2 = L::schunk((j ^ 1) < n_tiles);          // the tile's second 32 columns (see Lay::scol)
+            const uint32_t tS = tmem + lane_base + T_S + L::scol(slot(j));
             // tiles every row of the CTA sees completely skip the mask code (bruce.cu:2927-2928)
             // (rows past the end of a ragged M tile hold zero queries: whatever they compute is finite and never stored)
             const bool masked = !(t0 >= full_lo && t0 + BN - 1 <= p_first);
             wait(B_S + slot(j), phase(j), 50);
             tc_fence_after();
-            uint32_t v[2][32];
-            tmem_ld32_nowait(tS, v[0]);
-            tmem_ld32_nowait(tS + ch2, v[1]);
-            tmem_ld_wait();
+            uint32_t v[32];
+            tmem_ld32(tS + (grp ? ch2 : 0), v);
             if (masked) {
                 // Tiles that some row of the CTA sees only partly (the causal diagonal, the window edge, a
                 // ragged last chunk): hidden columns are replaced by "minus infinity" (bruce.cu:3021-3028),
                 // after which the common code below needs no mask.  The visibility bits are built by a rolled
                 // loop to keep this rarely executed path small.
-#pragma unroll
-                for (int c = 0; c < 2; ++c) {
-                    uint32_t bits = 0u;
+                uint32_t bits = 0u;
 #pragma unroll 1
-                    for (int i = 0; i < 32; ++i) {
-                        const int key = t0 + kappa(c * 32 + i);
-                        const bool ok = row_ok && key <= prow && key >= row_lo;
-                        bits |= (ok ? 1u : 0u) << i;
-                    }
-#pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        if (!((bits >> i) & 1u)) v[c][i] = __float_as_uint(NEG_BIG);
+                for (int i = 0; i < 32; ++i) {
+                    const int key = t0 + kappa(grp * 32 + i);
+                    const bool ok = row_ok && key <= prow && key >= row_lo;
+                    bits |= (ok ? 1u : 0u) << i;
                 }
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                    if (!((bits >> i) & 1u)) v[i] = __float_as_uint(NEG_BIG);
             }
             float mx;
             {
-                float m0 = __uint_as_float(v[0][0]), m1 = __uint_as_float(v[0][1]);
-                float m2 = __uint_as_float(v[0][2]), m3 = __uint_as_float(v[0][3]);
+                float m0 = __uint_as_float(v[0]), m1 = __uint_as_float(v[1]);
+                float m2 = __uint_as_float(v[2]), m3 = __uint_as_float(v[3]);
 #pragma unroll
                 for (int i = 4; i + 8 <= 32; i += 8) {
-                    m0 = fmax3(m0, __uint_as_float(v[0][i]), __uint_as_float(v[0][i + 1]));
-                    m1 = fmax3(m1, __uint_as_float(v[0][i + 2]), __uint_as_float(v[0][i + 3]));
-                    m2 = fmax3(m2, __uint_as_float(v[0][i + 4]), __uint_as_float(v[0][i + 5]));
-                    m3 = fmax3(m3, __uint_as_float(v[0][i + 6]), __uint_as_float(v[0][i + 7]));
+                    m0 = fmax3(m0, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+                    m1 = fmax3(m1, __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+                    m2 = fmax3(m2, __uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
+                    m3 = fmax3(m3, __uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
                 }
-                m0 = fmax3(m0, __uint_as_float(v[0][28]), __uint_as_float(v[0][29]));
-                m1 = fmax3(m1, __uint_as_float(v[0][30]), __uint_as_float(v[0][31]));
-#pragma unroll
-                for (int i = 0; i < 32; i += 8) {
-                    m0 = fmax3(m0, __uint_as_float(v[1][i]), __uint_as_float(v[1][i + 1]));
-                    m1 = fmax3(m1, __uint_as_float(v[1][i + 2]), __uint_as_float(v[1][i + 3]));
-                    m2 = fmax3(m2, __uint_as_float(v[1][i + 4]), __uint_as_float(v[1][i + 5]));
-                    m3 = fmax3(m3, __uint_as_float(v[1][i + 6]), __uint_as_float(v[1][i + 7]));
-                }
+                m0 = fmax3(m0, __uint_as_float(v[28]), __uint_as_float(v[29]));
+                m1 = fmax3(m1, __uint_as_float(v[30]), __uint_as_float(v[31]));
                 mx = fmax3(fmaxf(m0, m1), m2, m3);
             }
-            // The row reference is decided in tile order: wait until the other group has published its decision
-            // for tile j-1 (normally long done: that group started half a tile earlier).
-            if (j > 0 && !misc[1]) {
-                uint32_t spins = 0;
-                while (misc[4 + qtr] < (uint32_t)j) {
-                    if (++spins > (1u << 24)) {
-                        atomicOr(P.status, BATTN_DEV_WAIT_TIMEOUT);
-                        misc[1] = 1;
-                        break;
-                    }
-                }
-                __threadfence_block();
+            // the row maximum of the tile: exchange the two halves through shared memory (double-buffered by tile
+            // parity; the barrier of the next tile separates a buffer's reads from its next writes)
+            {
+                volatile float* x = mref + (j & 1) * 256;
+                x[grp * 128 + m] = mx;
+                named_bar_sync(4 + qtr, 64);
+                mx = fmaxf(mx, x[(grp ^ 1) * 128 + m]);
             }
-            float m_ref = mref[m];
             const float m_new = fmaxf(m_ref, mx);
             const bool need = m_new > m_ref + thr;
             if (__any_sync(0xffffffffu, need)) {
@@ -609,56 +592,46 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill_hd128(const Params P) {
                     tc_fence_after();
                     const float alpha = need ? fast_exp2((m_ref - m_new) * c2) : 1.f;
 #pragma unroll 1
-                    for (int c = 0; c < HD / 32; ++c) {
+                    for (int c = 0; c < HD / 64; ++c) {                 // each thread its half of the row
                         uint32_t o[32];
-                        const uint32_t ta = tmem + lane_base + T_O + L::ocol(c);
+                        const uint32_t ta = tmem + lane_base + T_O + L::ocol(2 * grp + c);
                         tmem_ld32(ta, o);
 #pragma unroll
                         for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
                         tmem_st32(ta, o);
                     }
-                    const uint32_t tl = tmem + lane_base + T_L;
-                    tmem_st1(tl, __float_as_uint(__uint_as_float(tmem_ld1(tl)) * alpha));
+                    if (grp == 0) {
+                        const uint32_t tl = tmem + lane_base + T_L;
+                        tmem_st1(tl, __float_as_uint(__uint_as_float(tmem_ld1(tl)) * alpha));
+                    }
                     tmem_st_wait();
                     tc_fence_before();
                 }
-                if (need) { m_ref = m_new; mref[m] = m_new; }
-            }
-            __syncwarp();
-            if (lane == 0) {
-                __threadfence_block();
-                misc[4 + qtr] = (uint32_t)(j + 1);
+                if (need) m_ref = m_new;
             }
             // p = 2^(s*c2 - m_ref*c2); a row that has seen no key yet keeps the offset at zero, so its hidden
             // columns ("minus infinity") still come out as exactly zero
             const float nb = m_ref > 0.5f * NEG_BIG ? -m_ref * c2 : 0.f;
             const uint64_t nbp = pack_f2(nb, nb);
-            // P (fp16 pairs) overwrites the first half of the S columns, which this thread has already read
-            uint32_t pk[32];
+            // P (fp16 pairs): the tile's 32 packed columns overwrite its first 32 S columns, this thread's half of
+            // them at offset 16 * grp.  The other thread of the row may still be reading those S columns: both have
+            // passed the barrier above only after their loads completed.
+            uint32_t pk[16];
 #pragma unroll
-            for (int c = 0; c < 2; ++c) {
-#pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    float e0, e1;
-                    ffma2(e0, e1, __uint_as_float(v[c][i]), __uint_as_float(v[c][i + 1]), c2p, nbp);
-                    pk[c * 16 + (i >> 1)] = pack_h2(fast_exp2(e0), fast_exp2(e1));
-                }
+            for (int i = 0; i < 32; i += 2) {
+                float e0, e1;
+                ffma2(e0, e1, __uint_as_float(v[i]), __uint_as_float(v[i + 1]), c2p, nbp);
+                pk[i >> 1] = pack_h2(fast_exp2(e0), fast_exp2(e1));
             }
-            tmem_st32(tS, pk);
+            tmem_st16(tS + 16 * grp, pk);
             tmem_st_wait();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) arrive_issuer(B_P + slot(j));
         }
         // ---- epilogue: O / sum(P) -> global; each of the two threads of a row writes half of it ----------
-        // A parity wait on phase k of a barrier is only meaningful once phase k-1 is known to be complete (before
-        // that it is satisfied at once).  The group that did not own the last tile therefore first waits for the
-        // P.V product of its OWN last tile -- whose predecessor in that ring slot completed before this group was
-        // handed the tile's scores -- and only then for the last tile's.
-        {
-            const int own_last = n_tiles - 1 - ((n_tiles - 1 - grp) & 1);
-            if (own_last >= 0 && own_last != n_tiles - 1) wait(B_PV + slot(own_last), phase(own_last), 50);
-        }
+        // (the last tile's predecessor in its ring slot completed before this thread was handed the tile's scores,
+        // so the parity wait below cannot be satisfied early)
         wait(B_PV + slot(n_tiles - 1), phase(n_tiles - 1), 50);
         tc_fence_after();
         const float l = __uint_as_float(tmem_ld1(tmem + lane_base + T_L));
@@ -668,7 +641,7 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill_hd128(const Params P) {
         float* rec = P.recs ? P.recs + ((((size_t)blockIdx.z * P.rows) + rbase + r) * P.Hq + kvh * G + h) * (size_t)(HD + 2)
                                   : nullptr;
         if (rec && row_ok && grp == 0) {
-            const float mr = mref[m];
+            const float mr = m_ref;
             rec[HD] = mr > 0.5f * NEG_BIG ? mr * c2 : NEG_BIG;
             rec[HD + 1] = l;
         }
