@@ -987,6 +987,22 @@ def run_gpu(args):
     d2h = h_out.numel()
 
     peak, peak_kind = measured_peak()
+    # whole call (decode kernel + merge) of every layer, back to back: a graph of 20 calls of that layer alone
+    call_us = {}
+    for L in layers:
+        for _ in range(2):
+            L.decode()
+        g20 = capture(lambda L=L: [L.decode() for _ in range(20)])
+        g20.replay()
+        torch.cuda.synchronize()
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        c0.record()
+        for _ in range(10):
+            g20.replay()
+        c1.record()
+        torch.cuda.synchronize()
+        call_us[(L.ctx, L.is_swa)] = c0.elapsed_time(c1) * 1e3 / 200
+        del g20
     sweep = []
     for c in ctxs:
         tf = statistics.mean(kernel_ms[(c, False)]) * 1e-3
@@ -994,6 +1010,8 @@ def run_gpu(args):
         sweep.append({"ctx": c, "full_us": tf * 1e6, "full_TBps": c * POS_BYTES / tf / 1e12,
                       "full_frac_of_peak": c * POS_BYTES / tf / 1e9 / peak,
                       "swa_us": ts * 1e6, "swa_TBps": visible(c, True) * POS_BYTES / ts / 1e12,
+                      "full_call_us_in_graph": call_us[(c, False)], "swa_call_us_in_graph": call_us[(c, True)],
+                      "full_call_frac_of_peak": c * POS_BYTES / (call_us[(c, False)] * 1e-6) / 1e9 / peak,
                       "attn_tok_per_s_layer_pair": 1.0 / (tf + ts)})
     top = ctxs[-1]
     t_top = statistics.mean(kernel_ms[(top, False)]) * 1e-3
@@ -1003,7 +1021,9 @@ def run_gpu(args):
     traffic = NCU_TRAFFIC_256K["bytes"] if NCU_TRAFFIC_256K["lib_version"] == lib_version else None
     roofline = {"bound": "hbm", "kernel": "k_flash_decode<128,1> @ ctx 262144, full layer", "achieved": achieved,
                 "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": achieved / peak,
-                "timed": "CUDA event pair around each launch, eager pass of the same K steps",
+                "timed": "CUDA event pair around each launch, eager pass of the same K steps (sweep[].full_us / swa_us "
+                         "are these kernel-alone times, event overhead included; *_call_us_in_graph is the whole call, "
+                         "decode kernel + merge, from a graph of 20 calls of that layer)",
                 "frac_of_nominal_8TBps": achieved / 8000.0, "launch_us": t_top * 1e6,
                 "algorithmic_bytes_per_launch": alg_bytes, "traffic": traffic,
                 "traffic_from": f"ncu capture of library revision {NCU_TRAFFIC_256K['lib_version']}; loaded revision {lib_version}"}

@@ -426,17 +426,25 @@ __global__ void __launch_bounds__(MERGE_B_THREADS) k_merge_balanced(const MergeP
         const XchgView& X = P.xchg;
         const int xitem = rowidx * P.Hq + hq;
         const int epoch = *X.epoch_ptr;
-        if (X.push && lane == 0) {
-            const size_t slot = (((size_t)(epoch & 1) * X.world + X.rank) * X.max_items + xitem) * RS;
+        // one warp pushes the whole record (one system-scope fence instead of one per warp)
+        __shared__ float4 s_push[HD / 4];
+        if (X.push) {
+            if (lane == 0) {
 #pragma unroll
-            for (int d = 0; d < XCHG_MAX_WORLD; ++d)
-                if (d < X.world) {
-                    float* dst = X.rec[d] + slot;                // plain stores into the peer's memory
+                for (int j = 0; j < DPW; ++j) s_push[warp + NWARP * j] = acc[j];
+            }
+            __syncthreads();
+            if (warp == 0) {
+                const size_t slot = (((size_t)(epoch & 1) * X.world + X.rank) * X.max_items + xitem) * RS;
 #pragma unroll
-                    for (int j = 0; j < DPW; ++j) *reinterpret_cast<float4*>(dst + 4 * (warp + NWARP * j)) = acc[j];
-                    if (warp == 0) *reinterpret_cast<float2*>(dst + HD) = make_float2(M, L);
-                }
-            __threadfence_system();
+                for (int d = 0; d < XCHG_MAX_WORLD; ++d)
+                    if (d < X.world) {
+                        float* dst = X.rec[d] + slot;            // plain stores into the peer's memory
+                        for (int dq = lane; dq < HD / 4; dq += 32) *reinterpret_cast<float4*>(dst + 4 * dq) = s_push[dq];
+                        if (lane == 0) *reinterpret_cast<float2*>(dst + HD) = make_float2(M, L);
+                    }
+                __threadfence_system();
+            }
         }
         __syncthreads();
         if (X.push && tid < X.world)

@@ -42,6 +42,10 @@ static inline void battn_shim_init(int n_head, int n_kv, int hd, int swa, int sl
     battn_geom g = {n_head, n_kv, hd, swa, slot_ctx, n_slots, BATTN_F32, BATTN_F32, 0.f};
     BATTN_CK(battn_init(&g, 0, &g_battn));
     g_battn_group = n_head / n_kv;
+    /* The engine's step order is the one early KV streaming asks for: positions reach the device by copies
+     * (bruce.cu:8043, 8259) or by k_advance at the END of a step (:8051), and the kernel in front of every
+     * attention launch is the prologue that writes that step's rows (:7667-7732). */
+    BATTN_CK(battn_set_early_kv_stream(g_battn, 1));
 }
 /* size of M.part (bruce.cu:5564): rows = MBUF for the prompt path */
 static inline size_t battn_shim_part_bytes(int max_slots, int max_rows) {
