@@ -155,3 +155,29 @@ def test_scratch_sized_for_512_rows_serves_every_shorter_chunk(name):
         # oracle: max-abs and the 2-norm ratios; the max-norm gate belongs to the oracle comparisons above)
         assert_close(to_np(out), to_np(ref), f"{name} {rows}-row chunk on the 512-row scratch", maxnorm=False)
     assert eng.device_status() == 0
+
+
+@pytest.mark.parametrize("name", ["B32", "B"])
+@pytest.mark.parametrize("is_swa", [False, True])
+def test_pair_kernel_tile_count_edges(name, is_swa):
+    """Chunks of two to five M tiles (CTA pairs; an odd count leaves the last pair's second CTA without rows) at
+    depths where a pair walks one, two, three, ... key tiles -- a last tile without a partner in the two-tile S
+    product -- with and without key splits, full-causal and with a window of four pair spans."""
+    from bruce_engine_b200.engine import AttnEngine
+    window = 256                                   # a window layer takes at most `window` rows per chunk
+    for rows, depth, seed in ((64, 0, 1), (64, 64, 2), (96, 100, 3), (128, 130, 4), (160, 190, 5), (64, 1000, 6),
+                              (100, 2000, 7), (33, 3000, 8)):
+        n = depth + rows
+        g = _geom(name, slot_ctx=n + (n & 1), window=window)
+        eng, og = AttnEngine(g), oracle_geom(g)
+        q, k, v = draw_qkv(g, n, rows, seed, q_f16=(g.q_dtype == 1))
+        kvk, kvv = eng.alloc_kv_layer(is_swa, fill=0xFF)
+        gpu_fill(eng, k, v, kvk, kvv, is_swa)
+        okvk, okvv = O.new_cache(og, is_swa, fill=0xFF), O.new_cache(og, is_swa, fill=0xFF)
+        oracle_fill(og, k, v, is_swa, kvk=okvk, kvv=okvv)
+        out = new_out(eng, 1, rows, g.n_head, g.head_dim)
+        eng.launch_attn_m(out, dev_q(eng, q), kvk, kvv, dev_i32([depth], eng.device), eng.alloc_part(1, rows), rows, is_swa)
+        torch.cuda.synchronize()
+        want = O.attend(og, q, okvk, okvv, [depth], rows=rows, is_swa=is_swa)
+        assert_close(to_np(out), want, f"pair edges {name} swa={is_swa} rows {rows} depth {depth}")
+        assert eng.device_status() == 0
