@@ -15,8 +15,8 @@
 // through tcgen05.commit with a two-CTA multicast.  In that mode the S products are issued for two key tiles at a
 // time (N = 128): a 64-column product runs at about half the tensor rate.
 // Twenty warps, each warpgroup resized with setmaxnreg for its role:
-//   warps 0-3   softmax group A (even key tiles), one thread per accumulator row
-//   warps 4-7   softmax group B (odd key tiles), one thread per accumulator row
+//   warps 0-7   softmax: two threads per accumulator row, warps 0-3 own the first 32 columns of every key tile,
+//               warps 4-7 the other 32
 //   warps 8-11  K dequant: raw q8_0 records -> fp16 K operand [key][dim], scale folded in
 //   warps 12-15 V dequant: raw q8_0 records -> fp16 V^T operand [dim][key], scale folded in
 //   warp 16     issues the S MMAs, warp 19 the P.V MMAs;  warps 17/18 stream raw K / V tiles with bulk copies
@@ -26,20 +26,20 @@
 //                     and an fp16 scale has 19 significant bits, fp16 keeps 11, the rest fits the second part),
 //                     so S carries no rounding of K -- a single folded operand alone moves single (row, head)
 //                     outputs by up to 7e-4 relative, most of the 1e-3 budget
-//   S_j = Q K_hi^T + Q K_lo^T   Q lives in tensor memory (the A operand), S_j in one of three 64-column buffers
-//   softmax           the owning group reads S_j once into registers, takes the row maximum, and writes
-//                     P_j = 2^(S_j*c - ref) as fp16 pairs over the first half of the same buffer
+//   S_j = Q K_hi^T + Q K_lo^T   Q lives in tensor memory (the A operand), S_j in a 64-column buffer of the ring
+//   softmax           each of a row's two threads reads its 32 scores once into registers; the row maximum is
+//                     exchanged through shared memory (one 64-thread named barrier per tile); both write
+//                     P_j = 2^(S_j*c - ref) as fp16 pairs over the first 32 columns of the same buffer
 //   O += P_j [V_j | 1]  P_j is the tensor-memory A operand; sixteen rows of ones appended to the V^T
 //                     operand make the same MMA accumulate sum(P) in fp32 next to O, from exactly the
 //                     fp16-rounded P it multiplies with V
-// The S issuer runs up to three tiles ahead of O, so when a softmax group finishes tile j, S_{j+2} is ready;
-// the two groups run half a tile apart, which lets one group's exponentials (the special-function pipe)
-// overlap the other group's loads, maxima and stores.
-// The row reference `ref` (a lazily updated running maximum, bruce.cu:3034-3060 in spirit) is shared by
-// the two threads that own a row in alternate tiles: decisions are taken strictly in tile order (a small
-// sequence word per 32-row quarter), and O is rescaled in tensor memory only when a row maximum grows by
-// more than 2^8 over the reference; the final normalisation uses the same reference, so the result does
-// not depend on how rarely it moves.
+// The S issuer runs ahead of O as far as the ring of S/P buffers allows; a buffer is free again when the P.V
+// product that read its P has completed, and that turn-around (S product -> softmax -> P.V product) is what
+// bounds the kernel.
+// The row reference `ref` (a lazily updated running maximum, bruce.cu:3034-3060 in spirit) is kept in a register
+// by both threads of a row -- they see the same maxima and take the same decisions -- and O is rescaled in tensor
+// memory only when a row maximum grows by more than 2^8 over the reference; the final normalisation uses the same
+// reference, so the result does not depend on how rarely it moves.
 // Row n of the K operand / column n of S holds key kappa(n), a fixed permutation inside each 64-key span
 // chosen so that every shared-memory access of the dequant warps is bank-conflict free.
 // Every wait is bounded; a wait that runs out sets the device status word, the remaining waits are
@@ -88,7 +88,7 @@ struct Lay {
     static constexpr int OFF_RAWK = OFF_V + NB * V_BYTES;
     static constexpr int OFF_RAWV = OFF_RAWK + NB * RAW_BYTES;
     static constexpr int OFF_BAR = OFF_RAWV + NB * RAW_BYTES;
-    static constexpr int OFF_MISC = OFF_BAR + N_BARS * 8 + 8;   // [0] tmem base, [1] abort flag, [4..7] decision sequence
+    static constexpr int OFF_MISC = OFF_BAR + N_BARS * 8 + 8;   // [0] tmem base, [1] abort flag
     static constexpr int OFF_MREF = OFF_MISC + 32;           // [tile parity][column half][128 rows] row maxima
     static constexpr int TOTAL = OFF_MREF + 2 * 2 * 128 * 4 + 1024;  // + slack to align the base to 1024
     static_assert(TOTAL <= 226 * 1024, "shared memory budget");
@@ -413,8 +413,7 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill_hd128(const Params P) {
         const int t = tid - W_VDQ * 32, wq = t >> 5;
         constexpr int NWG = VDIMS / 16;                         // groups of four dim-words this CTA converts
         constexpr int UPT = (VDIMS / 4) * (BN / 8) / 128;       // micro-tiles (4 dims x 8 keys) per thread: 2, PAIR: 1
-        constexpr int WBASE = 0;
-        const int wfirst = PAIR ? crank * (VDIMS / 4) : WBASE;  // first dim word of this CTA's half of the head
+        const int wfirst = PAIR ? crank * (VDIMS / 4) : 0;      // first dim word of this CTA's half of the head
         const int cc = lane & 7, wl = lane >> 3;                // key chunk (8 keys), fixed per thread
         int vkey[8];
 #pragma unroll
