@@ -41,10 +41,6 @@ namespace vt {
 
 using namespace pf;
 
-#ifndef BATTN_VT_KUNROLL
-#define BATTN_VT_KUNROLL 4
-#endif
-constexpr int KUNROLL = BATTN_VT_KUNROLL;      // unrolling of the K dequant loop: more would not fit the instruction cache
 
 #ifdef BATTN_VT_TRACE
 // debugging aid (not compiled into the library): per-role time stamps of CTA 0
@@ -68,8 +64,6 @@ static_assert(2 * REGS_SOFT + 3 * REGS_DEQ + REGS_CTL <= 6 * REGS_LAUNCH, "regis
 static_assert(NTHREADS * REGS_LAUNCH <= 65536, "register file");
 
 constexpr int NB = 2;                                   // depth of the operand rings and of the S^T buffers
-constexpr int K_SUB = BK * 128;                         // [128 keys][64 dims] fp16, 128-byte rows, swizzled
-constexpr int K_BYTES = 2 * K_SUB;
 constexpr int V_SUB = HD * 128;                         // [128 dims][64 keys]
 constexpr int V_BYTES = 2 * V_SUB;
 constexpr int P_SUB = NP * 128;                         // [32 pairs][64 keys]
@@ -77,10 +71,9 @@ constexpr int P_BYTES = 2 * P_SUB;
 constexpr int Q_SUB = NP * 128;                         // [32 pairs][64 dims]
 constexpr int Q_BYTES = 2 * Q_SUB;
 constexpr int RAW_BYTES = BK * REC;
-constexpr int OFF_K = 0;
-constexpr int OFF_V = OFF_K + NB * K_BYTES;
-constexpr int OFF_P = OFF_V + NB * V_BYTES;             // ONE P^T buffer: the product of the tile before has long completed
-constexpr int OFF_Q = OFF_P + P_BYTES;
+constexpr int OFF_V = 0;
+constexpr int OFF_P = OFF_V + NB * V_BYTES;             // two P^T buffers, by tile parity: the softmax of tile j+1 does not wait
+constexpr int OFF_Q = OFF_P + 2 * P_BYTES;             // for the P.V product of tile j
 constexpr int OFF_RAWK = OFF_Q + Q_BYTES;
 constexpr int OFF_RAWV = OFF_RAWK + NB * RAW_BYTES;
 constexpr int OFF_KSC = OFF_RAWV + NB * RAW_BYTES;      // [NB][128 keys][4] block scales * softmax scale * log2 e
@@ -89,12 +82,15 @@ constexpr int XCH_GROUP = 2 * 4 * NPH + 4 * NPH + 4 * NPH + 8;
 constexpr int OFF_XCH = OFF_KSC + NB * BK * 16;
 constexpr int OFF_BAR = OFF_XCH + 2 * XCH_GROUP * 4;
 enum { B_KRAW_FULL = 0, B_KRAW_FREE = 2, B_VRAW_FULL = 4, B_VRAW_FREE = 6, B_KF = 8, B_VF = 10, B_S = 12, B_SR = 14,
-       B_PV = 16, B_PF = 18, B_Q = 19, N_BARS = 20 };
+       B_PV = 16, B_PF = 18, B_Q = 20, N_BARS = 21 };
 constexpr int OFF_MISC = OFF_BAR + N_BARS * 8;          // [0] tmem base, [1] abort flag
 constexpr int OFF_CUM = OFF_MISC + 16;                  // cum[n_seq + 1]
-constexpr int T_O = 0, T_S = 32;                        // tensor-memory columns: O^T (32), then NB x 4 x 32 of S^T
-static_assert(T_S + NB * 4 * NP <= 512, "tensor memory budget");
-static_assert(K_SUB % 1024 == 0 && V_SUB % 1024 == 0 && P_SUB % 1024 == 0 && RAW_BYTES % 16 == 0 && OFF_Q % 1024 == 0 &&
+// tensor-memory columns: O^T (32), NB x 4 x 32 of S^T, then the K operand itself: NB tiles of [128 keys = lanes][128
+// dims as 64 columns of fp16 pairs].  The S^T product takes its A operand from there: an MMA whose 4 KB A operand comes
+// from shared memory occupied the issue path for 110-150 cycles per instruction (measured), eight of them per tile.
+constexpr int T_O = 0, T_S = 32, T_K = T_S + NB * 4 * NP, K_COLS = HD / 2;
+static_assert(T_K + NB * K_COLS <= 512, "tensor memory budget");
+static_assert(V_SUB % 1024 == 0 && P_SUB % 1024 == 0 && RAW_BYTES % 16 == 0 && OFF_Q % 1024 == 0 &&
               OFF_P % 1024 == 0, "operand alignment");
 
 __host__ __device__ constexpr size_t smem_bytes(int n_seq) { return (size_t)OFF_CUM + (size_t)(n_seq + 2) * 4 + 1024; }
@@ -156,7 +152,6 @@ __device__ __forceinline__ float pick16(const float (&v)[16], int idx) {
 __global__ void __maxnreg__(REGS_LAUNCH) k_verify_tc(const fd::Params P) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);      // 1024-byte aligned
-    uint8_t* Ksm = smem + OFF_K;
     uint8_t* Vsm = smem + OFF_V;
     uint8_t* Psm = smem + OFF_P;
     uint8_t* Qsm = smem + OFF_Q;
@@ -178,7 +173,7 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_verify_tc(const fd::Params P) {
             mbar_init(&bars[B_S + b], 1); mbar_init(&bars[B_PV + b], 1);
             mbar_init(&bars[B_SR + b], 8);
         }
-        mbar_init(&bars[B_PF], 8);
+        mbar_init(&bars[B_PF], 8); mbar_init(&bars[B_PF + 1], 8);
         mbar_init(&bars[B_Q], 8);
         misc[1] = 0;
         mbar_fence_init();
@@ -243,7 +238,7 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_verify_tc(const fd::Params P) {
         if (warp == W_MMA && lane == 0) {
             // ======================= S^T = K Q^T, one accumulator per 32-dim block =========================
             const uint32_t idS = umma_idesc(128, NP);
-            const uint64_t kd0 = umma_desc(smem_u32(Ksm)), qd0 = umma_desc(smem_u32(Qsm));
+            const uint64_t qd0 = umma_desc(smem_u32(Qsm));
             int cnt = 0, piece = 0;
             for (int g = g0; g < g1; ++piece) {
                 const fd::Piece pc = fd::locate(g, g1, cum, P.n_seq, P.Hkv);
@@ -253,12 +248,11 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_verify_tc(const fd::Params P) {
                     if (cnt >= NB) wait(B_SR + slot(cnt), phase(cnt - NB), 20);    // softmax has read the old S^T
                     tc_fence_after();
                     VT_TRACE(0, cnt, 0);
-                    const uint64_t kd = kd0 + (uint64_t)(slot(cnt) * (K_BYTES >> 4));
+                    const uint32_t ka = tmem + T_K + slot(cnt) * K_COLS;           // K tile: lane = key, 8 columns per 16 dims
 #pragma unroll
                     for (int ks = 0; ks < HD / 16; ++ks) {
-                        const uint64_t off = (uint64_t)((ks >> 2) * (K_SUB >> 4) + 2 * (ks & 3));
                         const uint64_t qoff = (uint64_t)((ks >> 2) * (Q_SUB >> 4) + 2 * (ks & 3));
-                        umma_f16(tmem + T_S + slot(cnt) * 4 * NP + (ks >> 1) * NP, kd + off, qd0 + qoff, idS, ks & 1);
+                        umma_f16_ts(tmem + T_S + slot(cnt) * 4 * NP + (ks >> 1) * NP, ka + 8 * ks, qd0 + qoff, idS, ks & 1);
                     }
                     umma_commit(&bars[B_S + slot(cnt)]);
                     VT_TRACE(0, cnt, 1);
@@ -273,11 +267,11 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_verify_tc(const fd::Params P) {
             for (int g = g0; g < g1;) {
                 const fd::Piece pc = fd::locate(g, g1, cum, P.n_seq, P.Hkv);
                 for (int t = 0; t < pc.n; ++t, ++cnt) {
-                    wait(B_PF, cnt & 1, 20);
+                    wait(B_PF + (cnt & 1), (cnt >> 1) & 1, 20);
                     wait(B_VF + slot(cnt), phase(cnt), 20);
                     tc_fence_after();
                     const uint64_t vd = vd0 + (uint64_t)(slot(cnt) * (V_BYTES >> 4));
-                    const uint64_t pd = pd0;
+                    const uint64_t pd = pd0 + (uint64_t)((cnt & 1) * (P_BYTES >> 4));
                     VT_TRACE(1, cnt, 0);
 #pragma unroll
                     for (int ks = 0; ks < BK / 16; ++ks)
@@ -405,7 +399,7 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_verify_tc(const fd::Params P) {
                 // the S^T product that read this K buffer (tile cnt - NB) is complete once the softmax warps have
                 // signalled that they read its result
                 if (cnt >= NB) wait(B_SR + slot(cnt), phase(cnt - NB), 50);
-                uint8_t* Kdst = Ksm + slot(cnt) * K_BYTES;
+                const uint32_t kt = tmem + ((uint32_t)((warp & 3) * 32) << 16) + T_K + slot(cnt) * K_COLS;
                 if (krow == 0) VT_TRACE(5, cnt, 1);
                 {
                     const uint2 sc = *reinterpret_cast<const uint2*>(src);
@@ -414,14 +408,21 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_verify_tc(const fd::Params P) {
                     *reinterpret_cast<float4*>(ksc + (slot(cnt) * BK + krow) * 4) =
                         make_float4(s01.x * P.scale_log2, s01.y * P.scale_log2, s23.x * P.scale_log2, s23.y * P.scale_log2);
                 }
-#pragma unroll KUNROLL
-                for (int ch = 0; ch < HD / 8; ++ch) {           // 16-byte chunks of the fp16 row
-                    const uint2 w = *reinterpret_cast<const uint2*>(src + 2 * NBLK + ch * 8);
-                    const uint32_t x = w.x ^ 0x80808080u, y = w.y ^ 0x80808080u;
-                    *reinterpret_cast<uint4*>(Kdst + (ch >> 3) * K_SUB + sw128(krow, ch & 7)) =
-                        make_uint4(sub1152(widen_lo(x)), sub1152(widen_hi(x)), sub1152(widen_lo(y)), sub1152(widen_hi(y)));
+                // the key's 128 exact integers as 64 columns of fp16 pairs in this thread's tensor-memory lane, 16 at a time
+#pragma unroll 1
+                for (int g4 = 0; g4 < HD / 32; ++g4) {
+                    uint32_t col[16];
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const uint2 w = *reinterpret_cast<const uint2*>(src + 2 * NBLK + (4 * g4 + c) * 8);
+                        const uint32_t x = w.x ^ 0x80808080u, y = w.y ^ 0x80808080u;
+                        col[4 * c] = sub1152(widen_lo(x)); col[4 * c + 1] = sub1152(widen_hi(x));
+                        col[4 * c + 2] = sub1152(widen_lo(y)); col[4 * c + 3] = sub1152(widen_hi(y));
+                    }
+                    tmem_st16(kt + 16 * g4, col);
                 }
-                proxy_fence();
+                tmem_st_wait();
+                tc_fence_before();
                 __syncwarp();
                 if (lane == 0) { mbar_arrive(&bars[B_KF + slot(cnt)]); mbar_arrive(&bars[B_KRAW_FREE + slot(cnt)]); }
                 if (krow == 0) VT_TRACE(5, cnt, 2);
@@ -584,8 +585,9 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_verify_tc(const fd::Params P) {
                     __syncwarp();
                 }
                 // ---- P^T = 2^(s - ref), fp16, into the B operand [pair][key]; the sums take the rounded weights ----
-                // the product that read the P buffer (the tile before) must be complete
-                if (cnt >= 1) wait(B_PV + slot(cnt - 1), phase(cnt - 1), 30);
+                // the product that read this P buffer (two tiles ago) must be complete
+                if (cnt >= 2) wait(B_PV + slot(cnt - 2), phase(cnt - 2), 30);
+                const uint32_t poff = (uint32_t)((cnt & 1) * P_BYTES);
                 if (tid == 0) VT_TRACE(6, cnt, 2);
 #pragma unroll
                 for (int i = 0; i < NPH; i += 2) {
@@ -596,13 +598,13 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_verify_tc(const fd::Params P) {
                     lsum[i + 1] = fmaf(__uint_as_float((ph >> 3) & 0x0FFFE000u), 5.192296858534828e33f, lsum[i + 1]);
                     asm volatile("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %2;\n\t"
                                  "st.shared.b16 [%0], lo;\n\tst.shared.b16 [%1], hi;\n\t}"
-                                 ::"r"(pcol[i & 7] + (uint32_t)((i >> 3) * 1024 + (i & 7) * 128)),
-                                   "r"(pcol[(i + 1) & 7] + (uint32_t)(((i + 1) >> 3) * 1024 + ((i + 1) & 7) * 128)), "r"(ph)
+                                 ::"r"(pcol[i & 7] + poff + (uint32_t)((i >> 3) * 1024 + (i & 7) * 128)),
+                                   "r"(pcol[(i + 1) & 7] + poff + (uint32_t)(((i + 1) >> 3) * 1024 + ((i + 1) & 7) * 128)), "r"(ph)
                                  : "memory");
                 }
                 proxy_fence();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&bars[B_PF]);
+                if (lane == 0) mbar_arrive(&bars[B_PF + (cnt & 1)]);
                 if (tid == 0) VT_TRACE(6, cnt, 3);
             }
 
