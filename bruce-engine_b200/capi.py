@@ -62,6 +62,7 @@ SIGNATURES = {
     "battn_pages_pool_bytes": (_I, [_P, _I, _I, _SZP]),
     "battn_pages_copy": (_I, [_P, _PG, _I, _I, _P]),
     "battn_kv_append_paged": (_I, [_P, _PG] + [_P] * 5 + [_I, _I, _P]),
+    "battn_qkv_prep_paged": (_I, [_P] * 8 + [_I, _PG] + [_P] * 3 + [_I, _I, _P]),
     "battn_decode_paged": (_I, [_P, _P, _P, _PG] + [_P] * 4 + [_I, _P]),
     "battn_verify_paged": (_I, [_P, _P, _P, _PG] + [_P] * 4 + [_I, _I, _P]),
     "battn_prefill_paged": (_I, [_P, _P, _P, _PG, _I, _P, _P, _I, _P]),

@@ -554,9 +554,10 @@ int battn_kv_copy_prefix(battn_handle* h, uint8_t* kvk, uint8_t* kvv, int src_sl
     return e == cudaSuccess ? BATTN_OK : cuda_fail(h, e);
 }
 
-int battn_qkv_prep(battn_handle* h, void* q_out, const float* q, const float* k, const float* v, const float* sqk,
-                   const float* cs, const float* sn, int theta_sel, uint8_t* kvk, uint8_t* kvv, const int* pos,
-                   const int* kslot, const int* act, int n_seq, int rows_per_seq, int is_swa, void* stream) {
+static int qkv_prep_impl(battn_handle* h, void* q_out, const float* q, const float* k, const float* v, const float* sqk,
+                         const float* cs, const float* sn, int theta_sel, uint8_t* kvk, uint8_t* kvv, const int* pos,
+                         const int* kslot, const int* act, int n_seq, int rows_per_seq, int is_swa, void* stream,
+                         const PagedView* pv) {
     const int rc = check_seq_args(h, k, v, kvk, kvv, pos, kslot, n_seq, rows_per_seq, MAX_PREFILL);
     if (rc) return rc;
     if (!q_out || !q || !sqk || !cs || !sn || (theta_sel != 1 && theta_sel != 2)) return BATTN_ERR_ARG;
@@ -569,6 +570,7 @@ int battn_qkv_prep(battn_handle* h, void* q_out, const float* q, const float* k,
     P.table_off = theta_sel == 2 ? g.HD / 2 : 0; P.q_out_f16 = g.q_f16;
     P.pstride = is_swa ? g.ring : g.slot_ctx; P.ring_mask = is_swa ? g.ring - 1 : -1;
     P.n_slots = g.n_slots; P.status = h->d_status;
+    if (pv) { P.pg = pv->pg; P.pstride = pv->capacity; P.ring_mask = -1; P.n_slots = pv->n_tables; }
     h->kvw_kind = 1; h->kvw_pos = pos; h->kvw_nseq = n_seq; h->kvw_rows = rows_per_seq;
     cudaStream_t st = (cudaStream_t)stream;
     cudaError_t e;
@@ -578,6 +580,13 @@ int battn_qkv_prep(battn_handle* h, void* q_out, const float* q, const float* k,
     h->launches += 1;
     if (e == cudaSuccess) e = cudaGetLastError();
     return e == cudaSuccess ? BATTN_OK : cuda_fail(h, e);
+}
+
+int battn_qkv_prep(battn_handle* h, void* q_out, const float* q, const float* k, const float* v, const float* sqk,
+                   const float* cs, const float* sn, int theta_sel, uint8_t* kvk, uint8_t* kvv, const int* pos,
+                   const int* kslot, const int* act, int n_seq, int rows_per_seq, int is_swa, void* stream) {
+    return qkv_prep_impl(h, q_out, q, k, v, sqk, cs, sn, theta_sel, kvk, kvv, pos, kslot, act, n_seq, rows_per_seq, is_swa,
+                         stream, nullptr);
 }
 
 int battn_rope_tables(battn_handle* h, float* cs, float* sn, const int* pos, int n_seq, int rows_per_seq, void* stream) {
@@ -717,6 +726,16 @@ int battn_kv_append_paged(battn_handle* h, const battn_pages* pages, const float
     const int rc = paged_view(pages, pv);
     if (rc) return rc;
     return kv_append_impl(h, k, v, pages->pool_k, pages->pool_v, pos, ktab, act, n_seq, rows_per_seq, 0, stream, &pv);
+}
+
+int battn_qkv_prep_paged(battn_handle* h, void* q_out, const float* q, const float* k, const float* v, const float* sqk,
+                         const float* cs, const float* sn, int theta_sel, const battn_pages* pages, const int* pos,
+                         const int* ktab, const int* act, int n_seq, int rows_per_seq, void* stream) {
+    PagedView pv;
+    const int rc = paged_view(pages, pv);
+    if (rc) return rc;
+    return qkv_prep_impl(h, q_out, q, k, v, sqk, cs, sn, theta_sel, pages->pool_k, pages->pool_v, pos, ktab, act, n_seq,
+                         rows_per_seq, 0, stream, &pv);
 }
 
 int battn_decode_paged(battn_handle* h, void* out, const void* q, const battn_pages* pages, const int* pos,

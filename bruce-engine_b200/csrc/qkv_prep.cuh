@@ -33,6 +33,7 @@ struct PrepParams {
     int q_out_f16;
     int pstride, ring_mask, n_slots;
     int* status;
+    Paging pg;            // table != nullptr: paged cache (pstride = positions a table row can hold)
 };
 
 template <int HD>
@@ -137,7 +138,7 @@ __global__ void __launch_bounds__(256) k_qkv_prep(const PrepParams P) {
             k0[j] = __fmul_rn(__fmaf_rn(e[j], c[j], -__fmul_rn(f[j], s[j])), norm);
             k1[j] = __fmul_rn(__fmaf_rn(e[j], s[j], __fmul_rn(f[j], c[j])), norm);
         }
-        const size_t roff = (((size_t)slot * P.Hkv + h) * P.pstride + pp) * (size_t)REC;
+        const size_t roff = kv_rec_index(P.pg, slot, h, P.Hkv, P.pstride, pp, P.status) * (size_t)REC;
         // one 32-value block = LPB neighbouring lanes; this lane's first-half values sit in block lane / LPB,
         // its second-half values NBLK/2 blocks later
         auto quant = [&](uint8_t* rec, int blk, const float (&x)[VEC]) {

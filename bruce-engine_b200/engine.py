@@ -205,6 +205,13 @@ class AttnEngine:
             self.h, C.byref(pages), _ptr(k), _ptr(v), _ptr(pos), _ptr(ktab), _ptr(act), pos.numel(), rows,
             self._stream()))
 
+    def qkv_prep_paged(self, q_out, q, k, v, sqk, cs, sn, pages, pos, ktab=None, act=None, rows: int = 1,
+                       theta_sel: int = 1):
+        """The fused prologue (qkv_prep) storing its K/V rows into a paged cache."""
+        self._check("battn_qkv_prep_paged", self.lib.battn_qkv_prep_paged(
+            self.h, _ptr(q_out), _ptr(q), _ptr(k), _ptr(v), _ptr(sqk), _ptr(cs), _ptr(sn), int(theta_sel),
+            C.byref(pages), _ptr(pos), _ptr(ktab), _ptr(act), pos.numel(), rows, self._stream()))
+
     def attn_paged(self, out, q, pages, pos, part, rows: int = 1, ktab=None, act=None, table_row: int = 0):
         """Attention over a paged cache: one row per sequence (decode), 2..8 rows (verify) or a prompt chunk of the
         sequence with table row `table_row`; the dispatch of launch_attn_m / launch_attn_ms."""

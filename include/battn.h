@@ -297,6 +297,10 @@ int battn_pages_copy(battn_handle* h, const battn_pages* pages, int from_page, i
  * `table_row`) / battn_attend_exact, is_swa = 0 */
 int battn_kv_append_paged(battn_handle* h, const battn_pages* pages, const float* k, const float* v, const int* pos,
                           const int* ktab, const int* act, int n_seq, int rows_per_seq, void* stream);
+/* as battn_qkv_prep (the whole prologue fused with the append), storing into the pages */
+int battn_qkv_prep_paged(battn_handle* h, void* q_out, const float* q, const float* k, const float* v, const float* sqk,
+                         const float* cs, const float* sn, int theta_sel, const battn_pages* pages, const int* pos,
+                         const int* ktab, const int* act, int n_seq, int rows_per_seq, void* stream);
 int battn_decode_paged(battn_handle* h, void* out, const void* q, const battn_pages* pages, const int* pos,
                        const int* ktab, const int* act, void* ws, int n_seq, void* stream);
 int battn_verify_paged(battn_handle* h, void* out, const void* q, const battn_pages* pages, const int* pos,

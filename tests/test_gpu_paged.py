@@ -241,3 +241,42 @@ def test_paged_bad_table_entry_sets_status():
         d = capi.CPages(s.pool_k.data_ptr(), s.pool_v.data_ptr(), s.table.data_ptr(), s.n_pages, 1, s.max_pages, page_len)
         with pytest.raises(capi.BattnError):
             eng.attn_paged(out, dev_q(eng, s.q[:, :1]), d, dev_i32([599], eng.device), s.part, rows=1)
+
+
+@pytest.mark.parametrize("name", ["B32", "R"])
+def test_paged_fused_prologue_writes_the_same_bytes(name):
+    """battn_qkv_prep_paged against battn_qkv_prep on the same inputs: the same q, and every page holds the bytes of
+    the contiguous partition (the contiguous form is pinned to the oracle and the reference's kernel elsewhere)."""
+    page_len, n_seq, rows = 128, 3, 5
+    g = _geom(name, slot_ctx=1024, n_slots=n_seq)
+    eng = _engine(g)
+    rng = np.random.default_rng(11)
+    HD = g.head_dim
+    q = rng.standard_normal((n_seq, rows, g.n_head, HD), dtype=np.float32)
+    k = rng.standard_normal((n_seq, rows, g.n_kv, HD), dtype=np.float32) * 3.0
+    v = rng.standard_normal((n_seq, rows, g.n_kv, HD), dtype=np.float32)
+    sqk = (1.0 + 0.2 * rng.standard_normal((g.n_head, HD))).astype(np.float32)
+    pos = np.array([125, 640, 3], dtype=np.int32)                    # the first sequence's rows cross a page boundary
+    cs, sn = O.rope_tables(HD, (pos[:, None] + np.arange(rows)[None]).reshape(-1))
+    table = np.array([[7, 2, -1, -1, -1, -1, -1, -1], [0, 1, 3, 4, 5, 6, -1, -1], [8, -1, -1, -1, -1, -1, -1, -1]], dtype=np.int32)
+    td = torch.from_numpy(table).to(eng.device)
+    pages, pool_k, pool_v = eng.alloc_pages(9, page_len, td, fill=0)
+    kvk, kvv = eng.alloc_kv_layer(False, fill=0)
+    up = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(eng.device)
+    qd, kd, vd, sq, csd, snd = up(q), up(k), up(v), up(sqk), up(cs), up(sn)
+    posd, rowsd = dev_i32(pos, eng.device), dev_i32([0, 1, 2], eng.device)
+    q_a = torch.empty_like(qd, dtype=eng.q_torch)
+    q_b = torch.empty_like(qd, dtype=eng.q_torch)
+    eng.qkv_prep(q_a, qd, kd, vd, sq, csd, snd, kvk, kvv, posd, kslot=rowsd, rows=rows)
+    eng.qkv_prep_paged(q_b, qd, kd, vd, sq, csd, snd, pages, posd, ktab=rowsd, rows=rows)
+    torch.cuda.synchronize()
+    assert torch.equal(q_a, q_b)
+    rec = g.rec
+    for pool, cache in ((pool_k, kvk), (pool_v, kvv)):
+        pool = pool.cpu().numpy().reshape(9, g.n_kv, page_len, rec)
+        cache = cache.cpu().numpy().reshape(n_seq, g.n_kv, g.slot_ctx, rec)
+        assert cache.any()
+        for i in range(n_seq):
+            for p in range(int(pos[i]), int(pos[i]) + rows):
+                assert (pool[table[i, p // page_len], :, p % page_len] == cache[i, :, p]).all(), (i, p)
+    assert eng.device_status() == 0
