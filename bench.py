@@ -304,6 +304,7 @@ def bench_prefill(torch, AttnEngine, G_B, device, reps: int, window: int = WINDO
     WINDOW = window
     g = G_B.with_(slot_ctx=PREFILL_PROMPT, window=WINDOW)
     eng = AttnEngine(g, device)
+    eng.set_early_kv_stream(True)      # append -> attention on one position buffer: the order the option asks for
     dev = eng.device
     gen = torch.Generator(device=dev)
     gen.manual_seed(7)

@@ -327,6 +327,9 @@ int launch_prefill(battn_handle* h, void* out, const void* q, const uint8_t* kvk
     P.scale_log2 = g.scale * LOG2E; P.status = h->d_status;
     apply_paging(P, pv);
     if (pv) P.slot = table_row;
+    // early KV streaming (head_dim 128): only behind the append / prologue of exactly this chunk, or no cache write
+    P.early = g.HD == 128 && h->early_stream &&
+              (h->kvw_kind == 0 || (h->kvw_kind == 1 && h->kvw_pos == pos && h->kvw_nseq == 1 && h->kvw_rows == rows));
     h->kvw_kind = 0;
     const int MR = 128 / g.G;
     P.nsplit = prefill_splits(h, rows, is_swa);
@@ -339,13 +342,15 @@ int launch_prefill(battn_handle* h, void* out, const void* q, const uint8_t* kvk
             cudaLaunchConfig_t cfg = {};
             cfg.gridDim = dim3((grid.x + 1) & ~1u, grid.y, grid.z); cfg.blockDim = dim3(pf128::NTHREADS);
             cfg.dynamicSmemBytes = pf128::TOTAL_PAIR; cfg.stream = st;
-            cudaLaunchAttribute attr[1];
+            cudaLaunchAttribute attr[2];
             attr[0].id = cudaLaunchAttributeClusterDimension;
             attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-            cfg.attrs = attr; cfg.numAttrs = 1;
+            attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[1].val.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs = attr; cfg.numAttrs = 2;
             cudaLaunchKernelEx(&cfg, pf128::k_prefill_hd128<true>, P);
         } else if (g.HD == 128) {
-            pf128::k_prefill_hd128<false><<<grid, pf128::NTHREADS, pf128::TOTAL, st>>>(P);
+            launch_pdl(pf128::k_prefill_hd128<false>, grid, dim3(pf128::NTHREADS), pf128::TOTAL, st, P);
         }
         else             pf::k_prefill<256, 64><<<grid, pf::NTHREADS, pf::Cfg<256, 64>::TOTAL, st>>>(P);
     }

@@ -71,6 +71,11 @@ struct Params {
     float* recs;
     Paging pg;       // table != nullptr: paged cache of a full-causal layer; `slot` is the table row of the sequence
     int slot = 0;
+    // head_dim 128 kernel, launched with programmatic stream serialisation: with early != 0 the position is read and
+    // the key tiles that lie entirely below the chunk's first row are streamed and converted before
+    // griddepcontrol.wait, i.e. while the append of the chunk's own rows is still running; Q, the tiles holding the
+    // chunk's rows and every write come after it (same contract as fd::Params::early)
+    int early = 0;
 };
 
 template <int HD, int BN>

@@ -182,6 +182,8 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill_hd128(const Params P) {
     const int mt_pair = n_mt - 1 - (PAIR ? (int)blockIdx.x & ~1 : (int)blockIdx.x);    // longest key ranges first (bruce.cu:2770)
     const int mt = mt_pair - crank;
     const int kvh = blockIdx.y;
+    const bool early = P.early != 0;
+    if (!early) { pdl_wait(); pdl_trigger(); }
     const int p0 = P.pos[0];
     if (p0 < 0 || (!P.is_swa && p0 + P.rows > P.slot_ctx)) {
         if (tid == 0) atomicOr(P.status, BATTN_DEV_BAD_POSITION);
@@ -203,6 +205,7 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill_hd128(const Params P) {
     const int n_tiles = max(0, min(per_split, n_all - (int)blockIdx.z * per_split));
     if (n_tiles == 0) {
         // more splits than key tiles (shallow context): an empty record, so the merge ignores this share
+        if (early) pdl_wait();
         if (tid < 128 && tid / G < rows_eff) {
             float* rec = P.recs + ((((size_t)blockIdx.z * P.rows) + rbase + tid / G) * P.Hq + kvh * G + tid % G) * (size_t)(HD + 2);
             for (int i = 0; i < HD; ++i) rec[i] = 0.f;
@@ -253,6 +256,7 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill_hd128(const Params P) {
     // Q into tensor memory: lane = row m = (position m / G, head m % G) (the reference's pair packing,
     // bruce.cu:2288-2296), 32-bit column c = dims (2c, 2c+1); two threads per row
     if (tid < 256) {
+        if (early) { pdl_wait(); pdl_trigger(); }              // Q is the predecessor's output; so is everything these warps write
         const int m = tid & 127, half = tid >> 7;
         const int r = m / G, h = m - r * G;
         uint32_t qv[32];
@@ -395,7 +399,10 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill_hd128(const Params P) {
             const uint8_t* src = isv ? P.kvv : P.kvk;
             uint8_t* ring = smem + (isv ? OFF_RAWV : OFF_RAWK);
             const int full = isv ? B_VRAW_FULL : B_KRAW_FULL, free_ = isv ? B_VRAW_FREE : B_KRAW_FREE;
+            bool waited = !early;
             for (int j = 0; j < n_tiles; ++j) {
+                // early streaming stops at the first tile that holds a row of this chunk
+                if (!waited && (tile_first + j + 1) * BN > p0) { pdl_wait(); pdl_trigger(); waited = true; }
                 if (j >= NB) wait(free_ + slot(j), phase(j - NB), 200);         // the dequant group left it (no hurry: the ring is three deep)
                 const int sp = ((tile_first + j) * BN) & P.ring_mask;
                 const int nk = P.pg.table ? BN : min(BN, P.pstride - sp);

@@ -181,3 +181,34 @@ def test_pair_kernel_tile_count_edges(name, is_swa):
         want = O.attend(og, q, okvk, okvv, [depth], rows=rows, is_swa=is_swa)
         assert_close(to_np(out), want, f"pair edges {name} swa={is_swa} rows {rows} depth {depth}")
         assert eng.device_status() == 0
+
+
+@pytest.mark.parametrize("is_swa", [False, True])
+def test_prompt_chunks_with_early_kv_streaming(is_swa):
+    """The prompt flow with early KV streaming on: every chunk's append and its attention call share one position
+    buffer (the pattern the library recognises), nothing synchronises in between, and the attention kernel starts
+    streaming the older tiles while the append of the chunk's own rows is still running.  All chunks are checked."""
+    from bruce_engine_b200.engine import AttnEngine
+    n_prompt, chunk, window = 1800, 384, 512
+    g = _geom("B32", slot_ctx=n_prompt, window=window)
+    eng, og = AttnEngine(g), oracle_geom(g)
+    eng.set_early_kv_stream(True)
+    q, k, v = draw_qkv(g, n_prompt, n_prompt, 31, q_f16=True)
+    kvk, kvv = eng.alloc_kv_layer(is_swa, fill=0xFF)
+    okvk, okvv = O.new_cache(og, is_swa, fill=0xFF), O.new_cache(og, is_swa, fill=0xFF)
+    kd, vd, qd = torch.from_numpy(k).cuda(), torch.from_numpy(v).cuda(), dev_q(eng, q)
+    part = eng.alloc_part(1, chunk)
+    outs = []
+    for a in range(0, n_prompt, chunk):
+        rows = min(chunk, n_prompt - a)
+        pos_d = dev_i32([a], eng.device)                    # a copy: complete before the append starts
+        eng.qkv_prep_store(kd[a:a + rows], vd[a:a + rows], kvk, kvv, pos_d, rows=rows, is_swa=is_swa)
+        out = new_out(eng, 1, rows, g.n_head, g.head_dim)
+        eng.launch_attn_m(out, qd[:, a:a + rows], kvk, kvv, pos_d, part, rows, is_swa)
+        outs.append((a, rows, out))
+    torch.cuda.synchronize()
+    for a, rows, out in outs:
+        oracle_fill(og, k[a:a + rows], v[a:a + rows], is_swa, kvk=okvk, kvv=okvv, start=a)
+        want = O.attend(og, q[:, a:a + rows], okvk, okvv, [a], rows=rows, is_swa=is_swa)
+        assert_close(to_np(out), want, f"early prompt chunk at {a} swa={is_swa}")
+    assert eng.device_status() == 0
