@@ -371,8 +371,9 @@ int launch_prefill(battn_handle* h, void* out, const void* q, const uint8_t* kvk
         M.mode = MERGE_GATHERED; M.part = P.recs; M.out = out; M.rec_out = nullptr;
         M.n_rows = rows; M.rows = 1; M.Hq = g.Hq; M.Hkv = g.Hkv; M.G = g.G;
         M.count = P.nsplit; M.log2_domain = 1; M.out_f16 = g.out_f16; M.status = h->d_status;
-        if (g.HD == 128) k_merge<128><<<rows * g.Hq, MERGE_THREADS, 0, st>>>(M);
-        else             k_merge<256><<<rows * g.Hq, MERGE_THREADS, 0, st>>>(M);
+        // (programmatic launch: the merge's blocks are resident and past their launch when the prompt kernel drains)
+        if (g.HD == 128) launch_pdl(k_merge<128>, dim3(rows * g.Hq), dim3(MERGE_THREADS), 0, st, M);
+        else             launch_pdl(k_merge<256>, dim3(rows * g.Hq), dim3(MERGE_THREADS), 0, st, M);
         h->launches += 1;
         e = cudaGetLastError();
     }

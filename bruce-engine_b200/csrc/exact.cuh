@@ -232,6 +232,8 @@ __global__ void __launch_bounds__(MERGE_THREADS) k_merge(const MergeParams P) {
     const int i = rowidx / P.rows;
     const int kvh = hq / P.G, h = hq % P.G;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    pdl_wait();                                  // (a no-op unless launched with programmatic stream serialisation)
+    pdl_trigger();
     const float* base;
     size_t stride;
     int count;
