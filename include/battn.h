@@ -253,7 +253,7 @@ int battn_partials(battn_handle* h, float* rec, const void* q, const uint8_t* kv
  * running; with this option they read pos / kslot / act and begin to stream the cache tiles that lie entirely below
  * the call's first position before that kernel has finished, while Q, the tile holding the call's own rows and every
  * write wait for it (about 0.8 us less per call).  The host promises that the kernel which precedes the call in the
- * stream writes neither pos / kslot / act nor cache rows other than the call's own (pos[i] .. pos[i]+rows-1) --
+ * stream writes neither pos / kslot / act (nor the page table of a paged call) nor cache rows other than the call's own (pos[i] .. pos[i]+rows-1) --
  * the reference's step order: positions uploaded by a copy at the start of the step (bruce.cu:8043, 8259),
  * k_qkv_prep* right before the attention launch (:7667-7732).  Copies and graph launches order fully and are always
  * safe predecessors.  The library additionally checks what it can see: a call streams early only if the last launch
