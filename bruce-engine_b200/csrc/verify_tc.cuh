@@ -512,10 +512,17 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_verify_tc(const fd::Params P) {
                     tmem_ld16_nowait(tS + 2 * NP, c);
                     tmem_ld16_nowait(tS + 3 * NP, d);
                     tmem_ld_wait();
+                    // two pairs per instruction (fma.rn.f32x2): the same products and sums, in the same order
+                    const uint64_t sx = pack_f2(sc.x, sc.x), sy = pack_f2(sc.y, sc.y), sz = pack_f2(sc.z, sc.z), sw = pack_f2(sc.w, sc.w);
 #pragma unroll
-                    for (int i = 0; i < NPH; ++i)
-                        v[i] = fmaf(__uint_as_float(d[i]), sc.w, fmaf(__uint_as_float(c[i]), sc.z,
-                               fmaf(__uint_as_float(b[i]), sc.y, __uint_as_float(a[i]) * sc.x)));
+                    for (int i = 0; i < NPH; i += 2) {
+                        uint64_t t;
+                        asm("{\n\t.reg .b64 x;\n\tmov.b64 x, {%1, %2};\n\tmul.rn.f32x2 %0, x, %3;\n\t}" : "=l"(t) : "r"(a[i]), "r"(a[i + 1]), "l"(sx));
+                        asm("{\n\t.reg .b64 x;\n\tmov.b64 x, {%1, %2};\n\tfma.rn.f32x2 %0, x, %3, %0;\n\t}" : "+l"(t) : "r"(b[i]), "r"(b[i + 1]), "l"(sy));
+                        asm("{\n\t.reg .b64 x;\n\tmov.b64 x, {%1, %2};\n\tfma.rn.f32x2 %0, x, %3, %0;\n\t}" : "+l"(t) : "r"(c[i]), "r"(c[i + 1]), "l"(sz));
+                        asm("{\n\t.reg .b64 x;\n\tmov.b64 x, {%1, %2};\n\tfma.rn.f32x2 %0, x, %3, %0;\n\t}" : "+l"(t) : "r"(d[i]), "r"(d[i + 1]), "l"(sw));
+                        asm("mov.b64 {%0, %1}, %2;" : "=f"(v[i]), "=f"(v[i + 1]) : "l"(t));
+                    }
                 }
                 tc_fence_before();
                 __syncwarp();
@@ -533,9 +540,13 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_verify_tc(const fd::Params P) {
                     }
                 }
                 // ---- does any score of the tile outgrow its reference?  (own differences, then a vote) --------------
-                float dmax = v[0] - ref[0];
+                float dv[NPH];                                     // score minus reference: the exponent of the weight
 #pragma unroll
-                for (int i = 1; i < NPH; ++i) dmax = fmaxf(dmax, v[i] - ref[i]);
+                for (int i = 0; i < NPH; ++i) dv[i] = v[i] - ref[i];
+                float dmax = fmax3(dv[0], dv[1], dv[2]);
+#pragma unroll
+                for (int i = 3; i + 1 < NPH; i += 2) dmax = fmax3(dmax, dv[i], dv[i + 1]);
+                dmax = fmaxf(dmax, dv[NPH - 1]);
                 const bool over = __any_sync(0xffffffffu, dmax > RESCALE_THRESHOLD);
                 if (lane == 0) flagx[(cnt & 1) * 4 + wq] = over ? 1.f : 0.f;
                 named_bar_sync(bar_a, 128);
@@ -583,6 +594,8 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_verify_tc(const fd::Params P) {
                         tc_fence_before();
                     }
                     __syncwarp();
+#pragma unroll
+                    for (int i = 0; i < NPH; ++i) dv[i] = v[i] - ref[i];           // against the new references
                 }
                 // ---- P^T = 2^(s - ref), fp16, into the B operand [pair][key]; the sums take the rounded weights ----
                 // the product that read this P buffer (two tiles ago) must be complete
@@ -591,7 +604,7 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_verify_tc(const fd::Params P) {
                 if (tid == 0) VT_TRACE(6, cnt, 2);
 #pragma unroll
                 for (int i = 0; i < NPH; i += 2) {
-                    const uint32_t ph = pack_h2(fast_exp2(v[i] - ref[i]), fast_exp2(v[i + 1] - ref[i + 1]));
+                    const uint32_t ph = pack_h2(fast_exp2(dv[i]), fast_exp2(dv[i + 1]));
                     // the two fp16 weights back as fp32 without the conversion unit: the half's bits moved into an fp32
                     // word, times 2^112 (exact for every non-negative half, subnormals included)
                     lsum[i] = fmaf(__uint_as_float((ph << 13) & 0x0FFFE000u), 5.192296858534828e33f, lsum[i]);
