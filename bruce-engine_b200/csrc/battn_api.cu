@@ -327,8 +327,8 @@ int launch_prefill(battn_handle* h, void* out, const void* q, const uint8_t* kvk
     P.scale_log2 = g.scale * LOG2E; P.status = h->d_status;
     apply_paging(P, pv);
     if (pv) P.slot = table_row;
-    // early KV streaming (head_dim 128): only behind the append / prologue of exactly this chunk, or no cache write
-    P.early = g.HD == 128 && h->early_stream &&
+    // early KV streaming: only behind the append / prologue of exactly this chunk, or no cache write
+    P.early = h->early_stream &&
               (h->kvw_kind == 0 || (h->kvw_kind == 1 && h->kvw_pos == pos && h->kvw_nseq == 1 && h->kvw_rows == rows));
     h->kvw_kind = 0;
     const int MR = 128 / g.G;
@@ -352,7 +352,7 @@ int launch_prefill(battn_handle* h, void* out, const void* q, const uint8_t* kvk
         } else if (g.HD == 128) {
             launch_pdl(pf128::k_prefill_hd128<false>, grid, dim3(pf128::NTHREADS), pf128::TOTAL, st, P);
         }
-        else             pf::k_prefill<256, 64><<<grid, pf::NTHREADS, pf::Cfg<256, 64>::TOTAL, st>>>(P);
+        else             launch_pdl(pf::k_prefill<256, 64>, grid, dim3(pf::NTHREADS), pf::Cfg<256, 64>::TOTAL, st, P);
     }
     h->launches += 1;
     cudaError_t e = cudaGetLastError();

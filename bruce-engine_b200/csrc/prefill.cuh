@@ -71,7 +71,7 @@ struct Params {
     float* recs;
     Paging pg;       // table != nullptr: paged cache of a full-causal layer; `slot` is the table row of the sequence
     int slot = 0;
-    // head_dim 128 kernel, launched with programmatic stream serialisation: with early != 0 the position is read and
+    // Both prompt kernels are launched with programmatic stream serialisation: with early != 0 the position is read and
     // the key tiles that lie entirely below the chunk's first row are streamed and converted before
     // griddepcontrol.wait, i.e. while the append of the chunk's own rows is still running; Q, the tiles holding the
     // chunk's rows and every write come after it (same contract as fd::Params::early)
@@ -266,6 +266,8 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill(const Params P) {
     const int n_mt = (P.rows + MR - 1) / MR;
     const int mt = n_mt - 1 - (int)blockIdx.x;              // longest key ranges first (bruce.cu:2770)
     const int kvh = blockIdx.y;
+    const bool early = P.early != 0;                        // see Params::early
+    if (!early) { pdl_wait(); pdl_trigger(); }
     const int p0 = P.pos[0];
     if (p0 < 0 || (!P.is_swa && p0 + P.rows > P.slot_ctx)) {
         if (tid == 0) atomicOr(P.status, BATTN_DEV_BAD_POSITION);
@@ -284,6 +286,7 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill(const Params P) {
     const int n_tiles = max(0, min(per_split, n_all - (int)blockIdx.z * per_split));
     if (n_tiles == 0) {
         // more splits than key tiles (shallow context): an empty record, so the merge ignores this share
+        if (early) pdl_wait();
         if (tid < 128 && tid / G < rows_eff) {
             float* rec = P.recs + ((((size_t)blockIdx.z * P.rows) + rbase + tid / G) * P.Hq + kvh * G + tid % G) * (size_t)(HD + 2);
             for (int i = 0; i < HD; ++i) rec[i] = 0.f;
@@ -339,6 +342,7 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill(const Params P) {
     if constexpr (C::Q_TMEM) {
         // Q into tensor memory: lane = row m, 32-bit column c = dims (2c, 2c+1); two threads per row
         if (tid < NSOFT) {
+            if (early) { pdl_wait(); pdl_trigger(); }             // Q is the predecessor's output; so is everything these warps write
             const int m = tid & 127, half = tid >> 7;
             const int r = m / G, h = m - r * G;
 #pragma unroll 1
@@ -445,8 +449,11 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_prefill(const Params P) {
     } else if (warp == (NSOFT + 2 * NDEQ) / 32 + 1) {
         // ======================= loader: streams raw K and V tiles into the ring with bulk copies ========
         if (lane == 0) {
+            bool waited = !early;
             for (int j = 0; j < n_tiles; ++j) {
                 const int b = j % C::RAW_STAGES;
+                // early streaming stops at the first tile that holds a row of this chunk
+                if (!waited && (tile_first + j + 1) * BN > p0) { pdl_wait(); pdl_trigger(); waited = true; }
                 if (j >= C::RAW_STAGES) wait(B_RAW_FREE0 + b, (j / C::RAW_STAGES - 1) & 1);   // both dequant groups left it
                 const int sp = ((tile_first + j) * BN) & P.ring_mask;
                 const int nk = P.pg.table ? BN : min(BN, P.pstride - sp);

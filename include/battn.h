@@ -249,7 +249,7 @@ int battn_partials(battn_handle* h, float* rec, const void* q, const uint8_t* kv
                    int rows, int batch, int is_swa, void* stream);
 
 /* Early KV streaming (off by default; battn_set_early_kv_stream(h, 1) turns it on for the handle).  The decode and
- * 2..4-row verify kernels and the head_dim-128 prompt kernel are launched so that they may start while the previous kernel of the stream is still
+ * 2..4-row verify kernels and the prompt kernels are launched so that they may start while the previous kernel of the stream is still
  * running; with this option they read pos / kslot / act and begin to stream the cache tiles that lie entirely below
  * the call's first position before that kernel has finished, while Q, the tile holding the call's own rows and every
  * write wait for it (about 0.8 us less per call).  The host promises that the kernel which precedes the call in the

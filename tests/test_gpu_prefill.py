@@ -183,17 +183,18 @@ def test_pair_kernel_tile_count_edges(name, is_swa):
         assert eng.device_status() == 0
 
 
+@pytest.mark.parametrize("name", ["B32", "R"])
 @pytest.mark.parametrize("is_swa", [False, True])
-def test_prompt_chunks_with_early_kv_streaming(is_swa):
+def test_prompt_chunks_with_early_kv_streaming(name, is_swa):
     """The prompt flow with early KV streaming on: every chunk's append and its attention call share one position
     buffer (the pattern the library recognises), nothing synchronises in between, and the attention kernel starts
     streaming the older tiles while the append of the chunk's own rows is still running.  All chunks are checked."""
     from bruce_engine_b200.engine import AttnEngine
     n_prompt, chunk, window = 1800, 384, 512
-    g = _geom("B32", slot_ctx=n_prompt, window=window)
+    g = _geom(name, slot_ctx=n_prompt, window=window)
     eng, og = AttnEngine(g), oracle_geom(g)
     eng.set_early_kv_stream(True)
-    q, k, v = draw_qkv(g, n_prompt, n_prompt, 31, q_f16=True)
+    q, k, v = draw_qkv(g, n_prompt, n_prompt, 31, q_f16=True)     # fp16-representable queries in both geometries
     kvk, kvv = eng.alloc_kv_layer(is_swa, fill=0xFF)
     okvk, okvv = O.new_cache(og, is_swa, fill=0xFF), O.new_cache(og, is_swa, fill=0xFF)
     kd, vd, qd = torch.from_numpy(k).cuda(), torch.from_numpy(v).cuda(), dev_q(eng, q)
@@ -210,5 +211,5 @@ def test_prompt_chunks_with_early_kv_streaming(is_swa):
     for a, rows, out in outs:
         oracle_fill(og, k[a:a + rows], v[a:a + rows], is_swa, kvk=okvk, kvv=okvv, start=a)
         want = O.attend(og, q[:, a:a + rows], okvk, okvv, [a], rows=rows, is_swa=is_swa)
-        assert_close(to_np(out), want, f"early prompt chunk at {a} swa={is_swa}")
+        assert_close(to_np(out), want, f"early prompt chunk {name} at {a} swa={is_swa}")
     assert eng.device_status() == 0
