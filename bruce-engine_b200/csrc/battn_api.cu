@@ -371,9 +371,11 @@ int launch_prefill(battn_handle* h, void* out, const void* q, const uint8_t* kvk
         M.mode = MERGE_GATHERED; M.part = P.recs; M.out = out; M.rec_out = nullptr;
         M.n_rows = rows; M.rows = 1; M.Hq = g.Hq; M.Hkv = g.Hkv; M.G = g.G;
         M.count = P.nsplit; M.log2_domain = 1; M.out_f16 = g.out_f16; M.status = h->d_status;
-        // (programmatic launch: the merge's blocks are resident and past their launch when the prompt kernel drains)
+        // (head_dim 128: programmatic launch, the merge's blocks are resident and past their launch when the prompt
+        // kernel drains -- 2 us less on a short chunk; at head_dim 256, where every 512-row chunk is split and the merge
+        // has thousands of blocks, the early launch cost 2 % and the plain launch stays)
         if (g.HD == 128) launch_pdl(k_merge<128>, dim3(rows * g.Hq), dim3(MERGE_THREADS), 0, st, M);
-        else             launch_pdl(k_merge<256>, dim3(rows * g.Hq), dim3(MERGE_THREADS), 0, st, M);
+        else             k_merge<256><<<rows * g.Hq, MERGE_THREADS, 0, st>>>(M);
         h->launches += 1;
         e = cudaGetLastError();
     }
