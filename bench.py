@@ -281,10 +281,15 @@ class Layer:
     def decode(self):
         self.eng.launch_attn_m(self.out, self.q, self.kvk, self.kvv, self.pos, self.part, 1, self.is_swa)
 
-    def decode_e2e(self):
-        """Append the step's new K/V row and attend, on the staged inputs (no copies here)."""
-        self.eng.qkv_prep_store(self.s_k, self.s_v, self.kvk, self.kvv, self.s_pos, rows=1, is_swa=self.is_swa)
-        self.eng.launch_attn_m(self.s_out, self.s_q, self.kvk, self.kvv, self.s_pos, self.part, 1, self.is_swa)
+    def decode_e2e(self, two_calls: bool = False):
+        """Append the step's new K/V row and attend, on the staged inputs (no copies here): one call whose decode
+        kernel appends the row itself, or (two_calls) battn_kv_append followed by battn_decode."""
+        if two_calls:
+            self.eng.qkv_prep_store(self.s_k, self.s_v, self.kvk, self.kvv, self.s_pos, rows=1, is_swa=self.is_swa)
+            self.eng.launch_attn_m(self.s_out, self.s_q, self.kvk, self.kvv, self.s_pos, self.part, 1, self.is_swa)
+        else:
+            self.eng.decode_append(self.s_out, self.s_q, self.s_k, self.s_v, self.kvk, self.kvv, self.s_pos,
+                                   self.part, is_swa=self.is_swa)
 
 
 PREFILL_PROMPT, PREFILL_CHUNK = 16384, 512
@@ -955,7 +960,7 @@ def run_gpu(args):
     def e2e_enqueue():
         d_in.copy_(h_in, non_blocking=True)
         for L in layers:
-            L.decode_e2e()
+            L.decode_e2e(args.e2e_two_calls)
         h_out.copy_(d_out, non_blocking=True)
 
     graph_e2e = capture(e2e_enqueue)
@@ -1086,6 +1091,8 @@ def run_gpu(args):
                                        "ms_per_step and value are per step of one block",
                        "block_repeats": repeats,
                        "early_kv_stream": True,
+                       "e2e_call": "battn_kv_append + battn_decode" if args.e2e_two_calls else
+                                   "battn_decode_append (the decode kernel quantises and stores the step's row)",
                        "n_gt_1": "value at N > 1 = N replicas of this sweep (one sequence set per GPU); the sharded "
                                  "workloads and their efficiency are in scaling_detail"},
             "e2e": {"value": e2e_value, "unit": "TB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -1113,6 +1120,8 @@ def main():
     ap.add_argument("--steps", type=int, default=500)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--e2e-two-calls", action="store_true",
+                    help="end-to-end region with battn_kv_append + battn_decode instead of battn_decode_append")
     ap.add_argument("--light", action="store_true", help="profiling run: eager launches, kernel timings only")
     ap.add_argument("--only-ctx", type=int, default=0, help="restrict the decode sweep to one context")
     ap.add_argument("--case", default="decode", choices=["decode", "prefill", "verify"], help="light run of one kernel family")

@@ -241,7 +241,7 @@ cudaError_t launch_fd_kernel(const fd::Params& P, int grid, size_t smem, cudaStr
 int launch_flash(battn_handle* h, void* out, float* rec_out, const void* q, const uint8_t* kvk, const uint8_t* kvv,
                  const int* pos, const int* kslot, const int* act, void* ws, int n_seq, int rows, int is_swa,
                  cudaStream_t st, const XchgView* xv = nullptr, int* epoch_ptr = nullptr, int epoch_advance = 0,
-                 const PagedView* pv = nullptr) {
+                 const PagedView* pv = nullptr, const float* k_new = nullptr, const float* v_new = nullptr) {
     const Geom& g = h->g;
     const int RG = rows * g.G;
     if (RG > 32) return BATTN_ERR_CAPACITY;
@@ -256,6 +256,7 @@ int launch_flash(battn_handle* h, void* out, float* rec_out, const void* q, cons
     P.slot_ctx = g.slot_ctx; P.n_slots = g.n_slots; P.is_swa = is_swa; P.q_f16 = g.q_f16;
     P.scale_log2 = g.scale * LOG2E; P.status = h->d_status;
     P.epoch_ptr = epoch_ptr; P.epoch_advance = epoch_advance;
+    P.k_new = k_new; P.v_new = v_new; P.kvk_w = const_cast<uint8_t*>(kvk); P.kvv_w = const_cast<uint8_t*>(kvv);
     apply_paging(P, pv);
     if (pv) P.n_slots = pv->n_tables;
     // early KV streaming: only when the last launch on this handle wrote no cache rows but this call's own
@@ -619,6 +620,16 @@ int battn_decode(battn_handle* h, void* out, const void* q, const uint8_t* kvk, 
     return launch_flash(h, out, nullptr, q, kvk, kvv, pos, kslot, act, ws, n_seq, 1, is_swa, (cudaStream_t)stream);
 }
 
+int battn_decode_append(battn_handle* h, void* out, const void* q, const float* k, const float* v, uint8_t* kvk,
+                        uint8_t* kvv, const int* pos, const int* kslot, const int* act, void* ws, int n_seq, int is_swa,
+                        void* stream) {
+    const int rc = check_seq_args(h, out, q, kvk, kvv, pos, kslot, n_seq, 1, 1);
+    if (rc) return rc;
+    if (!ws || ((uintptr_t)ws & 15) || !k || !v || ((((uintptr_t)k | (uintptr_t)v)) & 15)) return BATTN_ERR_ARG;
+    return launch_flash(h, out, nullptr, q, kvk, kvv, pos, kslot, act, ws, n_seq, 1, is_swa, (cudaStream_t)stream, nullptr,
+                        nullptr, 0, nullptr, k, v);
+}
+
 int battn_decode_noalloc(battn_handle* h, void* out, const void* q, const uint8_t* kvk, const uint8_t* kvv,
                          const int* pos, const int* kslot, const int* act, int n_seq, int is_swa, void* stream) {
     const int rc = check_seq_args(h, out, q, kvk, kvv, pos, kslot, n_seq, 1, 1);
@@ -756,6 +767,19 @@ int battn_decode_paged(battn_handle* h, void* out, const void* q, const battn_pa
     if (!ws || ((uintptr_t)ws & 15)) return BATTN_ERR_ARG;
     return launch_flash(h, out, nullptr, q, pages->pool_k, pages->pool_v, pos, ktab, act, ws, n_seq, 1, 0,
                         (cudaStream_t)stream, nullptr, nullptr, 0, &pv);
+}
+
+int battn_decode_append_paged(battn_handle* h, void* out, const void* q, const float* k, const float* v,
+                              const battn_pages* pages, const int* pos, const int* ktab, const int* act, void* ws,
+                              int n_seq, void* stream) {
+    PagedView pv;
+    int rc = paged_view(pages, pv);
+    if (rc) return rc;
+    rc = check_seq_args(h, out, q, pages->pool_k, pages->pool_v, pos, ktab, n_seq, 1, 1);
+    if (rc) return rc;
+    if (!ws || ((uintptr_t)ws & 15) || !k || !v || ((((uintptr_t)k | (uintptr_t)v)) & 15)) return BATTN_ERR_ARG;
+    return launch_flash(h, out, nullptr, q, pages->pool_k, pages->pool_v, pos, ktab, act, ws, n_seq, 1, 0,
+                        (cudaStream_t)stream, nullptr, nullptr, 0, &pv, k, v);
 }
 
 int battn_verify_paged(battn_handle* h, void* out, const void* q, const battn_pages* pages, const int* pos,

@@ -25,6 +25,7 @@
 //     of four), which makes every shared-memory read of the 136-byte-stride records conflict-free.
 #pragma once
 #include "common.cuh"
+#include "kv_append.cuh"
 
 namespace battn {
 namespace fd {
@@ -64,6 +65,14 @@ struct Params {
     // memory when the predecessor finishes.  Q, the tile that holds the step's own rows, and every write (header,
     // records, epoch) come after the wait.  The host sets early only when the predecessor wrote no other cache rows.
     int early;
+    // Decode that appends its own row (rows == 1): k_new / v_new are the step's fp32 K and V rows
+    // [n_seq][n_kv][head_dim].  The CTA whose share holds the tile of position pos[i] quantises the row of its kv head
+    // into that tile in shared memory (the bulk copy brought the slot's old bytes) and into the cache, with the append
+    // kernel's own quantiser, before the tile is used: no separate append launch in front of the attention call.
+    const float* k_new;
+    const float* v_new;
+    uint8_t* kvk_w;  // the caches again, writable
+    uint8_t* kvv_w;
 };
 
 template <int HD>
@@ -303,6 +312,19 @@ k_flash_decode(const Params P) {
                 const uint8_t* Kt = stages + (size_t)s * 2 * TILE_BYTES;
                 const uint8_t* Vt = Kt + TILE_BYTES;
                 const int t0 = (tile0 + t) * TILE;
+                if (P.k_new && sr.p0 >= t0 && sr.p0 < t0 + TILE) {
+                    // the tile of the call's own row: warp 0 writes the K record, warp 1 the V record
+                    if (warp < 2) {
+                        const float* src = (warp ? P.v_new : P.k_new) + ((size_t)pc.i * P.Hkv + pc.kvh) * HD;
+                        uint8_t* tile = stages + (size_t)s * 2 * TILE_BYTES + (warp ? TILE_BYTES : 0);
+                        quantise_record<HD>(src, tile + (sr.p0 - t0) * REC, lane);
+                        const size_t ri = kv_rec_index(P.pg, sr.slot, pc.kvh, P.Hkv, P.pstride, sr.p0 & P.ring_mask, P.status);
+                        quantise_record<HD>(src, (warp ? P.kvv_w : P.kvk_w) + ri * (size_t)REC, lane);
+                        // the stage is refilled by a bulk copy later: order these generic-proxy writes before it
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    }
+                    named_bar_sync(1, NW * 32);
+                }
                 // tiles every row sees completely take the mask-free path (bruce.cu:2927-2928)
                 const bool masked = !(t0 >= full_lo && t0 + TILE - 1 <= sr.p0);
 

@@ -23,6 +23,34 @@ struct AppendParams {
     Paging pg;          // table != nullptr: paged cache (pstride = positions a table row can hold)
 };
 
+// One warp quantises one (kv head, position) row of HD fp32 values into a scale-first q8_0 record at `dst` (global or
+// shared memory): per 32 values d = amax / 127, id = d ? 1 / d : 0, q = lrintf(x * id), scale = fp16(d), no clamp
+// (bruce.cu:698-710).  The one quantiser of the library: the append kernel and the decode kernel that appends its own
+// row both call it, so their bytes are the same by construction.
+template <int HD>
+__device__ __forceinline__ void quantise_record(const float* __restrict__ src, uint8_t* dst, int lane) {
+    constexpr int NBLK = HD / 32;
+#pragma unroll
+    for (int it = 0; it < HD / 128; ++it) {
+        const float4 x = *reinterpret_cast<const float4*>(src + it * 128 + lane * 4);
+        float amax = fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w)));
+        // 8 lanes x 4 values = one 32-value block
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+        const float d = __fdiv_rn(amax, 127.f);                       // IEEE divide (bruce.cu:704)
+        const float id = d != 0.f ? __fdiv_rn(1.f, d) : 0.f;          // (bruce.cu:705)
+        // lrintf(x * id): one fp32 multiply, round half to even, no clamp (bruce.cu:709)
+        const uint32_t q0 = (uint32_t)(uint8_t)(int8_t)__float2int_rn(__fmul_rn(x.x, id));
+        const uint32_t q1 = (uint32_t)(uint8_t)(int8_t)__float2int_rn(__fmul_rn(x.y, id));
+        const uint32_t q2 = (uint32_t)(uint8_t)(int8_t)__float2int_rn(__fmul_rn(x.z, id));
+        const uint32_t q3 = (uint32_t)(uint8_t)(int8_t)__float2int_rn(__fmul_rn(x.w, id));
+        *reinterpret_cast<uint32_t*>(dst + 2 * NBLK + it * 128 + lane * 4) = q0 | (q1 << 8) | (q2 << 16) | (q3 << 24);
+        if ((lane & 7) == 0)
+            reinterpret_cast<__half*>(dst)[it * 4 + (lane >> 3)] = __float2half_rn(d);   // (bruce.cu:708)
+    }
+}
+
 template <int HD>
 __global__ void __launch_bounds__(256) k_kv_append(const AppendParams P) {
     constexpr int NBLK = HD / 32;
@@ -52,25 +80,7 @@ __global__ void __launch_bounds__(256) k_kv_append(const AppendParams P) {
     const float* src = (which ? P.v : P.k) + (((size_t)i * P.rows + r) * P.Hkv + kvh) * HD;
     uint8_t* dst = (which ? P.kvv : P.kvk) + kv_rec_index(P.pg, slot, kvh, P.Hkv, P.pstride, pp, P.status) * (size_t)REC;
 
-#pragma unroll
-    for (int it = 0; it < HD / 128; ++it) {
-        const float4 x = *reinterpret_cast<const float4*>(src + it * 128 + lane * 4);
-        float amax = fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w)));
-        // 8 lanes x 4 values = one 32-value block
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
-        const float d = __fdiv_rn(amax, 127.f);                       // IEEE divide (bruce.cu:704)
-        const float id = d != 0.f ? __fdiv_rn(1.f, d) : 0.f;          // (bruce.cu:705)
-        // lrintf(x * id): one fp32 multiply, round half to even, no clamp (bruce.cu:709)
-        const uint32_t q0 = (uint32_t)(uint8_t)(int8_t)__float2int_rn(__fmul_rn(x.x, id));
-        const uint32_t q1 = (uint32_t)(uint8_t)(int8_t)__float2int_rn(__fmul_rn(x.y, id));
-        const uint32_t q2 = (uint32_t)(uint8_t)(int8_t)__float2int_rn(__fmul_rn(x.z, id));
-        const uint32_t q3 = (uint32_t)(uint8_t)(int8_t)__float2int_rn(__fmul_rn(x.w, id));
-        *reinterpret_cast<uint32_t*>(dst + 2 * NBLK + it * 128 + lane * 4) = q0 | (q1 << 8) | (q2 << 16) | (q3 << 24);
-        if ((lane & 7) == 0)
-            reinterpret_cast<__half*>(dst)[it * 4 + (lane >> 3)] = __float2half_rn(d);   // (bruce.cu:708)
-    }
+    quantise_record<HD>(src, dst, lane);
 }
 
 // Prefix sharing between slots: the first n_pos cached positions of slot `src` copied into slot `dst` of the same

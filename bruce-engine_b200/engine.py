@@ -148,6 +148,18 @@ class AttnEngine:
                                        _ptr(act), _ptr(part), rows_per_seq, rows, int(is_swa), st)
             self._check("battn_verify", rc)
 
+    def decode_append(self, out, q, k, v, kvk, kvv, pos, part, kslot=None, act=None, is_swa: bool = False):
+        """One row per sequence: append k, v ([n_seq][n_kv][head_dim] fp32) at pos[i] and attend, the append done by
+        the decode kernel itself (battn_decode_append)."""
+        rc = self.lib.battn_decode_append(self.h, _ptr(out), _ptr(q), _ptr(k), _ptr(v), _ptr(kvk), _ptr(kvv), _ptr(pos),
+                                          _ptr(kslot), _ptr(act), _ptr(part), pos.numel(), int(is_swa), self._stream())
+        self._check("battn_decode_append", rc)
+
+    def decode_append_paged(self, out, q, k, v, pages, pos, part, ktab=None, act=None):
+        rc = self.lib.battn_decode_append_paged(self.h, _ptr(out), _ptr(q), _ptr(k), _ptr(v), C.byref(pages), _ptr(pos),
+                                                _ptr(ktab), _ptr(act), _ptr(part), pos.numel(), self._stream())
+        self._check("battn_decode_append_paged", rc)
+
     def set_early_kv_stream(self, enable: bool):
         """Whether decode calls stream the cache tiles below their first position before the preceding kernel of
         the stream has finished (battn_set_early_kv_stream; off by default: the host must not let a kernel that

@@ -165,6 +165,17 @@ int battn_decode(battn_handle* h, void* out, const void* q, const uint8_t* kvk, 
                  const int* pos, const int* kslot, const int* act, void* ws,
                  int n_seq, int is_swa, void* stream);
 
+/* Decode that appends its own row: battn_kv_append (one row per sequence) and battn_decode in ONE launch pair.
+ *   k, v   fp32 [n_seq][n_kv][head_dim], already RoPE'd / normalised (as for battn_kv_append)
+ * The CTA of the decode kernel that streams the tile of position pos[i] quantises the row of its kv head -- with the
+ * append kernel's own quantiser, so the cache bytes are those battn_kv_append writes -- into that tile in shared memory
+ * and into the cache, before the tile is used.  Saves the append launch and the kernel boundary between it and the
+ * attention kernel (about 2.7 us per call).  For hosts that keep their own prologue kernel; hosts that use
+ * battn_qkv_prep (prologue and append fused) call battn_decode after it as before. */
+int battn_decode_append(battn_handle* h, void* out, const void* q, const float* k, const float* v, uint8_t* kvk,
+                        uint8_t* kvv, const int* pos, const int* kslot, const int* act, void* ws, int n_seq, int is_swa,
+                        void* stream);
+
 /* Decode attention for callers that cannot hand the library a scratch buffer.  (This entry point has
  * no counterpart in the reference, whose host always owns a `part` allocation.)
  *
@@ -303,6 +314,9 @@ int battn_qkv_prep_paged(battn_handle* h, void* q_out, const float* q, const flo
                          const int* ktab, const int* act, int n_seq, int rows_per_seq, void* stream);
 int battn_decode_paged(battn_handle* h, void* out, const void* q, const battn_pages* pages, const int* pos,
                        const int* ktab, const int* act, void* ws, int n_seq, void* stream);
+int battn_decode_append_paged(battn_handle* h, void* out, const void* q, const float* k, const float* v,
+                              const battn_pages* pages, const int* pos, const int* ktab, const int* act, void* ws,
+                              int n_seq, void* stream);
 int battn_verify_paged(battn_handle* h, void* out, const void* q, const battn_pages* pages, const int* pos,
                        const int* ktab, const int* act, void* ws, int rows, int batch, void* stream);
 int battn_prefill_paged(battn_handle* h, void* out, const void* q, const battn_pages* pages, int table_row,

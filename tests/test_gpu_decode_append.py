@@ -1,0 +1,139 @@
+"""battn_decode_append: the decode call that appends its own row, through the C ABI.
+
+Two copies of the same cache are stepped side by side with the same seeded rows: one by battn_kv_append followed by
+battn_decode (both pinned to the CPU oracle by the other tests), one by battn_decode_append.  After every step the
+outputs must be equal bit for bit, and at the end so must every byte of the two caches.  Covered: both geometries,
+full-causal and sliding-window layers (the ring wraps inside the run), ragged multi-slot batches with idle rows, an
+empty sequence (position 0), positions on both sides of a tile boundary, the paged cache, early KV streaming."""
+import numpy as np
+import pytest
+import torch
+
+from tests.gpu_util import dev_i32, dev_q, gpu_fill, new_out
+from tests.util import draw_qkv
+
+pytestmark = pytest.mark.gpu
+
+
+def _geom(name, **kw):
+    from bruce_engine_b200.layout import F32, G_B, G_R
+    base = {"B": G_B, "B32": G_B.with_(out_dtype=F32), "R": G_R}[name]
+    return base.with_(**kw)
+
+
+def _engine(g, early):
+    from bruce_engine_b200.engine import AttnEngine
+    eng = AttnEngine(g)
+    eng.set_early_kv_stream(early)
+    return eng
+
+
+def _bits(t):
+    return t.view(torch.int16 if t.element_size() == 2 else torch.int32)
+
+
+@pytest.mark.parametrize("early", [False, True])
+@pytest.mark.parametrize("name,is_swa", [("B32", False), ("B32", True), ("B", False), ("R", False), ("R", True)])
+def test_decode_append_equals_append_then_decode(name, is_swa, early):
+    window = 256
+    lens = [0, 1, 15, 16, 17, 255, 500, 2 * window - 3, 1500, 4097]
+    n_seq, steps = len(lens), 12
+    g = _geom(name, slot_ctx=4352, n_slots=n_seq + 2, window=window)
+    eng = _engine(g, early)
+    dev = eng.device
+    ka, va = eng.alloc_kv_layer(is_swa, fill=0x7F)
+    slots = [1, 0, 3, 2, 5, 4, 7, 6, 9, 11]                      # slot 8 and 10 stay untouched
+    for i, n in enumerate(lens):
+        if n:
+            _, k, v = draw_qkv(g, n, 1, 700 + i)
+            gpu_fill(eng, k, v, ka, va, is_swa, slot=slots[i])
+    torch.cuda.synchronize()
+    kb, vb = ka.clone(), va.clone()
+    part = eng.alloc_part(n_seq, 1)
+    kslot = dev_i32(slots, dev)
+    rng = np.random.default_rng(5)
+    for s in range(steps):
+        act_np = (rng.random(n_seq) < 0.8).astype(np.int32)
+        act_np[s % n_seq] = 0
+        pos_np = np.array(lens, dtype=np.int32)
+        q, k, v = draw_qkv(g, n_seq, 1, 900 + s, n_seq=n_seq, q_f16=(g.q_dtype == 1))
+        qd = dev_q(eng, q[:, 0])
+        kd = torch.from_numpy(k).to(dev)
+        vd = torch.from_numpy(v).to(dev)
+        pos, act = dev_i32(pos_np, dev), dev_i32(act_np, dev)
+        oa = new_out(eng, n_seq, g.n_head, g.head_dim)
+        ob = new_out(eng, n_seq, g.n_head, g.head_dim)
+        eng.qkv_prep_store(kd, vd, ka, va, pos, kslot=kslot, act=act, is_swa=is_swa)
+        eng.launch_attn_ms(oa, qd, ka, va, pos, kslot, act, part, n_seq, is_swa=is_swa)
+        eng.decode_append(ob, qd, kd, vd, kb, vb, pos, part, kslot=kslot, act=act, is_swa=is_swa)
+        torch.cuda.synchronize()
+        assert eng.device_status() == 0
+        assert torch.equal(_bits(oa), _bits(ob)), f"step {s}: outputs differ"
+        live = torch.from_numpy(act_np.astype(bool)).to(dev)
+        assert not torch.isnan(ob[live].float()).any() and torch.isnan(ob[~live].float()).all()
+        lens = [n + int(a) for n, a in zip(lens, act_np)]
+    assert torch.equal(ka, kb) and torch.equal(va, vb)
+
+
+def test_decode_append_single_sequence_without_slot_tables():
+    g = _geom("B32", slot_ctx=2048, n_slots=1)
+    eng = _engine(g, True)
+    dev = eng.device
+    ka, va = eng.alloc_kv_layer(False, fill=0x7F)
+    _, k, v = draw_qkv(g, 1000, 1, 3)
+    gpu_fill(eng, k, v, ka, va, False)
+    kb, vb = ka.clone(), va.clone()
+    part = eng.alloc_part(1, 1)
+    for s in range(20):
+        q, k, v = draw_qkv(g, 1, 1, 40 + s)
+        qd, kd, vd = dev_q(eng, q[:, 0]), torch.from_numpy(k).to(dev), torch.from_numpy(v).to(dev)
+        pos = dev_i32([1000 + s], dev)
+        oa, ob = new_out(eng, 1, g.n_head, g.head_dim), new_out(eng, 1, g.n_head, g.head_dim)
+        eng.qkv_prep_store(kd, vd, ka, va, pos)
+        eng.launch_attn_m(oa, qd, ka, va, pos, part, 1)
+        eng.decode_append(ob, qd, kd, vd, kb, vb, pos, part)
+        assert torch.equal(_bits(oa), _bits(ob))
+    assert torch.equal(ka, kb) and torch.equal(va, vb)
+
+
+@pytest.mark.parametrize("name", ["B32", "R"])
+def test_decode_append_paged(name):
+    page_len, lens = 128, [0, 127, 128, 300, 1000]
+    n_seq, steps = len(lens), 10
+    max_pages = 10
+    g = _geom(name, slot_ctx=page_len * max_pages, n_slots=n_seq)
+    eng = _engine(g, True)
+    dev = eng.device
+    rng = np.random.default_rng(11)
+    n_pages = n_seq * max_pages + 2
+    table_np = rng.permutation(n_pages)[:n_seq * max_pages].reshape(n_seq, max_pages).astype(np.int32)
+    table = torch.from_numpy(table_np).to(dev)
+    pa, pak, pav = eng.alloc_pages(n_pages, page_len, table, fill=0x7F)
+    for i, n in enumerate(lens):
+        if n:
+            _, k, v = draw_qkv(g, n, 1, 70 + i)
+            kd, vd = torch.from_numpy(k).to(dev), torch.from_numpy(v).to(dev)
+            for a in range(0, n, 512):
+                b = min(n, a + 512)
+                eng.kv_append_paged(pa, kd[a:b], vd[a:b], dev_i32([a], dev), ktab=dev_i32([i], dev), rows=b - a)
+    torch.cuda.synchronize()
+    pb, pbk, pbv = eng.alloc_pages(n_pages, page_len, table)
+    pbk.copy_(pak)
+    pbv.copy_(pav)
+    part = eng.alloc_part(n_seq, 1)
+    ktab = dev_i32(range(n_seq), dev)
+    for s in range(steps):
+        act_np = np.ones(n_seq, dtype=np.int32)
+        act_np[s % n_seq] = 0
+        q, k, v = draw_qkv(g, n_seq, 1, 300 + s, n_seq=n_seq, q_f16=(g.q_dtype == 1))
+        qd, kd, vd = dev_q(eng, q[:, 0]), torch.from_numpy(k).to(dev), torch.from_numpy(v).to(dev)
+        pos, act = dev_i32(lens, dev), dev_i32(act_np, dev)
+        oa, ob = new_out(eng, n_seq, g.n_head, g.head_dim), new_out(eng, n_seq, g.n_head, g.head_dim)
+        eng.kv_append_paged(pa, kd, vd, pos, ktab=ktab, act=act)
+        eng.attn_paged(oa, qd, pa, pos, part, rows=1, ktab=ktab, act=act)
+        eng.decode_append_paged(ob, qd, kd, vd, pb, pos, part, ktab=ktab, act=act)
+        torch.cuda.synchronize()
+        assert eng.device_status() == 0
+        assert torch.equal(_bits(oa), _bits(ob)), f"step {s}: outputs differ"
+        lens = [n + int(a) for n, a in zip(lens, act_np)]
+    assert torch.equal(pak, pbk) and torch.equal(pav, pbv)
