@@ -95,6 +95,8 @@ cudaError_t fd_prepare_all(battn_handle* h) {
     else           e = cudaFuncSetAttribute((const void*)pf::k_prefill<256, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, pf::Cfg<256, 64>::TOTAL);
     if (e != cudaSuccess) return e;
     if ((e = fd_prepare<HD, 1>(h, 0)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute((const void*)fd::k_flash_decode<HD, 1, true>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX)) != cudaSuccess) return e;
     if ((e = fd_prepare<HD, 2>(h, 1)) != cudaSuccess) return e;
     return cudaSuccess;
 }
@@ -234,6 +236,8 @@ int launch_exact(battn_handle* h, void* out, float* rec_out, const void* q, cons
 
 template <int HD, int NT>
 cudaError_t launch_fd_kernel(const fd::Params& P, int grid, size_t smem, cudaStream_t st) {
+    if constexpr (NT == 1)
+        if (P.k_new) return launch_pdl(fd::k_flash_decode<HD, 1, true>, dim3(grid), dim3(fd::NTHREADS), smem, st, P);
     return launch_pdl(fd::k_flash_decode<HD, NT>, dim3(grid), dim3(fd::NTHREADS), smem, st, P);
 }
 

@@ -114,7 +114,8 @@ __device__ __forceinline__ Piece locate(int g, int g1, const int* cum, int n_seq
     return pc;
 }
 
-template <int HD, int NT>
+// AP: the decode call that appends its own row (a separate instance, so that the plain kernel carries none of it)
+template <int HD, int NT, bool AP = false>
 __global__ void __launch_bounds__(NTHREADS, (NT == 1 ? 3 : (NT == 2 ? 2 : 1)))
 k_flash_decode(const Params P) {
     using C = Cfg<HD>;
@@ -312,7 +313,7 @@ k_flash_decode(const Params P) {
                 const uint8_t* Kt = stages + (size_t)s * 2 * TILE_BYTES;
                 const uint8_t* Vt = Kt + TILE_BYTES;
                 const int t0 = (tile0 + t) * TILE;
-                if (P.k_new && sr.p0 >= t0 && sr.p0 < t0 + TILE) {
+                if (AP && sr.p0 >= t0 && sr.p0 < t0 + TILE) {
                     // the tile of the call's own row: warp 0 writes the K record, warp 1 the V record
                     if (warp < 2) {
                         const float* src = (warp ? P.v_new : P.k_new) + ((size_t)pc.i * P.Hkv + pc.kvh) * HD;
