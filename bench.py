@@ -695,7 +695,7 @@ def bench_seq_split(torch, dist, AttnEngine, G_B, bd, local, rank, world, reps: 
     fill_positions(torch, eng, kvk, kvv, 2000, sh.start, sh.end, local_start=sh.start)
     q = seeded_q(torch, dev, 2999, (1, g.n_head, g.head_dim))
     out = torch.zeros_like(q)
-    res = {"tokens": n_total, "bytes": n_total * POS_BYTES, "exchange_bytes_per_rank": g.n_head * (g.head_dim + 2) * 4}
+    res = {"tokens": n_total, "bytes": n_total * POS_BYTES, "exchange_bytes_per_rank": g.n_head * (g.head_dim + 2) * 8}
     if world > 1:
         dec = bd.SeqSplitDecoder(eng, n_total, exchange="push")
         ms, _ = time_steps(torch, dist, world, lambda: dec.decode(out, q, kvk, kvv, n_total - 1, 1), reps)
@@ -709,7 +709,8 @@ def bench_seq_split(torch, dist, AttnEngine, G_B, bd, local, rank, world, reps: 
         ms_nccl, _ = time_steps(torch, dist, world, lambda: dec_n.decode(out_n, q, kvk, kvv, n_total - 1, 1), reps)
         res.update({"ms_per_step": ms, "ms_local_decode_only": ms_local, "ms_exchange_and_merge": max(0.0, ms - ms_local),
                     "ms_per_step_nccl_allgather": ms_nccl,
-                    "exchange": "push: peer stores + epoch flags from the merge epilogue, bounded acquire-spin, CUDA graph"})
+                    "exchange": "push: peer stores from the merge epilogue, every word paired with the step number (no fence, no "
+                                "flag), bounded spin on the words, CUDA graph"})
         nccl_vs_push = float((out_n.float() - out.float()).abs().max())
         dec.close()
     else:

@@ -390,10 +390,7 @@ int launch_prefill(battn_handle* h, void* out, const void* q, const uint8_t* kvk
 // device-side view of an exchange for one launch
 XchgView xchg_view(const battn_xchg* x, const int* epoch, int push, int wait) {
     XchgView v{};
-    for (int d = 0; d < x->world; ++d) {
-        v.rec[d] = reinterpret_cast<float*>(x->area[d]);
-        v.flag[d] = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(x->area[d]) + x->rec_bytes);
-    }
+    for (int d = 0; d < x->world; ++d) v.area[d] = reinterpret_cast<uint8_t*>(x->area[d]);
     v.world = x->world; v.rank = x->rank; v.max_items = x->max_items; v.epoch_ptr = epoch;
     v.wait_polls = x->wait_polls; v.push = push; v.wait = wait;
     return v;
@@ -832,13 +829,14 @@ int battn_xchg_create(battn_handle* h, int rank, int world, int max_rows, battn_
     if (!x) return BATTN_ERR_ARG;
     const Geom& g = h->g;
     x->h = h; x->world = world; x->rank = rank; x->max_items = max_rows * g.Hq;
-    x->rec_bytes = align_up((size_t)2 * world * x->max_items * (g.HD + 4) * sizeof(float), 256);
-    x->bytes = x->rec_bytes + align_up((size_t)world * x->max_items * sizeof(int), 256);
+    // [2 parities][world][items] records of HD + 2 words, every word paired with its step number (exact.cuh)
+    x->rec_bytes = align_up((size_t)2 * world * x->max_items * (g.HD + 2) * 8, 256);
+    x->bytes = x->rec_bytes;
     x->wait_polls = 1u << 17;                          // about 20 ms
     for (int d = 0; d < 8; ++d) { x->area[d] = nullptr; x->ipc_opened[d] = false; }
     cudaError_t e = cudaSetDevice(h->device);
     if (e == cudaSuccess) e = cudaMalloc(&x->area[rank], x->bytes);
-    if (e == cudaSuccess) e = cudaMemset(x->area[rank], 0, x->bytes);      // flags start below every epoch >= 1
+    if (e == cudaSuccess) e = cudaMemset(x->area[rank], 0, x->bytes);      // step numbers start below every epoch >= 1
     if (e == cudaSuccess && ipc_handle_out) {
         cudaIpcMemHandle_t ih;
         e = cudaIpcGetMemHandle(&ih, x->area[rank]);

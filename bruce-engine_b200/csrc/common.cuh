@@ -52,7 +52,7 @@ struct battn_handle {
 struct battn_xchg {
     battn_handle* h;
     int world, rank, max_items;
-    size_t rec_bytes, bytes;          // records, then flags
+    size_t rec_bytes, bytes;          // the receive area: records whose words carry their step number
     void* area[8];                    // area[d]: device d's receive area as mapped into this process
     bool ipc_opened[8];
     unsigned wait_polls;

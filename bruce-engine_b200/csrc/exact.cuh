@@ -110,87 +110,87 @@ __global__ void __launch_bounds__(256) k_attn_exact(const ExactParams P) {
 enum { MERGE_REGULAR = 0, MERGE_GATHERED = 1 };
 
 // Exchange of split records between the devices that hold the position shards of ONE sequence.
-// Every device owns a receive area, mapped into all peers: records [2 parities][world][max_items][HD + 4] floats
-// (o[HD], m in log2 units, l, pad) followed by flags [world][max_items] ints.  Device `rank` pushes its merged
-// record of item (row, head) for step `epoch` into slot [epoch & 1][rank][item] of EVERY device (its own included)
-// with plain stores, fences them system-wide, and then stores `epoch` into flag [rank][item] there.  A reader
-// polls its local flags until they reach its epoch.  Two record buffers suffice: a device cannot push step e + 2
-// before its own merge of step e + 1 completed, which needed every peer's push of e + 1, which those peers issue
-// after their merge of step e.
+// Every device owns a receive area, mapped into all peers: records [2 parities][world][max_items], a record being
+// HD + 2 payload words (o[HD], m in log2 units, l) EACH PAIRED WITH THE STEP NUMBER: 16-byte units
+// {word, step, word, step}.  Device `rank` pushes its merged record of item (row, head) for step `epoch` into slot
+// [epoch & 1][rank][item] of EVERY device (its own included) with plain 16-byte stores and nothing else: no fence and
+// no separate flag.  A reader polls the units it needs until their step numbers have reached its epoch -- an 8-byte
+// half of a unit arrives whole, so a word that carries the step's number is the step's word (the low-latency
+// protocol of collective libraries for small messages).  One trip over the link instead of store, fence round trip
+// and flag store.  Two record buffers suffice: a device cannot push step e + 2 before its own merge of step e + 1
+// completed, which needed every peer's push of e + 1, which those peers issue after their merge of step e.
 constexpr int XCHG_MAX_WORLD = 8;
 struct XchgView {
-    float* rec[XCHG_MAX_WORLD];     // receive area of device d as mapped HERE (rec[rank] is the local one), or null
-    int* flag[XCHG_MAX_WORLD];
+    uint8_t* area[XCHG_MAX_WORLD];  // receive area of device d as mapped HERE (area[rank] is the local one), or null
     int world, rank, max_items;
     const int* epoch_ptr;           // device-resident step number, advanced by the decode kernel of the same call
-    unsigned wait_polls;            // bound of the acquire-spin (polls of ~100 ns)
+    unsigned wait_polls;            // bound of the spin (polls of ~100 ns)
     int push, wait;                 // which halves of the exchange this launch performs
 };
 
-__device__ __forceinline__ int ld_acquire_sys(const int* p) {
-    int v;
-    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+template <int HD>
+__host__ __device__ constexpr size_t xchg_record_bytes() { return (size_t)(HD + 2) * 8; }
+
+__device__ __forceinline__ void st_unit(uint8_t* p, float a, float b, int epoch) {
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %2};" ::"l"(p), "r"(__float_as_uint(a)), "r"(epoch),
+                 "r"(__float_as_uint(b)) : "memory");
+}
+__device__ __forceinline__ uint4 ld_unit(const uint8_t* p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
     return v;
 }
-__device__ __forceinline__ void st_release_sys(int* p, int v) {
-    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ bool unit_ready(const uint4& v, int epoch) {
+    return (int)v.y - epoch >= 0 && (int)v.w - epoch >= 0;
 }
 
-// Waits (bounded) until every device's record of `item` for X.epoch has landed in the local receive area, then
-// merges them: called by the first HD/4 threads' block after a block-wide barrier.  Returns false on time-out.
-template <int HD, int NTHR>
-__device__ __forceinline__ bool xchg_wait(const XchgView& X, int epoch, int item, int* status) {
-    bool ok = true;
-    if (threadIdx.x < X.world) {
-        ok = false;
-        const int* f = X.flag[X.rank] + (size_t)threadIdx.x * X.max_items + item;
-        for (unsigned it = 0; it < X.wait_polls; ++it) {
-            if (ld_acquire_sys(f) - epoch >= 0) { ok = true; break; }
-            __nanosleep(100);
-        }
-    }
-    ok = __syncthreads_and(ok);
-    if (!ok && threadIdx.x == 0) atomicOr(status, BATTN_DEV_WAIT_TIMEOUT);
-    return ok;
-}
-
-// Merge of the `world` records of `item` in the local receive area; thread dq owns dims 4dq .. 4dq+3.
+// Pushes float4 `dq` of this device's record of `item` (and, with_ml, its (m, l)) into device `d`'s receive area.
 template <int HD>
-__device__ __forceinline__ void xchg_merge_store(const XchgView& X, int epoch, int item, int dq, void* out, int out_f16,
-                                                 size_t oi) {
-    constexpr int RS = HD + 4;
-    const float* base = X.rec[X.rank] + ((size_t)(epoch & 1) * X.world * X.max_items + item) * RS;
-    const size_t stride = (size_t)X.max_items * RS;
-    float4 o[XCHG_MAX_WORLD];
-    float2 ml[XCHG_MAX_WORLD];
-    float M = NEG_BIG;
-#pragma unroll
-    for (int r = 0; r < XCHG_MAX_WORLD; ++r)
-        if (r < X.world) {
-            o[r] = __ldcg(reinterpret_cast<const float4*>(base + r * stride + 4 * dq));
-            ml[r] = __ldcg(reinterpret_cast<const float2*>(base + r * stride + HD));
-            M = fmaxf(M, ml[r].x);
-        }
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    float L = 0.f;
-#pragma unroll
-    for (int r = 0; r < XCHG_MAX_WORLD; ++r)
-        if (r < X.world) {
-            const float w = fast_exp2(ml[r].x - M);
-            L = fmaf(ml[r].y, w, L);
-            acc.x = fmaf(o[r].x, w, acc.x); acc.y = fmaf(o[r].y, w, acc.y);
-            acc.z = fmaf(o[r].z, w, acc.z); acc.w = fmaf(o[r].w, w, acc.w);
-        }
-    const float il = L > 0.f ? 1.f / L : 0.f;
-    if (out_f16) {
-        const __half2 a = __floats2half2_rn(acc.x * il, acc.y * il), b = __floats2half2_rn(acc.z * il, acc.w * il);
-        *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(out) + oi) =
-            make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
-    } else {
-        *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + oi) =
-            make_float4(acc.x * il, acc.y * il, acc.z * il, acc.w * il);
-    }
+__device__ __forceinline__ void xchg_push(const XchgView& X, int epoch, int item, int d, int dq, const float4& o,
+                                          bool with_ml, float m, float l) {
+    uint8_t* dst = X.area[d] + (((size_t)(epoch & 1) * X.world + X.rank) * X.max_items + item) * xchg_record_bytes<HD>();
+    st_unit(dst + 32 * dq, o.x, o.y, epoch);
+    st_unit(dst + 32 * dq + 16, o.z, o.w, epoch);
+    if (with_ml) st_unit(dst + 8 * HD, m, l, epoch);
 }
+
+// Polls (bounded) the local receive area until float4 `dq` and (m, l) of device `r`'s record of `item` for the step
+// have landed, and returns them.  False when the wait ran out.
+template <int HD>
+__device__ __forceinline__ bool xchg_poll(const XchgView& X, int epoch, int item, int r, int dq, float4& o, float2& ml) {
+    const uint8_t* src = X.area[X.rank] + (((size_t)(epoch & 1) * X.world + r) * X.max_items + item) * xchg_record_bytes<HD>();
+    for (unsigned it = 0; it < X.wait_polls; ++it) {
+        const uint4 a = ld_unit(src + 32 * dq), b = ld_unit(src + 32 * dq + 16), c = ld_unit(src + 8 * HD);
+        if (unit_ready(a, epoch) && unit_ready(b, epoch) && unit_ready(c, epoch)) {
+            o = make_float4(__uint_as_float(a.x), __uint_as_float(a.z), __uint_as_float(b.x), __uint_as_float(b.z));
+            ml = make_float2(__uint_as_float(c.x), __uint_as_float(c.z));
+            return true;
+        }
+        __nanosleep(100);
+    }
+    return false;
+}
+
+// One step of the merge of the devices' records, in device order (both callers run exactly this sequence).
+struct XchgAcc {
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+    float L = 0.f;
+    __device__ __forceinline__ void add(const float4& o, float m, float l, float M) {
+        const float w = fast_exp2(m - M);
+        L = fmaf(l, w, L);
+        a.x = fmaf(o.x, w, a.x); a.y = fmaf(o.y, w, a.y); a.z = fmaf(o.z, w, a.z); a.w = fmaf(o.w, w, a.w);
+    }
+    __device__ __forceinline__ void store(void* out, int out_f16, size_t oi) const {
+        const float il = L > 0.f ? 1.f / L : 0.f;
+        if (out_f16) {
+            const __half2 x = __floats2half2_rn(a.x * il, a.y * il), y = __floats2half2_rn(a.z * il, a.w * il);
+            *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(out) + oi) =
+                make_uint2(*reinterpret_cast<const uint32_t*>(&x), *reinterpret_cast<const uint32_t*>(&y));
+        } else {
+            *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + oi) = make_float4(a.x * il, a.y * il, a.z * il, a.w * il);
+        }
+    }
+};
 
 struct MergeParams {
     int mode;              // k_merge only: MERGE_REGULAR or MERGE_GATHERED
@@ -425,40 +425,51 @@ __global__ void __launch_bounds__(MERGE_B_THREADS) k_merge_balanced(const MergeP
     const size_t obase = ((size_t)rowidx * P.Hq + hq) * HD;
     if (xq) {
         // ---- sequence split: push this device's record to every peer, then merge what the peers pushed ----
+        // Every lane of a warp holds the warp's float4(s) of the record: lane d sends them to device d, lane r then
+        // polls device r's record, and the merge over the devices runs on shuffled values in device order.
         const XchgView& X = P.xchg;
         const int xitem = rowidx * P.Hq + hq;
         const int epoch = *X.epoch_ptr;
-        // one warp pushes the whole record (one system-scope fence instead of one per warp)
-        __shared__ float4 s_push[HD / 4];
-        if (X.push) {
-            if (lane == 0) {
+        if (X.push && lane < X.world) {
 #pragma unroll
-                for (int j = 0; j < DPW; ++j) s_push[warp + NWARP * j] = acc[j];
-            }
-            __syncthreads();
-            if (warp == 0) {
-                const size_t slot = (((size_t)(epoch & 1) * X.world + X.rank) * X.max_items + xitem) * RS;
-#pragma unroll
-                for (int d = 0; d < XCHG_MAX_WORLD; ++d)
-                    if (d < X.world) {
-                        float* dst = X.rec[d] + slot;            // plain stores into the peer's memory
-                        for (int dq = lane; dq < HD / 4; dq += 32) *reinterpret_cast<float4*>(dst + 4 * dq) = s_push[dq];
-                        if (lane == 0) *reinterpret_cast<float2*>(dst + HD) = make_float2(M, L);
-                    }
-                __threadfence_system();
-            }
+            for (int j = 0; j < DPW; ++j)
+                xchg_push<HD>(X, epoch, xitem, lane, warp + NWARP * j, acc[j], warp == 0 && j == 0, M, L);
         }
-        __syncthreads();
-        if (X.push && tid < X.world)
-            st_release_sys(X.flag[tid] + (size_t)X.rank * X.max_items + xitem, epoch);
         if (!X.wait || !P.out) return;
-        if (!xchg_wait<HD, MERGE_B_THREADS>(X, epoch, xitem, P.status)) return;
-        if (lane == 0) {
+        bool ok = true;
+        float4 o[DPW];
+        float2 ml = make_float2(NEG_BIG, 0.f);
+#pragma unroll
+        for (int j = 0; j < DPW; ++j) o[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (lane < X.world) {
+#pragma unroll
+            for (int j = 0; j < DPW; ++j) ok = ok && xchg_poll<HD>(X, epoch, xitem, lane, warp + NWARP * j, o[j], ml);
+        }
+        ok = __syncthreads_and(ok);
+        if (!ok) {                                               // a peer's record never came: output untouched
+            if (tid == 0) atomicOr(P.status, BATTN_DEV_WAIT_TIMEOUT);
+            return;
+        }
+        float Mx = NEG_BIG;
+#pragma unroll
+        for (int r = 0; r < XCHG_MAX_WORLD; ++r) {
+            const float m = __shfl_sync(0xffffffffu, ml.x, r);
+            if (r < X.world) Mx = fmaxf(Mx, m);
+        }
+        XchgAcc xa[DPW];
+#pragma unroll
+        for (int r = 0; r < XCHG_MAX_WORLD; ++r) {
+            const float m = __shfl_sync(0xffffffffu, ml.x, r), l = __shfl_sync(0xffffffffu, ml.y, r);
 #pragma unroll
             for (int j = 0; j < DPW; ++j) {
-                const int dq = warp + NWARP * j;
-                xchg_merge_store<HD>(X, epoch, xitem, dq, P.out, P.out_f16, obase + 4 * dq);
+                const float4 v = make_float4(__shfl_sync(0xffffffffu, o[j].x, r), __shfl_sync(0xffffffffu, o[j].y, r),
+                                             __shfl_sync(0xffffffffu, o[j].z, r), __shfl_sync(0xffffffffu, o[j].w, r));
+                if (r < X.world) xa[j].add(v, m, l, Mx);
             }
+        }
+        if (lane == 0) {
+#pragma unroll
+            for (int j = 0; j < DPW; ++j) xa[j].store(P.out, P.out_f16, obase + 4 * (warp + NWARP * j));
         }
         return;
     }
@@ -496,11 +507,32 @@ template <int HD>
 __global__ void __launch_bounds__(HD / 4 < 32 ? 32 : HD / 4) k_merge_wait(const MergeParams P) {
     pdl_wait();
     pdl_trigger();
-    const int xitem = blockIdx.x;
-    const int epoch = *P.xchg.epoch_ptr;
-    if (!xchg_wait<HD, HD / 4>(P.xchg, epoch, xitem, P.status)) return;
-    if ((int)threadIdx.x < HD / 4)
-        xchg_merge_store<HD>(P.xchg, epoch, xitem, threadIdx.x, P.out, P.out_f16, (size_t)xitem * HD + 4 * threadIdx.x);
+    const XchgView& X = P.xchg;
+    const int xitem = blockIdx.x, dq = threadIdx.x;
+    const int epoch = *X.epoch_ptr;
+    float4 o[XCHG_MAX_WORLD];
+    float2 ml[XCHG_MAX_WORLD];
+    bool ok = true;
+    float M = NEG_BIG;
+    if (dq < HD / 4) {
+#pragma unroll
+        for (int r = 0; r < XCHG_MAX_WORLD; ++r)
+            if (r < X.world) {
+                ok = ok && xchg_poll<HD>(X, epoch, xitem, r, dq, o[r], ml[r]);
+                M = fmaxf(M, ml[r].x);
+            }
+    }
+    ok = __syncthreads_and(ok);
+    if (!ok) {
+        if (threadIdx.x == 0) atomicOr(P.status, BATTN_DEV_WAIT_TIMEOUT);
+        return;
+    }
+    if (dq >= HD / 4) return;
+    XchgAcc xa;
+#pragma unroll
+    for (int r = 0; r < XCHG_MAX_WORLD; ++r)
+        if (r < X.world) xa.add(o[r], ml[r].x, ml[r].y, M);
+    xa.store(P.out, P.out_f16, (size_t)xitem * HD + 4 * dq);
 }
 
 }  // namespace battn

@@ -112,11 +112,13 @@ def empty_records(rows: int, n_head: int, head_dim: int, device) -> torch.Tensor
 
 class HostExchange:
     """Host-side model of the device exchange of split records (battn_partials_push / battn_merge_wait): the same
-    receive slots, the same two record buffers selected by the step's parity, the same epoch flags with the
-    "flag >= step" rule, the same bounded wait.  The ranks' memory is a key-value store they share (any
-    torch.distributed Store); records are numpy arrays [rows][n_head][head_dim + 2] with m in natural-log units.
-    It exists to test the protocol -- stale flags, a dropped push, a rank that sits a step out -- among CPU ranks; the
-    data path on GPUs is the kernel."""
+    receive slots, the same two record buffers selected by the step's parity, the same rule that a record is the
+    step's record when the step number stored WITH it has reached the step ("number >= step"; on the device every
+    8-byte word of a record carries the number, here the record as a whole does), the same bounded wait.  The ranks'
+    memory is a key-value store they share (any torch.distributed Store); records are numpy arrays
+    [rows][n_head][head_dim + 2] with m in natural-log units.
+    It exists to test the protocol -- stale records, a dropped push, a rank that sits a step out -- among CPU ranks;
+    the data path on GPUs is the kernel."""
 
     TIMEOUT = object()
 
@@ -124,20 +126,20 @@ class HostExchange:
         self.store, self.rank, self.world = store, rank, world
         self.wait_s, self.poll_s = wait_s, poll_s
         self.epoch = 0
-        for src in range(world):                       # this rank's receive area starts with flags below every step
-            store.set(f"flag/{rank}/{src}", "0")
+        for src in range(world):                       # this rank's receive area starts with numbers below every step
+            for parity in (0, 1):
+                store.set(f"rec/{rank}/{parity}/{src}", (0).to_bytes(4, "little", signed=True))
 
     def push(self, rec, advance: int = 1, drop_to=()):
-        """Advance the step counter and store this rank's record of the step in every rank's receive slot, then the
-        flag.  `drop_to`: destinations whose copy is lost (a test's way of dropping a message)."""
+        """Advance the step counter and store this rank's record of the step, tagged with the step number, in every
+        rank's receive slot.  `drop_to`: destinations whose copy is lost (a test's way of dropping a message)."""
         import numpy as np
         self.epoch += advance
-        blob = np.ascontiguousarray(rec, dtype=np.float32).tobytes()
+        blob = self.epoch.to_bytes(4, "little", signed=True) + np.ascontiguousarray(rec, dtype=np.float32).tobytes()
         for dst in range(self.world):
             if dst in drop_to:
                 continue
-            self.store.set(f"rec/{dst}/{self.epoch & 1}/{self.rank}", blob)          # data first ...
-            self.store.set(f"flag/{dst}/{self.rank}", str(self.epoch))               # ... then the flag
+            self.store.set(f"rec/{dst}/{self.epoch & 1}/{self.rank}", blob)
 
     def wait_merge(self, shape):
         """Wait (bounded) until every rank's record of the current step has landed here, then merge.  Returns the
@@ -148,13 +150,16 @@ class HostExchange:
 
         from oracle import oracle as O
         deadline = time.monotonic() + self.wait_s
+        parts = []
         for src in range(self.world):
-            while int(self.store.get(f"flag/{self.rank}/{src}")) - self.epoch < 0:    # a later step also satisfies it
+            while True:
+                blob = self.store.get(f"rec/{self.rank}/{self.epoch & 1}/{src}")
+                if int.from_bytes(blob[:4], "little", signed=True) - self.epoch >= 0:
+                    break
                 if time.monotonic() > deadline:
                     return HostExchange.TIMEOUT
                 time.sleep(self.poll_s)
-        parts = [np.frombuffer(self.store.get(f"rec/{self.rank}/{self.epoch & 1}/{src}"), dtype=np.float32).reshape(shape)
-                 for src in range(self.world)]
+            parts.append(np.frombuffer(blob[4:], dtype=np.float32).reshape(shape))
         return O.merge(np.stack(parts))
 
 

@@ -330,8 +330,9 @@ int battn_attend_exact_paged(battn_handle* h, void* out, const void* q, const ba
  * Device r of `world` holds positions [r*N/world, (r+1)*N/world) of the sequence in its own cache, with LOCAL
  * positions.  A decode step runs the ordinary split-K decode on every shard; the epilogue of that kernel stores the
  * shard's merged record (o, m, l) of every (row, head) straight into a receive area on EVERY device of the group
- * (plain stores through peer-mapped pointers over NVLink, a system-scope fence, then an epoch flag), and then
- * waits -- bounded -- until the other devices' records of the same step have landed locally and merges them.
+ * (plain 16-byte stores through peer-mapped pointers over NVLink, every payload word paired with the step number:
+ * no fence and no separate flag), and then waits -- bounded -- until the words of the other devices' records carry
+ * the step's number locally and merges them.
  * No collective library call, no host round trip: one decode + one merge launch per step per device.
  *
  * battn_xchg_create allocates this device's receive area (cudaMalloc; call outside stream capture) and returns a

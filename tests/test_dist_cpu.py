@@ -106,7 +106,7 @@ def test_sequence_split_decode_over_gloo_ranks(world):
         assert np.abs(got - want).max() < 1e-5
 
 
-# ---- the exchange protocol of the sequence split (epoch flags, parity buffers, bounded wait) among CPU ranks ----------
+# ---- the exchange protocol of the sequence split (step numbers, parity buffers, bounded wait) among CPU ranks --------
 def _xchg_worker(rank, world, port, ret):
     """Four steps of a 3-rank group.  Step 2: the last rank sits out (its peers time out, it catches up with
     advance = 2).  Step 3: rank 0's push to rank 1 is dropped (only rank 1 times out).  Steps 1 and 4: everybody
@@ -138,7 +138,7 @@ def _xchg_worker(rank, world, port, ret):
     # step 1: ordinary
     x.push(record(1)); out = x.wait_merge((1, H, HD + 2)); log.append(out is not bd.HostExchange.TIMEOUT and np.allclose(out, want(1), atol=1e-6))
     barrier(1)
-    # step 2: the last rank sits out; the others find a STALE flag (step 1) from it and must not accept it
+    # step 2: the last rank sits out; the others find a STALE record (step 0 or 1) from it and must not accept it
     if rank != world - 1:
         x.push(record(2)); out = x.wait_merge((1, H, HD + 2)); log.append(out is bd.HostExchange.TIMEOUT)
     else:
@@ -149,7 +149,7 @@ def _xchg_worker(rank, world, port, ret):
     x.push(record(3), advance=adv, drop_to=(1,) if rank == 0 else ())
     out = x.wait_merge((1, H, HD + 2))
     if rank == 1:
-        log.append(out is bd.HostExchange.TIMEOUT)              # sees rank 0's flag of step 2 only
+        log.append(out is bd.HostExchange.TIMEOUT)              # sees rank 0's record of step 1 only
     else:
         log.append(out is not bd.HostExchange.TIMEOUT and np.allclose(out, want(3), atol=1e-6))
     barrier(3)
