@@ -4,7 +4,8 @@ Two copies of the same cache are stepped side by side with the same seeded rows:
 battn_decode (both pinned to the CPU oracle by the other tests), one by battn_decode_append.  After every step the
 outputs must be equal bit for bit, and at the end so must every byte of the two caches.  Covered: both geometries,
 full-causal and sliding-window layers (the ring wraps inside the run), ragged multi-slot batches with idle rows, an
-empty sequence (position 0), positions on both sides of a tile boundary, the paged cache, early KV streaming."""
+empty sequence (position 0), positions on both sides of a tile boundary, the paged cache, early KV streaming.  The
+last test pins the call to the CPU oracle directly, inside a CUDA graph replayed at advancing positions."""
 import numpy as np
 import pytest
 import torch
@@ -137,3 +138,77 @@ def test_decode_append_paged(name):
         assert torch.equal(_bits(oa), _bits(ob)), f"step {s}: outputs differ"
         lens = [n + int(a) for n, a in zip(lens, act_np)]
     assert torch.equal(pak, pbk) and torch.equal(pav, pbv)
+
+
+def test_decode_append_in_a_replayed_graph_against_the_oracle():
+    """The appending decode captured once and replayed at device-resident positions that advance on the device;
+    cache bytes and outputs of every replay against the CPU oracle (append, then attend)."""
+    from oracle import oracle as O
+    from tests.util import assert_close, oracle_geom
+    n_seq, steps = 4, 6
+    g = _geom("B", slot_ctx=512, window=64, n_slots=n_seq)
+    eng, og = _engine(g, True), oracle_geom(g)
+    dev = eng.device
+    rng = np.random.default_rng(23)
+    start = np.array([130, 0, 255, 61], dtype=np.int32)           # ragged; the last one crosses the window edge
+    kslot = np.array([2, 0, 3, 1], dtype=np.int32)
+    act = np.array([1, 1, 0, 1], dtype=np.int32)
+    layers = []
+    for is_swa in (False, True):
+        okvk, okvv = O.new_cache(og, is_swa), O.new_cache(og, is_swa)
+        for i in range(n_seq):
+            n0 = int(start[i])
+            if n0 and act[i]:
+                kh = rng.standard_normal((1, n0, g.n_kv, g.head_dim), dtype=np.float32)
+                vh = rng.standard_normal((1, n0, g.n_kv, g.head_dim), dtype=np.float32)
+                O.kv_append(og, kh, vh, okvk, okvv, [0], kslot=[kslot[i]], rows=n0, is_swa=is_swa)
+        layers.append(dict(is_swa=is_swa, okvk=okvk, okvv=okvv, kvk=torch.from_numpy(okvk).to(dev),
+                           kvv=torch.from_numpy(okvv).to(dev), out=new_out(eng, n_seq, g.n_head, g.head_dim),
+                           part=eng.alloc_part(n_seq, 1)))
+    q_in = torch.zeros((n_seq, g.n_head, g.head_dim), dtype=torch.float16, device=dev)
+    k_in = torch.zeros((n_seq, g.n_kv, g.head_dim), device=dev)
+    v_in = torch.zeros((n_seq, g.n_kv, g.head_dim), device=dev)
+    pos_d, slot_d, act_d = dev_i32(start, dev), dev_i32(kslot, dev), dev_i32(act, dev)
+
+    def step():
+        for L in layers:
+            eng.decode_append(L["out"], q_in, k_in, v_in, L["kvk"], L["kvv"], pos_d, L["part"], kslot=slot_d, act=act_d,
+                              is_swa=L["is_swa"])
+        pos_d.add_(act_d)
+
+    snap = [(L["kvk"].clone(), L["kvv"].clone()) for L in layers]
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        step()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step()
+    for L, (a, b) in zip(layers, snap):
+        L["kvk"].copy_(a)
+        L["kvv"].copy_(b)
+    pos_d.copy_(dev_i32(start, dev))
+    pos = start.copy()
+    for t in range(steps):
+        q = rng.standard_normal((n_seq, 1, g.n_head, g.head_dim), dtype=np.float32).astype(np.float16).astype(np.float32)
+        k = rng.standard_normal((n_seq, 1, g.n_kv, g.head_dim), dtype=np.float32)
+        v = rng.standard_normal((n_seq, 1, g.n_kv, g.head_dim), dtype=np.float32)
+        q_in.copy_(torch.from_numpy(q[:, 0]).to(dev))
+        k_in.copy_(torch.from_numpy(k[:, 0]).to(dev))
+        v_in.copy_(torch.from_numpy(v[:, 0]).to(dev))
+        graph.replay()
+        torch.cuda.synchronize()
+        for L in layers:
+            O.kv_append(og, k, v, L["okvk"], L["okvv"], pos, kslot=kslot, act=act, rows=1, is_swa=L["is_swa"])
+            assert (L["kvk"].cpu().numpy() == L["okvk"]).all() and (L["kvv"].cpu().numpy() == L["okvv"]).all(), \
+                f"cache bytes differ at step {t}"
+            want = O.attend(og, q, L["okvk"], L["okvv"], pos, kslot=kslot, act=act, rows=1, is_swa=L["is_swa"])
+            got = L["out"].float().cpu().numpy()
+            live = act.astype(bool)
+            assert_close(got[live], want[live][:, 0] if want.ndim == 4 else want[live],
+                         f"appending decode in a graph, step {t} swa={L['is_swa']}")
+        pos = pos + act
+        assert (pos_d.cpu().numpy() == pos).all()
+    assert eng.device_status() == 0
