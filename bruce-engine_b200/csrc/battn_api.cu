@@ -265,8 +265,10 @@ int launch_flash(battn_handle* h, void* out, float* rec_out, const void* q, cons
     if (pv) P.n_slots = pv->n_tables;
     // early KV streaming: only when the last launch on this handle wrote no cache rows but this call's own
     P.early = h->early_stream && (h->kvw_kind == 0 || (h->kvw_kind == 1 && h->kvw_pos == pos && h->kvw_nseq == n_seq &&
-                                                       h->kvw_rows == rows));
-    h->kvw_kind = 0;
+                                                       h->kvw_rows == rows) ||
+                                  (h->kvw_kind == 3 && h->kvw_cache != (const void*)kvk));
+    h->kvw_kind = k_new ? 3 : 0;
+    h->kvw_cache = kvk;
 
     cudaError_t e;
     int fd_grid = 0;                                   // grid of the flash-decode kernel, when that one runs
@@ -334,7 +336,8 @@ int launch_prefill(battn_handle* h, void* out, const void* q, const uint8_t* kvk
     if (pv) P.slot = table_row;
     // early KV streaming: only behind the append / prologue of exactly this chunk, or no cache write
     P.early = h->early_stream &&
-              (h->kvw_kind == 0 || (h->kvw_kind == 1 && h->kvw_pos == pos && h->kvw_nseq == 1 && h->kvw_rows == rows));
+              (h->kvw_kind == 0 || (h->kvw_kind == 1 && h->kvw_pos == pos && h->kvw_nseq == 1 && h->kvw_rows == rows) ||
+               (h->kvw_kind == 3 && h->kvw_cache != (const void*)kvk));
     h->kvw_kind = 0;
     const int MR = 128 / g.G;
     P.nsplit = prefill_splits(h, rows, is_swa);
@@ -441,7 +444,7 @@ int battn_init(const battn_geom* geom, int device, battn_handle** out_handle) {
     g = g0;
     h->device = device; h->last_cuda_error = 0; h->launches = 0; h->d_status = nullptr;
     h->prof_ev = nullptr; h->prof_cap = 0; h->prof_n = 0;
-    h->early_stream = 0; h->kvw_kind = 0; h->kvw_nseq = 0; h->kvw_rows = 0; h->kvw_pos = nullptr;
+    h->early_stream = 0; h->kvw_kind = 0; h->kvw_nseq = 0; h->kvw_rows = 0; h->kvw_pos = nullptr; h->kvw_cache = nullptr;
 
     cudaError_t e = cudaSetDevice(device);
     cudaDeviceProp prop;

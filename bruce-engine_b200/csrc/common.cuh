@@ -42,10 +42,13 @@ struct battn_handle {
     int fd_smem[3];
     // Early KV streaming of the decode kernels (see fd::Params::early): allowed for a call when the last launch on
     // this handle wrote no cache rows other than the call's own (kvw_kind 0: none, 1: rows_per_seq rows at kvw_pos of
-    // n_seq sequences, 2: anything else).
+    // n_seq sequences, 2: anything else, 3: the appending decode call wrote one row per sequence into kvw_cache -- its
+    // merge releases the next launch before that decode kernel has finished, so the next call streams early only
+    // from a different cache).
     int early_stream;
     int kvw_kind, kvw_nseq, kvw_rows;
     const int* kvw_pos;
+    const void* kvw_cache;
 };
 
 // Receive area of one device in a sequence split (see XchgView in exact.cuh) and its mappings of the peers' areas.

@@ -171,7 +171,9 @@ int battn_decode(battn_handle* h, void* out, const void* q, const uint8_t* kvk, 
  * append kernel's own quantiser, so the cache bytes are those battn_kv_append writes -- into that tile in shared memory
  * and into the cache, before the tile is used.  Saves the append launch and the kernel boundary between it and the
  * attention kernel (about 2.7 us per call).  For hosts that keep their own prologue kernel; hosts that use
- * battn_qkv_prep (prologue and append fused) call battn_decode after it as before. */
+ * battn_qkv_prep (prologue and append fused) call battn_decode after it as before.
+ * With early KV streaming on, the call that follows streams early only from a different cache (kvk pointer, or
+ * pool): the merge of this call releases its successor before the decode kernel that wrote the row has finished. */
 int battn_decode_append(battn_handle* h, void* out, const void* q, const float* k, const float* v, uint8_t* kvk,
                         uint8_t* kvv, const int* pos, const int* kslot, const int* act, void* ws, int n_seq, int is_swa,
                         void* stream);

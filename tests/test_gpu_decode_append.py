@@ -212,3 +212,34 @@ def test_decode_append_in_a_replayed_graph_against_the_oracle():
         pos = pos + act
         assert (pos_d.cpu().numpy() == pos).all()
     assert eng.device_status() == 0
+
+
+@pytest.mark.parametrize("name", ["B32", "R"])
+def test_consecutive_appending_decodes_on_one_cache_without_a_sync(name):
+    """Forty appending decode calls on the SAME cache queued back to back with early KV streaming on, across several
+    tile boundaries: the merge of call n releases call n + 1 before the decode kernel of call n (which writes the
+    row call n + 1 reads) has finished, so the library must not let call n + 1 stream that cache early."""
+    g = _geom(name, slot_ctx=1024, n_slots=1)
+    eng = _engine(g, True)
+    dev = eng.device
+    n0, steps = 100, 40
+    ka, va = eng.alloc_kv_layer(False, fill=0x7F)
+    _, k, v = draw_qkv(g, n0, 1, 9)
+    gpu_fill(eng, k, v, ka, va, False)
+    kb, vb = ka.clone(), va.clone()
+    part = eng.alloc_part(1, 1)
+    q, k, v = draw_qkv(g, steps, 1, 77, n_seq=steps, q_f16=(g.q_dtype == 1))
+    qd, kd, vd = dev_q(eng, q[:, 0]), torch.from_numpy(k).to(dev), torch.from_numpy(v).to(dev)
+    pos = [dev_i32([n0 + s], dev) for s in range(steps)]
+    oa = new_out(eng, steps, g.n_head, g.head_dim)
+    ob = new_out(eng, steps, g.n_head, g.head_dim)
+    torch.cuda.synchronize()
+    for s in range(steps):
+        eng.decode_append(ob[s:s + 1], qd[s:s + 1], kd[s:s + 1], vd[s:s + 1], kb, vb, pos[s], part)
+    for s in range(steps):
+        eng.qkv_prep_store(kd[s:s + 1], vd[s:s + 1], ka, va, pos[s])
+        eng.launch_attn_m(oa[s:s + 1], qd[s:s + 1], ka, va, pos[s], part, 1)
+    torch.cuda.synchronize()
+    assert eng.device_status() == 0
+    assert torch.equal(_bits(oa), _bits(ob))
+    assert torch.equal(ka, kb) and torch.equal(va, vb)
