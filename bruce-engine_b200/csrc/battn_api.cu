@@ -266,7 +266,7 @@ int launch_flash(battn_handle* h, void* out, float* rec_out, const void* q, cons
     // early KV streaming: only when the last launch on this handle wrote no cache rows but this call's own
     P.early = h->early_stream && (h->kvw_kind == 0 || (h->kvw_kind == 1 && h->kvw_pos == pos && h->kvw_nseq == n_seq &&
                                                        h->kvw_rows == rows) ||
-                                  (h->kvw_kind == 3 && h->kvw_cache != (const void*)kvk));
+                                  (h->kvw_kind == 3 && (RG <= 16 || h->kvw_cache != (const void*)kvk)));
     h->kvw_kind = k_new ? 3 : 0;
     h->kvw_cache = kvk;
 

@@ -43,8 +43,8 @@ struct battn_handle {
     // Early KV streaming of the decode kernels (see fd::Params::early): allowed for a call when the last launch on
     // this handle wrote no cache rows other than the call's own (kvw_kind 0: none, 1: rows_per_seq rows at kvw_pos of
     // n_seq sequences, 2: anything else, 3: the appending decode call wrote one row per sequence into kvw_cache -- its
-    // merge releases the next launch before that decode kernel has finished, so the next call streams early only
-    // from a different cache).
+    // merge releases the next launch before that decode kernel has finished; the flash-decode kernel never streams
+    // the tile of the row before its own early, the other kernels stream early only from a different cache).
     int early_stream;
     int kvw_kind, kvw_nseq, kvw_rows;
     const int* kvw_pos;

@@ -208,9 +208,11 @@ k_flash_decode(const Params P) {
                     const int s = cnt % STAGES, use = cnt / STAGES;
                     const int page = page_nx;
                     if (trow && t + 1 < pc.n) page_nx = trow[((tile0 + t + 1) * TILE) >> P.pg.shift];
-                    // early streaming stops at the tile that holds this step's own rows, and before the first stage
-                    // that needs the consumers (they do not start before the predecessor has finished)
-                    if (!waited && ((tile0 + t + 1) * TILE > sr.p0 || use > 0)) {
+                    // early streaming stops at the tile that holds the row BEFORE this step's own rows (the decode
+                    // kernel of a preceding appending call, which writes that row, may still be running: its merge
+                    // releases this launch before it waits), and before the first stage that needs the consumers
+                    // (they do not start before the predecessor has finished)
+                    if (!waited && ((tile0 + t + 1) * TILE >= sr.p0 || use > 0)) {
                         pdl_wait();
                         pdl_trigger();
                         waited = true;

@@ -172,8 +172,9 @@ int battn_decode(battn_handle* h, void* out, const void* q, const uint8_t* kvk, 
  * and into the cache, before the tile is used.  Saves the append launch and the kernel boundary between it and the
  * attention kernel (about 2.7 us per call).  For hosts that keep their own prologue kernel; hosts that use
  * battn_qkv_prep (prologue and append fused) call battn_decode after it as before.
- * With early KV streaming on, the call that follows streams early only from a different cache (kvk pointer, or
- * pool): the merge of this call releases its successor before the decode kernel that wrote the row has finished. */
+ * With early KV streaming on: the merge of this call releases its successor before the decode kernel that wrote
+ * the row has finished, so a decode call never streams the tile of the row before its own early, and a verify or
+ * prompt call that follows streams early only from a different cache (kvk pointer, or pool). */
 int battn_decode_append(battn_handle* h, void* out, const void* q, const float* k, const float* v, uint8_t* kvk,
                         uint8_t* kvv, const int* pos, const int* kslot, const int* act, void* ws, int n_seq, int is_swa,
                         void* stream);
