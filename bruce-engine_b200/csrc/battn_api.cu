@@ -260,6 +260,7 @@ int launch_flash(battn_handle* h, void* out, float* rec_out, const void* q, cons
     P.slot_ctx = g.slot_ctx; P.n_slots = g.n_slots; P.is_swa = is_swa; P.q_f16 = g.q_f16;
     P.scale_log2 = g.scale * LOG2E; P.status = h->d_status;
     P.epoch_ptr = epoch_ptr; P.epoch_advance = epoch_advance;
+    P.cph = 0;
     P.k_new = k_new; P.v_new = v_new; P.kvk_w = const_cast<uint8_t*>(kvk); P.kvv_w = const_cast<uint8_t*>(kvv);
     apply_paging(P, pv);
     if (pv) P.n_slots = pv->n_tables;
@@ -298,6 +299,7 @@ int launch_flash(battn_handle* h, void* out, float* rec_out, const void* q, cons
         if (per_sm < 1) per_sm = 1;
         const int grid = h->num_sms * per_sm;
         fd_grid = grid;
+        if (n_seq == 1 && grid >= g.Hkv) P.cph = grid / g.Hkv;     // one sequence: no share crosses a kv head
         ProfScope prof(h, st);
         if (g.HD == 128) e = idx == 0 ? launch_fd_kernel<128, 1>(P, grid, smem, st) : launch_fd_kernel<128, 2>(P, grid, smem, st);
         else             e = idx == 0 ? launch_fd_kernel<256, 1>(P, grid, smem, st) : launch_fd_kernel<256, 2>(P, grid, smem, st);
@@ -307,6 +309,7 @@ int launch_flash(battn_handle* h, void* out, float* rec_out, const void* q, cons
     M.mode = 0; M.part = P.part; M.out = out; M.rec_out = rec_out;
     M.n_rows = n_seq * rows; M.rows = rows; M.Hq = g.Hq; M.Hkv = g.Hkv; M.G = g.G;
     M.count = 0; M.log2_domain = 1; M.out_f16 = g.out_f16; M.hdr = P.hdr; M.status = h->d_status;
+    M.cph = P.cph;
     if (P.early && fd_grid > 0 && n_seq == 1) {
         // the merge recomputes the cut from the positions while it waits for the decode kernel
         M.pre_grid = fd_grid; M.pre_tile = fd::TILE;

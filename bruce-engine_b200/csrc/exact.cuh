@@ -212,6 +212,7 @@ struct MergeParams {
     // k_merge_balanced, single sequence behind an early-streaming decode kernel: the work cut is recomputed from the
     // positions before the wait (pre_grid CTAs, pre_tile keys per tile) instead of read from the header after it
     int pre_grid, pre_tile;
+    int cph;               // the decode kernel's cut: > 0: one sequence, cph CTAs per kv head; 0: linear
     // sequence split across devices (k_merge_balanced as the pushing epilogue, k_merge_wait): see XchgView
     XchgView xchg;
 };
@@ -343,7 +344,7 @@ __global__ void __launch_bounds__(MERGE_B_THREADS) k_merge_balanced(const MergeP
         // what the decode kernel derives from the same positions (flash_decode.cuh): one L2 round trip less behind the wait
         const SeqRange sr = seq_range(P.pos, P.kslot, P.act, 0, P.rows, P.is_swa, P.W, P.slot_ctx, P.n_slots, P.status);
         c1 = sr.active ? ((sr.hi + P.pre_tile - 1) / P.pre_tile - sr.lo / P.pre_tile) : 0;
-        per = max(1, (P.Hkv * c1 + P.pre_grid - 1) / P.pre_grid);
+        per = P.cph > 0 ? max(1, (c1 + P.cph - 1) / P.cph) : max(1, (P.Hkv * c1 + P.pre_grid - 1) / P.pre_grid);
     }
     pdl_wait();
     if (!pre) {
@@ -356,7 +357,9 @@ __global__ void __launch_bounds__(MERGE_B_THREADS) k_merge_balanced(const MergeP
     if (nt <= 0 && !xq) return;                                  // inactive sequence: no output
     const int item = i * P.Hkv + kvh;
     const long long t0 = (long long)P.Hkv * c0 + (long long)kvh * nt, t1 = t0 + nt;
-    const int clo = (int)(t0 / per), chi = (int)((t1 - 1) / per);
+    // the CTAs that hold pieces of this item: the decode kernel's cut (per-head groups of cph CTAs, or linear)
+    const int clo = P.cph > 0 ? kvh * P.cph : (int)(t0 / per);
+    const int chi = P.cph > 0 ? clo + (nt + per - 1) / per - 1 : (int)((t1 - 1) / per);
     const int RG = P.rows * P.G;
     // (an inactive shard of a split sequence contributes the empty record (0, -1e30, 0), bruce.cu:2319-2322)
     const int count = nt <= 0 ? 0 : min(chi - clo + 1, MERGE_MAX_COUNT);

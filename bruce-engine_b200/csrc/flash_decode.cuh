@@ -69,6 +69,7 @@ struct Params {
     // [n_seq][n_kv][head_dim].  The CTA whose share holds the tile of position pos[i] quantises the row of its kv head
     // into that tile in shared memory (the bulk copy brought the slot's old bytes) and into the cache, with the append
     // kernel's own quantiser, before the tile is used: no separate append launch in front of the attention call.
+    int cph;              // > 0: one sequence, cph CTAs per kv head (see the cut in k_flash_decode); 0: linear cut
     const float* k_new;
     const float* v_new;
     uint8_t* kvk_w;  // the caches again, writable
@@ -177,7 +178,11 @@ k_flash_decode(const Params P) {
         __syncthreads();
     }
     const int total = P.Hkv * cum[P.n_seq];
-    const int per = max(1, (total + (int)gridDim.x - 1) / (int)gridDim.x);
+    // One sequence (cph > 0): the CTAs are dealt to the kv heads in groups of cph and no share crosses a head -- a CTA
+    // whose share straddles two heads runs two pieces (Q staging, in-CTA merge and record twice) and is the last to
+    // finish.  Several sequences: one cut through the concatenated (sequence, head, tile) order.
+    const int per = P.cph > 0 ? max(1, (cum[1] + P.cph - 1) / P.cph)
+                              : max(1, (total + (int)gridDim.x - 1) / (int)gridDim.x);
     if (blockIdx.x == 0) {
         // the header and the step counter are read by the previous call's merge: written after the wait
         if (early) { pdl_wait(); pdl_trigger(); }
@@ -185,9 +190,18 @@ k_flash_decode(const Params P) {
         if (tid == 0) { P.hdr[0] = per; P.hdr[1] = total; }
         for (int i = tid; i <= P.n_seq; i += NTHREADS) P.hdr[2 + i] = cum[i];
     }
-    const long long g0l = (long long)blockIdx.x * per;
-    if (g0l >= total) return;                       // uniform for the whole CTA
-    const int g0 = (int)g0l, g1 = min(total, g0 + per);
+    int g0, g1;
+    if (P.cph > 0) {
+        const int nt = cum[1], kvh = blockIdx.x / P.cph, sh = blockIdx.x - kvh * P.cph;
+        if (kvh >= P.Hkv || sh * per >= nt) return;  // uniform for the whole CTA
+        g0 = kvh * nt + sh * per;
+        g1 = kvh * nt + min(nt, (sh + 1) * per);
+    } else {
+        const long long g0l = (long long)blockIdx.x * per;
+        if (g0l >= total) return;                   // uniform for the whole CTA
+        g0 = (int)g0l;
+        g1 = min(total, g0 + per);
+    }
 
     if (warp == NW) {
         // =========================== producer: one thread issues the bulk copies ===================
