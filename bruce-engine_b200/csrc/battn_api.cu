@@ -276,6 +276,7 @@ int launch_flash(battn_handle* h, void* out, float* rec_out, const void* q, cons
     if (RG > 16 && g.HD == 128 && g.W >= 64 && vt::smem_bytes(n_seq) <= SMEM_MAX) {
         // 5..8 rows at head_dim 128: the tensor-memory verify kernel, one CTA per SM (128-key tiles must not wrap the
         // ring, hence the window bound; very large batches exceed its shared memory and take the kernel below)
+        if (n_seq == 1 && h->num_sms >= g.Hkv) P.cph = h->num_sms / g.Hkv;
         ProfScope prof(h, st);
         e = launch_pdl(vt::k_verify_tc, dim3(h->num_sms), dim3(vt::NTHREADS), vt::smem_bytes(n_seq), st, P);
     } else if (RG > 16) {
@@ -286,6 +287,7 @@ int launch_flash(battn_handle* h, void* out, float* rec_out, const void* q, cons
         if (per_sm > h->vw_ctas_per_sm) per_sm = h->vw_ctas_per_sm;
         if (per_sm < 1) per_sm = 1;
         const int grid = h->num_sms * per_sm;
+        if (n_seq == 1 && grid >= g.Hkv) P.cph = grid / g.Hkv;
         ProfScope prof(h, st);
         e = g.HD == 128 ? launch_pdl(vw::k_verify_wide<128>, dim3(grid), dim3(vw::NTHREADS), smem, st, P)
                         : launch_pdl(vw::k_verify_wide<256>, dim3(grid), dim3(vw::NTHREADS), smem, st, P);

@@ -116,6 +116,31 @@ __device__ __forceinline__ Piece locate(int g, int g1, const int* cum, int n_seq
 }
 
 // AP: the decode call that appends its own row (a separate instance, so that the plain kernel carries none of it)
+// The share of CTA `cta` of `n_cta`: tiles [g0, g1) of the concatenated (sequence, kv head, tile) order, `per` tiles
+// per CTA; g0 == g1: no work.  One sequence (cph > 0): the CTAs are dealt to the kv heads in groups of cph and no share
+// crosses a head -- a CTA whose share straddles two heads runs two pieces (Q staging, in-CTA merge and record twice)
+// and is the last to finish.  Several sequences: one cut through the whole order.
+struct Share {
+    int per, g0, g1;
+};
+__device__ __forceinline__ Share cut_share(const int* cum, int n_seq, int Hkv, int cph, int cta, int n_cta) {
+    Share sh;
+    const int total = Hkv * cum[n_seq];
+    if (cph > 0) {
+        const int nt = cum[1], kvh = cta / cph, c = cta - kvh * cph;
+        sh.per = max(1, (nt + cph - 1) / cph);
+        const bool none = kvh >= Hkv || c * sh.per >= nt;
+        sh.g0 = none ? total : kvh * nt + c * sh.per;
+        sh.g1 = none ? total : kvh * nt + min(nt, (c + 1) * sh.per);
+    } else {
+        sh.per = max(1, (total + n_cta - 1) / n_cta);
+        const long long g0l = (long long)cta * sh.per;
+        sh.g0 = (int)(g0l < total ? g0l : total);
+        sh.g1 = min(total, sh.g0 + sh.per);
+    }
+    return sh;
+}
+
 template <int HD, int NT, bool AP = false>
 __global__ void __launch_bounds__(NTHREADS, (NT == 1 ? 3 : (NT == 2 ? 2 : 1)))
 k_flash_decode(const Params P) {
@@ -178,11 +203,8 @@ k_flash_decode(const Params P) {
         __syncthreads();
     }
     const int total = P.Hkv * cum[P.n_seq];
-    // One sequence (cph > 0): the CTAs are dealt to the kv heads in groups of cph and no share crosses a head -- a CTA
-    // whose share straddles two heads runs two pieces (Q staging, in-CTA merge and record twice) and is the last to
-    // finish.  Several sequences: one cut through the concatenated (sequence, head, tile) order.
-    const int per = P.cph > 0 ? max(1, (cum[1] + P.cph - 1) / P.cph)
-                              : max(1, (total + (int)gridDim.x - 1) / (int)gridDim.x);
+    const Share share = cut_share(cum, P.n_seq, P.Hkv, P.cph, (int)blockIdx.x, (int)gridDim.x);
+    const int per = share.per;
     if (blockIdx.x == 0) {
         // the header and the step counter are read by the previous call's merge: written after the wait
         if (early) { pdl_wait(); pdl_trigger(); }
@@ -190,18 +212,8 @@ k_flash_decode(const Params P) {
         if (tid == 0) { P.hdr[0] = per; P.hdr[1] = total; }
         for (int i = tid; i <= P.n_seq; i += NTHREADS) P.hdr[2 + i] = cum[i];
     }
-    int g0, g1;
-    if (P.cph > 0) {
-        const int nt = cum[1], kvh = blockIdx.x / P.cph, sh = blockIdx.x - kvh * P.cph;
-        if (kvh >= P.Hkv || sh * per >= nt) return;  // uniform for the whole CTA
-        g0 = kvh * nt + sh * per;
-        g1 = kvh * nt + min(nt, (sh + 1) * per);
-    } else {
-        const long long g0l = (long long)blockIdx.x * per;
-        if (g0l >= total) return;                   // uniform for the whole CTA
-        g0 = (int)g0l;
-        g1 = min(total, g0 + per);
-    }
+    const int g0 = share.g0, g1 = share.g1;
+    if (g0 >= g1) return;                           // uniform for the whole CTA
 
     if (warp == NW) {
         // =========================== producer: one thread issues the bulk copies ===================

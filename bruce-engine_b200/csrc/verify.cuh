@@ -98,14 +98,14 @@ __global__ void __launch_bounds__(NTHREADS, HD == 128 ? 3 : 1) k_verify_wide(con
     }
     __syncthreads();
     const int total = P.Hkv * cum[P.n_seq];
-    const int per = max(1, (total + (int)gridDim.x - 1) / (int)gridDim.x);
+    const fd::Share share = fd::cut_share(cum, P.n_seq, P.Hkv, P.cph, (int)blockIdx.x, (int)gridDim.x);
+    const int per = share.per;
     if (blockIdx.x == 0) {
         if (tid == 0) { P.hdr[0] = per; P.hdr[1] = total; }
         for (int i = tid; i <= P.n_seq; i += NTHREADS) P.hdr[2 + i] = cum[i];
     }
-    const long long g0l = (long long)blockIdx.x * per;
-    if (g0l >= total) return;
-    const int g0 = (int)g0l, g1 = min(total, g0 + per);
+    const int g0 = share.g0, g1 = share.g1;
+    if (g0 >= g1) return;
 
     if (warp == NW) {
         // =========================== producer ==========================================================

@@ -213,13 +213,13 @@ __global__ void __maxnreg__(REGS_LAUNCH) k_verify_tc(const fd::Params P) {
     __syncthreads();
     const uint32_t tmem = misc[0];
     const int total = P.Hkv * cum[P.n_seq];
-    const int per = max(1, (total + (int)gridDim.x - 1) / (int)gridDim.x);
+    const fd::Share share = fd::cut_share(cum, P.n_seq, P.Hkv, P.cph, (int)blockIdx.x, (int)gridDim.x);
+    const int per = share.per;
     if (blockIdx.x == 0) {
         if (tid == 0) { P.hdr[0] = per; P.hdr[1] = total; }
         for (int i = tid; i <= P.n_seq; i += NTHREADS) P.hdr[2 + i] = cum[i];
     }
-    const long long g0l = (long long)blockIdx.x * per;
-    const int g0 = (int)(g0l < total ? g0l : total), g1 = min(total, g0 + per);      // empty share: g0 == g1
+    const int g0 = share.g0, g1 = share.g1;                                          // empty share: g0 == g1
 
     // bounded wait that degrades to "do not wait" once any wait has run out
     auto wait = [&](int b, uint32_t parity, uint32_t sleep_ns) {
