@@ -48,7 +48,7 @@ METRIC = "decode-attn HBM TB/s (ctx sweep 8K-256K, full + window-4096 layer per 
 # DRAM bytes (read + write) of one flash-decode launch at 256K, from an ncu capture of the library revision named
 # beside it (dram__bytes_read.sum + dram__bytes_write.sum).  Reported as roofline.traffic only while the loaded
 # library still is that revision (battn_version()); a changed kernel needs a new capture.
-NCU_TRAFFIC_256K = {"lib_version": 3, "bytes": 570508544 + 4738304}
+NCU_TRAFFIC_256K = {"lib_version": 4, "bytes": 570502144 + 4255488}
 MIN_TIMED_S = 0.5                     # the K-step block is repeated until the timed region is at least this long
 
 

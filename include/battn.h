@@ -38,7 +38,7 @@
 extern "C" {
 #endif
 
-#define BATTN_VERSION 3
+#define BATTN_VERSION 4
 
 /* status codes */
 enum {

@@ -28,7 +28,7 @@ def test_library_builds_and_exports_every_declared_symbol():
     for n in names:
         assert hasattr(lib, n), f"{n} declared in battn.h but not exported"
     assert set(names) == set(capi.SIGNATURES), "ctypes binding and header disagree"
-    assert capi.load().battn_version() == 3
+    assert capi.load().battn_version() == 4
 
 
 def test_argument_errors_without_a_device():
