@@ -11,6 +11,7 @@
 // devices; k_merge_balanced merges the work-balanced records of the flash-decode kernels.
 #pragma once
 #include "common.cuh"
+#include "work_cut.h"
 
 namespace battn {
 
@@ -356,10 +357,9 @@ __global__ void __launch_bounds__(MERGE_B_THREADS) k_merge_balanced(const MergeP
     const bool xq = P.xchg.world > 0;                            // this launch feeds a cross-device exchange
     if (nt <= 0 && !xq) return;                                  // inactive sequence: no output
     const int item = i * P.Hkv + kvh;
-    const long long t0 = (long long)P.Hkv * c0 + (long long)kvh * nt, t1 = t0 + nt;
     // the CTAs that hold pieces of this item: the decode kernel's cut (per-head groups of cph CTAs, or linear)
-    const int clo = P.cph > 0 ? kvh * P.cph : (int)(t0 / per);
-    const int chi = P.cph > 0 ? clo + (nt + per - 1) / per - 1 : (int)((t1 - 1) / per);
+    int clo = 0, chi = -1;
+    if (nt > 0) fd::item_ctas(P.cph, per, P.Hkv, c0, nt, kvh, clo, chi);
     const int RG = P.rows * P.G;
     // (an inactive shard of a split sequence contributes the empty record (0, -1e30, 0), bruce.cu:2319-2322)
     const int count = nt <= 0 ? 0 : min(chi - clo + 1, MERGE_MAX_COUNT);

@@ -26,6 +26,7 @@
 #pragma once
 #include "common.cuh"
 #include "kv_append.cuh"
+#include "work_cut.h"
 
 namespace battn {
 namespace fd {
@@ -94,53 +95,7 @@ __host__ __device__ constexpr size_t smem_bytes(int RG, int n_seq) {
 
 __device__ __forceinline__ int perm16(int kappa) { return kappa ^ ((kappa >> 2) & 1); }
 
-struct Piece {
-    int i, kvh, tl, n;   // sequence, kv head, first tile (relative to the item), tiles in this piece
-};
-
-// The piece that starts at global tile index g (g < g1): every thread of the CTA computes the same.
-__device__ __forceinline__ Piece locate(int g, int g1, const int* cum, int n_seq, int Hkv) {
-    int lo = 0, hi = n_seq - 1;
-    while (lo < hi) {
-        const int mid = (lo + hi + 1) >> 1;
-        if (Hkv * cum[mid] <= g) lo = mid; else hi = mid - 1;
-    }
-    Piece pc;
-    pc.i = lo;
-    const int nt = cum[lo + 1] - cum[lo];
-    const int rem = g - Hkv * cum[lo];
-    pc.kvh = rem / nt;
-    pc.tl = rem - pc.kvh * nt;
-    pc.n = min(nt - pc.tl, g1 - g);
-    return pc;
-}
-
 // AP: the decode call that appends its own row (a separate instance, so that the plain kernel carries none of it)
-// The share of CTA `cta` of `n_cta`: tiles [g0, g1) of the concatenated (sequence, kv head, tile) order, `per` tiles
-// per CTA; g0 == g1: no work.  One sequence (cph > 0): the CTAs are dealt to the kv heads in groups of cph and no share
-// crosses a head -- a CTA whose share straddles two heads runs two pieces (Q staging, in-CTA merge and record twice)
-// and is the last to finish.  Several sequences: one cut through the whole order.
-struct Share {
-    int per, g0, g1;
-};
-__device__ __forceinline__ Share cut_share(const int* cum, int n_seq, int Hkv, int cph, int cta, int n_cta) {
-    Share sh;
-    const int total = Hkv * cum[n_seq];
-    if (cph > 0) {
-        const int nt = cum[1], kvh = cta / cph, c = cta - kvh * cph;
-        sh.per = max(1, (nt + cph - 1) / cph);
-        const bool none = kvh >= Hkv || c * sh.per >= nt;
-        sh.g0 = none ? total : kvh * nt + c * sh.per;
-        sh.g1 = none ? total : kvh * nt + min(nt, (c + 1) * sh.per);
-    } else {
-        sh.per = max(1, (total + n_cta - 1) / n_cta);
-        const long long g0l = (long long)cta * sh.per;
-        sh.g0 = (int)(g0l < total ? g0l : total);
-        sh.g1 = min(total, sh.g0 + sh.per);
-    }
-    return sh;
-}
-
 template <int HD, int NT, bool AP = false>
 __global__ void __launch_bounds__(NTHREADS, (NT == 1 ? 3 : (NT == 2 ? 2 : 1)))
 k_flash_decode(const Params P) {
