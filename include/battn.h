@@ -346,8 +346,8 @@ int battn_attend_exact_paged(battn_handle* h, void* out, const void* q, const ba
  *
  * battn_partials_push: arguments as battn_partials, minus `rec`.  `epoch` points to this device's step counter in
  * DEVICE memory (4 bytes the host allocates and zeroes once, together with the exchange object: the counter never goes
- * back while the object lives, stale records are told from fresh ones by it); the call adds `epoch_advance` to it on the device
- * before use -- 1 in the normal case, so that a captured graph replays at successive steps; 1 + k after this
+ * back while the object lives, stale records are told from fresh ones by it); the call adds `epoch_advance` to it on
+ * the device before use -- 1 in the normal case, so that a captured graph replays at successive steps; 1 + k after this
  * device sat out k steps of the group -- and the resulting step number must be the same on every device.  With
  * out != NULL the same launch also performs the wait-and-merge and writes the normalised output
  * [batch*rows][n_head][head_dim]; with out == NULL it only pushes and battn_merge_wait finishes the step later.
