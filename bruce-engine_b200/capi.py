@@ -51,6 +51,7 @@ SIGNATURES = {
     "battn_rope_tables": (_I, [_P] * 4 + [_I, _I, _P]),
     "battn_decode": (_I, [_P] * 9 + [_I, _I, _P]),
     "battn_decode_append": (_I, [_P] * 11 + [_I, _I, _P]),
+    "battn_qkv_decode": (_I, [_P] * 8 + [_I] + [_P] * 6 + [_I, _I, _P]),
     "battn_decode_noalloc": (_I, [_P] * 8 + [_I, _I, _P]),
     "battn_verify": (_I, [_P] * 9 + [_I, _I, _I, _P]),
     "battn_prefill": (_I, [_P] * 7 + [_I, _I, _P]),

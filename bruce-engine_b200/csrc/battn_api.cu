@@ -95,7 +95,9 @@ cudaError_t fd_prepare_all(battn_handle* h) {
     else           e = cudaFuncSetAttribute((const void*)pf::k_prefill<256, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, pf::Cfg<256, 64>::TOTAL);
     if (e != cudaSuccess) return e;
     if ((e = fd_prepare<HD, 1>(h, 0)) != cudaSuccess) return e;
-    if ((e = cudaFuncSetAttribute((const void*)fd::k_flash_decode<HD, 1, true>,
+    if ((e = cudaFuncSetAttribute((const void*)fd::k_flash_decode<HD, 1, 1>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute((const void*)fd::k_flash_decode<HD, 1, 2>,
                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX)) != cudaSuccess) return e;
     if ((e = fd_prepare<HD, 2>(h, 1)) != cudaSuccess) return e;
     return cudaSuccess;
@@ -234,10 +236,21 @@ int launch_exact(battn_handle* h, void* out, float* rec_out, const void* q, cons
     return e == cudaSuccess ? BATTN_OK : cuda_fail(h, e);
 }
 
+// inputs of the QKV prologue for the decode call that runs it itself
+struct PrologueIn {
+    const float* q_raw;
+    const float* sqk;
+    const float* cs;
+    const float* sn;
+    int table_off;
+};
+
 template <int HD, int NT>
 cudaError_t launch_fd_kernel(const fd::Params& P, int grid, size_t smem, cudaStream_t st) {
-    if constexpr (NT == 1)
-        if (P.k_new) return launch_pdl(fd::k_flash_decode<HD, 1, true>, dim3(grid), dim3(fd::NTHREADS), smem, st, P);
+    if constexpr (NT == 1) {
+        if (P.q_raw) return launch_pdl(fd::k_flash_decode<HD, 1, 2>, dim3(grid), dim3(fd::NTHREADS), smem, st, P);
+        if (P.k_new) return launch_pdl(fd::k_flash_decode<HD, 1, 1>, dim3(grid), dim3(fd::NTHREADS), smem, st, P);
+    }
     return launch_pdl(fd::k_flash_decode<HD, NT>, dim3(grid), dim3(fd::NTHREADS), smem, st, P);
 }
 
@@ -245,7 +258,8 @@ cudaError_t launch_fd_kernel(const fd::Params& P, int grid, size_t smem, cudaStr
 int launch_flash(battn_handle* h, void* out, float* rec_out, const void* q, const uint8_t* kvk, const uint8_t* kvv,
                  const int* pos, const int* kslot, const int* act, void* ws, int n_seq, int rows, int is_swa,
                  cudaStream_t st, const XchgView* xv = nullptr, int* epoch_ptr = nullptr, int epoch_advance = 0,
-                 const PagedView* pv = nullptr, const float* k_new = nullptr, const float* v_new = nullptr) {
+                 const PagedView* pv = nullptr, const float* k_new = nullptr, const float* v_new = nullptr,
+                 const PrologueIn* pro = nullptr) {
     const Geom& g = h->g;
     const int RG = rows * g.G;
     if (RG > 32) return BATTN_ERR_CAPACITY;
@@ -261,6 +275,8 @@ int launch_flash(battn_handle* h, void* out, float* rec_out, const void* q, cons
     P.scale_log2 = g.scale * LOG2E; P.status = h->d_status;
     P.epoch_ptr = epoch_ptr; P.epoch_advance = epoch_advance;
     P.cph = 0;
+    P.q_raw = pro ? pro->q_raw : nullptr; P.sqk = pro ? pro->sqk : nullptr; P.cs = pro ? pro->cs : nullptr;
+    P.sn = pro ? pro->sn : nullptr; P.table_off = pro ? pro->table_off : 0;
     P.k_new = k_new; P.v_new = v_new; P.kvk_w = const_cast<uint8_t*>(kvk); P.kvv_w = const_cast<uint8_t*>(kvv);
     apply_paging(P, pv);
     if (pv) P.n_slots = pv->n_tables;
@@ -637,6 +653,18 @@ int battn_decode_append(battn_handle* h, void* out, const void* q, const float* 
     if (!ws || ((uintptr_t)ws & 15) || !k || !v || ((((uintptr_t)k | (uintptr_t)v)) & 15)) return BATTN_ERR_ARG;
     return launch_flash(h, out, nullptr, q, kvk, kvv, pos, kslot, act, ws, n_seq, 1, is_swa, (cudaStream_t)stream, nullptr,
                         nullptr, 0, nullptr, k, v);
+}
+
+int battn_qkv_decode(battn_handle* h, void* out, const float* q, const float* k, const float* v, const float* sqk,
+                     const float* cs, const float* sn, int theta_sel, uint8_t* kvk, uint8_t* kvv, const int* pos,
+                     const int* kslot, const int* act, void* ws, int n_seq, int is_swa, void* stream) {
+    const int rc = check_seq_args(h, out, q, kvk, kvv, pos, kslot, n_seq, 1, 1);
+    if (rc) return rc;
+    if (!ws || ((uintptr_t)ws & 15) || !k || !v || !sqk || !cs || !sn || (theta_sel != 1 && theta_sel != 2)) return BATTN_ERR_ARG;
+    if ((((uintptr_t)k | (uintptr_t)v | (uintptr_t)sqk | (uintptr_t)cs | (uintptr_t)sn) & 15) != 0) return BATTN_ERR_ARG;
+    PrologueIn pro{q, sqk, cs, sn, theta_sel == 2 ? h->g.HD / 2 : 0};
+    return launch_flash(h, out, nullptr, q, kvk, kvv, pos, kslot, act, ws, n_seq, 1, is_swa, (cudaStream_t)stream, nullptr,
+                        nullptr, 0, nullptr, k, v, &pro);
 }
 
 int battn_decode_noalloc(battn_handle* h, void* out, const void* q, const uint8_t* kvk, const uint8_t* kvv,

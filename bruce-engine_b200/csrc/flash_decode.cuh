@@ -26,6 +26,7 @@
 #pragma once
 #include "common.cuh"
 #include "kv_append.cuh"
+#include "qkv_prep.cuh"
 #include "work_cut.h"
 
 namespace battn {
@@ -71,6 +72,13 @@ struct Params {
     // into that tile in shared memory (the bulk copy brought the slot's old bytes) and into the cache, with the append
     // kernel's own quantiser, before the tile is used: no separate append launch in front of the attention call.
     int cph;              // > 0: one sequence, cph CTAs per kv head (see the cut in k_flash_decode); 0: linear cut
+    // AP == 2, the decode call that runs the whole QKV prologue itself: raw q [n_seq][Hq][HD], sqk [Hq][HD], the rows'
+    // RoPE tables cs / sn [n_seq][HD] (table_off selects the theta), and k_new / v_new are the RAW k and v rows
+    const float* q_raw;
+    const float* sqk;
+    const float* cs;
+    const float* sn;
+    int table_off;
     const float* k_new;
     const float* v_new;
     uint8_t* kvk_w;  // the caches again, writable
@@ -95,8 +103,9 @@ __host__ __device__ constexpr size_t smem_bytes(int RG, int n_seq) {
 
 __device__ __forceinline__ int perm16(int kappa) { return kappa ^ ((kappa >> 2) & 1); }
 
-// AP: the decode call that appends its own row (a separate instance, so that the plain kernel carries none of it)
-template <int HD, int NT, bool AP = false>
+// AP: 1 = the decode call that appends its own (prepared) row, 2 = the one that also runs the QKV prologue of its row
+// (separate instances, so that the plain kernel carries none of it)
+template <int HD, int NT, int AP = 0>
 __global__ void __launch_bounds__(NTHREADS, (NT == 1 ? 3 : (NT == 2 ? 2 : 1)))
 k_flash_decode(const Params P) {
     using C = Cfg<HD>;
@@ -241,6 +250,32 @@ k_flash_decode(const Params P) {
 
             named_bar_sync(1, NW * 32);            // previous piece finished with qs / mbuf
             // ---- stage Q of this item as fp16 [pair][HD]; pair = row * G + head-in-group ----------
+            if constexpr (AP == 2) {
+                // the prologue of this item's query heads, one warp per head, with the prologue kernel's arithmetic
+                // (qkv_prep.cuh); the fp16 rounding is the one battn_qkv_prep (fp16 q) or the staging below (fp32 q) applies
+                constexpr int VEC = HD / 64, H2 = HD / 2;
+                float c[VEC], s_[VEC];
+                prep::tables<HD>(P.cs + (size_t)pc.i * HD + P.table_off, P.sn + (size_t)pc.i * HD + P.table_off, lane, c, s_);
+                for (int n = warp; n < NT * 8; n += NW) {
+                    __half* row = qs + n * QSTR;
+                    if (n < RG) {
+                        const int hq = pc.kvh * P.G + n;             // rows == 1: pair n is head n of the group
+                        float lo[VEC], hi[VEC];
+                        prep::q_head<HD>(P.q_raw + ((size_t)pc.i * P.Hq + hq) * HD, P.sqk + (size_t)hq * HD, c, s_, lane, lo, hi);
+#pragma unroll
+                        for (int j = 0; j < VEC; j += 2) {
+                            *reinterpret_cast<__half2*>(row + VEC * lane + j) = __floats2half2_rn(lo[j], lo[j + 1]);
+                            *reinterpret_cast<__half2*>(row + H2 + VEC * lane + j) = __floats2half2_rn(hi[j], hi[j + 1]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < VEC; j += 2) {
+                            *reinterpret_cast<__half2*>(row + VEC * lane + j) = __floats2half2_rn(0.f, 0.f);
+                            *reinterpret_cast<__half2*>(row + H2 + VEC * lane + j) = __floats2half2_rn(0.f, 0.f);
+                        }
+                    }
+                }
+            } else
             for (int idx = ctid; idx < NT * 8 * (HD / 8); idx += NW * 32) {
                 const int n = idx / (HD / 8), ch = idx - n * (HD / 8);
                 uint4 val = make_uint4(0u, 0u, 0u, 0u);
@@ -301,9 +336,28 @@ k_flash_decode(const Params P) {
                     if (warp < 2) {
                         const float* src = (warp ? P.v_new : P.k_new) + ((size_t)pc.i * P.Hkv + pc.kvh) * HD;
                         uint8_t* tile = stages + (size_t)s * 2 * TILE_BYTES + (warp ? TILE_BYTES : 0);
-                        quantise_record<HD>(src, tile + (sr.p0 - t0) * REC, lane);
                         const size_t ri = kv_rec_index(P.pg, sr.slot, pc.kvh, P.Hkv, P.pstride, sr.p0 & P.ring_mask, P.status);
-                        quantise_record<HD>(src, (warp ? P.kvv_w : P.kvk_w) + ri * (size_t)REC, lane);
+                        uint8_t* rec_t = tile + (sr.p0 - t0) * REC;
+                        uint8_t* rec_c = (warp ? P.kvv_w : P.kvk_w) + ri * (size_t)REC;
+                        if constexpr (AP == 2) {
+                            // raw rows: k is scaled and rotated first, v is quantised as it is (qkv_prep.cuh)
+                            constexpr int VEC = HD / 64, H2 = HD / 2;
+                            float x0[VEC], x1[VEC];
+                            if (warp == 0) {
+                                float c[VEC], s_[VEC];
+                                prep::tables<HD>(P.cs + (size_t)pc.i * HD + P.table_off, P.sn + (size_t)pc.i * HD + P.table_off,
+                                                 lane, c, s_);
+                                prep::k_head<HD>(src, c, s_, lane, x0, x1);
+                            } else {
+                                prep::load<VEC>(src + VEC * lane, x0);
+                                prep::load<VEC>(src + H2 + VEC * lane, x1);
+                            }
+                            prep::quant_head<HD>(rec_t, x0, x1, lane);
+                            prep::quant_head<HD>(rec_c, x0, x1, lane);
+                        } else {
+                            quantise_record<HD>(src, rec_t, lane);
+                            quantise_record<HD>(src, rec_c, lane);
+                        }
                         // the stage is refilled by a bulk copy later: order these generic-proxy writes before it
                         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     }

@@ -155,6 +155,15 @@ class AttnEngine:
                                           _ptr(kslot), _ptr(act), _ptr(part), pos.numel(), int(is_swa), self._stream())
         self._check("battn_decode_append", rc)
 
+    def qkv_decode(self, out, q, k, v, sqk, cs, sn, kvk, kvv, pos, part, kslot=None, act=None, is_swa: bool = False,
+                   theta_sel: int = 1):
+        """One row per sequence: the QKV prologue (as qkv_prep), the append and the attention in one call whose decode
+        kernel does all three (battn_qkv_decode); q, k, v are the raw fp32 rows."""
+        rc = self.lib.battn_qkv_decode(self.h, _ptr(out), _ptr(q), _ptr(k), _ptr(v), _ptr(sqk), _ptr(cs), _ptr(sn),
+                                       int(theta_sel), _ptr(kvk), _ptr(kvv), _ptr(pos), _ptr(kslot), _ptr(act),
+                                       _ptr(part), pos.numel(), int(is_swa), self._stream())
+        self._check("battn_qkv_decode", rc)
+
     def decode_append_paged(self, out, q, k, v, pages, pos, part, ktab=None, act=None):
         rc = self.lib.battn_decode_append_paged(self.h, _ptr(out), _ptr(q), _ptr(k), _ptr(v), C.byref(pages), _ptr(pos),
                                                 _ptr(ktab), _ptr(act), _ptr(part), pos.numel(), self._stream())

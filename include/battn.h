@@ -179,6 +179,16 @@ int battn_decode_append(battn_handle* h, void* out, const void* q, const float* 
                         uint8_t* kvv, const int* pos, const int* kslot, const int* act, void* ws, int n_seq, int is_swa,
                         void* stream);
 
+/* Decode that runs the QKV prologue of its row itself: battn_qkv_prep (one row per sequence) and battn_decode in ONE
+ * launch pair.  q, k, v, sqk, cs, sn, theta_sel: the RAW inputs, exactly as for battn_qkv_prep.  Every CTA of the decode
+ * kernel prepares the query heads it needs (L2 scale, RoPE, sqk; rounded to fp16 as the attention kernels take them), the
+ * CTA that streams the tile of position pos[i] prepares and quantises the K row and quantises the V row of its kv head:
+ * the same device functions as the prologue kernel, so cache bytes and output bits are those of battn_qkv_prep followed
+ * by battn_decode.  The prepared q is not written anywhere.  Same rule for early KV streaming as battn_decode_append. */
+int battn_qkv_decode(battn_handle* h, void* out, const float* q, const float* k, const float* v, const float* sqk,
+                     const float* cs, const float* sn, int theta_sel, uint8_t* kvk, uint8_t* kvv, const int* pos,
+                     const int* kslot, const int* act, void* ws, int n_seq, int is_swa, void* stream);
+
 /* Decode attention for callers that cannot hand the library a scratch buffer.  (This entry point has
  * no counterpart in the reference, whose host always owns a `part` allocation.)
  *

@@ -243,3 +243,53 @@ def test_consecutive_appending_decodes_on_one_cache_without_a_sync(name):
     assert eng.device_status() == 0
     assert torch.equal(_bits(oa), _bits(ob))
     assert torch.equal(ka, kb) and torch.equal(va, vb)
+
+
+@pytest.mark.parametrize("name,is_swa", [("B32", False), ("B32", True), ("R", False), ("R", True)])
+def test_qkv_decode_equals_prologue_then_decode(name, is_swa):
+    """battn_qkv_decode (the decode kernel runs the QKV prologue of its row) against battn_qkv_prep followed by
+    battn_decode -- both pinned to the reference's own kernels and to the oracle by other tests -- on two copies of a
+    cache stepped side by side: equal output bits every step, equal cache bytes at the end."""
+    window = 256
+    lens = [0, 1, 63, 64, 65, 300, 2 * window - 2, 1500]
+    n_seq, steps = len(lens), 8
+    g = _geom(name, slot_ctx=2048, n_slots=n_seq + 1, window=window)
+    eng = _engine(g, True)
+    dev = eng.device
+    HD = g.head_dim
+    ka, va = eng.alloc_kv_layer(is_swa, fill=0x7F)
+    slots = [1, 0, 3, 2, 5, 4, 8, 6]
+    for i, n in enumerate(lens):
+        if n:
+            _, k, v = draw_qkv(g, n, 1, 1700 + i)
+            gpu_fill(eng, k, v, ka, va, is_swa, slot=slots[i])
+    torch.cuda.synchronize()
+    kb, vb = ka.clone(), va.clone()
+    part = eng.alloc_part(n_seq, 1)
+    kslot = dev_i32(slots, dev)
+    rng = np.random.default_rng(31)
+    sqk = torch.from_numpy((8.0 + rng.standard_normal((g.n_head, HD))).astype(np.float32)).to(dev)
+    cs = torch.zeros((n_seq, HD), device=dev)
+    sn = torch.zeros((n_seq, HD), device=dev)
+    theta = 2 if is_swa else 1
+    for s in range(steps):
+        act_np = (rng.random(n_seq) < 0.8).astype(np.int32)
+        act_np[s % n_seq] = 0
+        q = torch.from_numpy(rng.standard_normal((n_seq, 1, g.n_head, HD), dtype=np.float32)).to(dev)
+        k = torch.from_numpy(rng.standard_normal((n_seq, 1, g.n_kv, HD), dtype=np.float32)).to(dev)
+        v = torch.from_numpy(rng.standard_normal((n_seq, 1, g.n_kv, HD), dtype=np.float32)).to(dev)
+        pos, act = dev_i32(lens, dev), dev_i32(act_np, dev)
+        eng.rope_tables(cs, sn, pos, rows=1)
+        qp = torch.zeros((n_seq, 1, g.n_head, HD), dtype=eng.q_torch, device=dev)
+        oa = new_out(eng, n_seq, g.n_head, HD)
+        ob = new_out(eng, n_seq, g.n_head, HD)
+        eng.qkv_prep(qp, q, k, v, sqk, cs, sn, ka, va, pos, kslot=kslot, act=act, rows=1, is_swa=is_swa, theta_sel=theta)
+        eng.launch_attn_ms(oa, qp, ka, va, pos, kslot, act, part, n_seq, is_swa=is_swa)
+        eng.qkv_decode(ob, q, k, v, sqk, cs, sn, kb, vb, pos, part, kslot=kslot, act=act, is_swa=is_swa, theta_sel=theta)
+        torch.cuda.synchronize()
+        assert eng.device_status() == 0
+        assert torch.equal(_bits(oa), _bits(ob)), f"step {s}: outputs differ"
+        live = torch.from_numpy(act_np.astype(bool)).to(dev)
+        assert not torch.isnan(ob[live].float()).any() and torch.isnan(ob[~live].float()).all()
+        lens = [n + int(a) for n, a in zip(lens, act_np)]
+    assert torch.equal(ka, kb) and torch.equal(va, vb)
