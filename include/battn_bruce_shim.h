@@ -102,6 +102,23 @@ static inline void launch_attn_m(float* out, const float* q, const uint8_t* kvk,
     else                                       BATTN_CK(battn_prefill(g_battn, out, q, kvk, kvv, pos, part, rows, is_swa, st));
 }
 
+/* The decode step's pair of launches -- k_qkv_prep_fast then launch_attn_m with rows == 1 (bruce.cu:7671-7675, :7729)
+ * or k_qkv_prep_fast_ms then launch_attn_ms (:7667, :7720) -- as ONE call: the decode kernel prepares q, prepares and
+ * appends the K/V row and attends.  Same cache bytes and outputs; q is left as it was (the prepared q is not stored). */
+static inline void qkv_prep_attn_m1(float* out, const float* q, const float* k, const float* v, const float* sqk,
+                                    uint8_t* kvk, uint8_t* kvv, const int* pos, float* part, int is_swa, int theta_sel,
+                                    const float* cs, const float* sn, cudaStream_t st) {
+    BATTN_CK(battn_qkv_decode(g_battn, out, q, k, v, sqk, cs, sn, theta_sel, kvk, kvv, pos, nullptr, nullptr, part, 1,
+                              is_swa, st));
+}
+static inline void qkv_prep_attn_ms(float* out, const float* q, const float* k, const float* v, const float* sqk,
+                                    uint8_t* kvk_layer, uint8_t* kvv_layer, const int* pos, const int* kslot,
+                                    const int* act, float* part, int rows, int is_swa, int theta_sel, const float* cs,
+                                    const float* sn, cudaStream_t st) {
+    BATTN_CK(battn_qkv_decode(g_battn, out, q, k, v, sqk, cs, sn, theta_sel, kvk_layer, kvv_layer, pos, kslot, act, part,
+                              rows, is_swa, st));
+}
+
 /* launch_attn_ms (bruce.cu:4158; call :7720) with the merge folded in */
 static inline void launch_attn_ms(float* out, const float* q, const uint8_t* kvk, const uint8_t* kvv,
                                   const int* pos, const int* kslot, const int* act, float* part, int rows,

@@ -1,6 +1,7 @@
 """A whole serving step captured ONCE into a CUDA graph and replayed at new positions, as the reference
 does (bruce.cu:7877-7900, 8223-8241): RoPE tables -> fused QKV prologue + append -> multi-slot decode
-attention on a full-causal and a sliding-window layer, then the device-side position increment.  Positions,
+attention on a full-causal and a sliding-window layer (as three launches per layer, or as the one call whose decode
+kernel runs prologue and append itself), then the device-side position increment.  Positions,
 slot map and activity flags live in device memory, so the same graph serves every token; no call allocates,
 synchronises or reads on the host.  Every replayed step is checked against the oracle stepping alongside."""
 import numpy as np
@@ -14,7 +15,8 @@ from tests.util import assert_close, oracle_geom
 pytestmark = pytest.mark.gpu
 
 
-def test_decode_step_graph_replays_at_new_positions():
+@pytest.mark.parametrize("fused", [False, True])
+def test_decode_step_graph_replays_at_new_positions(fused):
     from bruce_engine_b200.engine import AttnEngine
     from bruce_engine_b200.layout import G_B
     n_seq, steps = 4, 7
@@ -59,6 +61,10 @@ def test_decode_step_graph_replays_at_new_positions():
     def step():
         eng.rope_tables(cs, sn, pos_d, rows=1)
         for L in layers:
+            if fused:       # prologue, append and attention by the decode kernel itself (battn_qkv_decode)
+                eng.qkv_decode(L["out"], q_in, k_in, v_in, sqk_d, cs, sn, L["kvk"], L["kvv"], pos_d, L["part"], kslot=slot_d,
+                               act=act_d, is_swa=L["is_swa"], theta_sel=L["theta"])
+                continue
             eng.qkv_prep(L["q16"], q_in, k_in, v_in, sqk_d, cs, sn, L["kvk"], L["kvv"], pos_d, kslot=slot_d, act=act_d,
                          rows=1, is_swa=L["is_swa"], theta_sel=L["theta"])
             eng.launch_attn_ms(L["out"], L["q16"], L["kvk"], L["kvv"], pos_d, slot_d, act_d, L["part"], n_seq, L["is_swa"])
@@ -102,7 +108,8 @@ def test_decode_step_graph_replays_at_new_positions():
         for L in layers:
             q_want = O.qkv_prep(og, q, k, v, sqk, tables_c, tables_s, L["okvk"], L["okvv"], pos, kslot=kslot, act=act,
                                 rows=1, is_swa=L["is_swa"], theta_sel=L["theta"])
-            assert (L["q16"].cpu().numpy().view(np.uint16) == q_want.astype(np.float16).view(np.uint16)).all()
+            if not fused:
+                assert (L["q16"].cpu().numpy().view(np.uint16) == q_want.astype(np.float16).view(np.uint16)).all()
             assert (L["kvk"].cpu().numpy() == L["okvk"]).all() and (L["kvv"].cpu().numpy() == L["okvv"]).all(), \
                 f"cache bytes differ at step {t}"
             want = O.attend(og, q_want.astype(np.float16).astype(np.float32), L["okvk"], L["okvv"], pos, kslot=kslot,
@@ -113,4 +120,4 @@ def test_decode_step_graph_replays_at_new_positions():
         pos = pos + act
         assert (pos_d.cpu().numpy() == pos).all()
     assert eng.device_status() == 0
-    assert per_step == 1 + 2 * 3, "one table kernel, then prologue + flash-decode + merge per layer"
+    assert per_step == 1 + 2 * (2 if fused else 3), "one table kernel, then (prologue +) flash-decode + merge per layer"
