@@ -67,6 +67,7 @@ SIGNATURES = {
     "battn_qkv_prep_paged": (_I, [_P] * 8 + [_I, _PG] + [_P] * 3 + [_I, _I, _P]),
     "battn_decode_paged": (_I, [_P, _P, _P, _PG] + [_P] * 4 + [_I, _P]),
     "battn_decode_append_paged": (_I, [_P] * 5 + [_PG] + [_P] * 4 + [_I, _P]),
+    "battn_qkv_decode_paged": (_I, [_P] * 8 + [_I] + [_PG] + [_P] * 4 + [_I, _P]),
     "battn_verify_paged": (_I, [_P, _P, _P, _PG] + [_P] * 4 + [_I, _I, _P]),
     "battn_prefill_paged": (_I, [_P, _P, _P, _PG, _I, _P, _P, _I, _P]),
     "battn_attend_exact_paged": (_I, [_P, _P, _P, _PG] + [_P] * 4 + [_I, _I, _I, _P]),

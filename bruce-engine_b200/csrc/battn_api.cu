@@ -819,6 +819,21 @@ int battn_decode_append_paged(battn_handle* h, void* out, const void* q, const f
                         (cudaStream_t)stream, nullptr, nullptr, 0, &pv, k, v);
 }
 
+int battn_qkv_decode_paged(battn_handle* h, void* out, const float* q, const float* k, const float* v, const float* sqk,
+                           const float* cs, const float* sn, int theta_sel, const battn_pages* pages, const int* pos,
+                           const int* ktab, const int* act, void* ws, int n_seq, void* stream) {
+    PagedView pv;
+    int rc = paged_view(pages, pv);
+    if (rc) return rc;
+    rc = check_seq_args(h, out, q, pages->pool_k, pages->pool_v, pos, ktab, n_seq, 1, 1);
+    if (rc) return rc;
+    if (!ws || ((uintptr_t)ws & 15) || !k || !v || !sqk || !cs || !sn || (theta_sel != 1 && theta_sel != 2)) return BATTN_ERR_ARG;
+    if ((((uintptr_t)k | (uintptr_t)v | (uintptr_t)sqk | (uintptr_t)cs | (uintptr_t)sn) & 15) != 0) return BATTN_ERR_ARG;
+    PrologueIn pro{q, sqk, cs, sn, theta_sel == 2 ? h->g.HD / 2 : 0};
+    return launch_flash(h, out, nullptr, q, pages->pool_k, pages->pool_v, pos, ktab, act, ws, n_seq, 1, 0,
+                        (cudaStream_t)stream, nullptr, nullptr, 0, &pv, k, v, &pro);
+}
+
 int battn_verify_paged(battn_handle* h, void* out, const void* q, const battn_pages* pages, const int* pos,
                        const int* ktab, const int* act, void* ws, int rows, int batch, void* stream) {
     PagedView pv;

@@ -169,6 +169,12 @@ class AttnEngine:
                                                 _ptr(ktab), _ptr(act), _ptr(part), pos.numel(), self._stream())
         self._check("battn_decode_append_paged", rc)
 
+    def qkv_decode_paged(self, out, q, k, v, sqk, cs, sn, pages, pos, part, ktab=None, act=None, theta_sel: int = 1):
+        rc = self.lib.battn_qkv_decode_paged(self.h, _ptr(out), _ptr(q), _ptr(k), _ptr(v), _ptr(sqk), _ptr(cs), _ptr(sn),
+                                             int(theta_sel), C.byref(pages), _ptr(pos), _ptr(ktab), _ptr(act), _ptr(part),
+                                             pos.numel(), self._stream())
+        self._check("battn_qkv_decode_paged", rc)
+
     def set_early_kv_stream(self, enable: bool):
         """Whether decode calls stream the cache tiles below their first position before the preceding kernel of
         the stream has finished (battn_set_early_kv_stream; off by default: the host must not let a kernel that

@@ -317,8 +317,8 @@ int battn_pages_pool_bytes(const battn_handle* h, int n_pages, int page_len, siz
 /* Copy on write: the K and V records of physical page from_page copied into to_page (two device-to-device copies on
  * `stream`), for a sequence that is about to append into a page it shares with another one. */
 int battn_pages_copy(battn_handle* h, const battn_pages* pages, int from_page, int to_page, void* stream);
-/* as battn_kv_append / battn_decode / battn_verify / battn_prefill (more than 32 / group rows; one sequence, table row
- * `table_row`) / battn_attend_exact, is_swa = 0 */
+/* as battn_kv_append / battn_decode (battn_decode_append, battn_qkv_decode) / battn_verify / battn_prefill (more than
+ * 32 / group rows; one sequence, table row `table_row`) / battn_attend_exact, is_swa = 0 */
 int battn_kv_append_paged(battn_handle* h, const battn_pages* pages, const float* k, const float* v, const int* pos,
                           const int* ktab, const int* act, int n_seq, int rows_per_seq, void* stream);
 /* as battn_qkv_prep (the whole prologue fused with the append), storing into the pages */
@@ -330,6 +330,9 @@ int battn_decode_paged(battn_handle* h, void* out, const void* q, const battn_pa
 int battn_decode_append_paged(battn_handle* h, void* out, const void* q, const float* k, const float* v,
                               const battn_pages* pages, const int* pos, const int* ktab, const int* act, void* ws,
                               int n_seq, void* stream);
+int battn_qkv_decode_paged(battn_handle* h, void* out, const float* q, const float* k, const float* v, const float* sqk,
+                           const float* cs, const float* sn, int theta_sel, const battn_pages* pages, const int* pos,
+                           const int* ktab, const int* act, void* ws, int n_seq, void* stream);
 int battn_verify_paged(battn_handle* h, void* out, const void* q, const battn_pages* pages, const int* pos,
                        const int* ktab, const int* act, void* ws, int rows, int batch, void* stream);
 int battn_prefill_paged(battn_handle* h, void* out, const void* q, const battn_pages* pages, int table_row,

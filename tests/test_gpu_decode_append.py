@@ -293,3 +293,49 @@ def test_qkv_decode_equals_prologue_then_decode(name, is_swa):
         assert not torch.isnan(ob[live].float()).any() and torch.isnan(ob[~live].float()).all()
         lens = [n + int(a) for n, a in zip(lens, act_np)]
     assert torch.equal(ka, kb) and torch.equal(va, vb)
+
+
+def test_qkv_decode_paged():
+    """The fused decode step over a paged cache against battn_qkv_prep_paged + battn_decode_paged."""
+    page_len, lens = 128, [0, 127, 128, 300, 900]
+    n_seq, steps, max_pages = len(lens), 6, 8
+    g = _geom("B32", slot_ctx=page_len * max_pages, n_slots=n_seq)
+    eng = _engine(g, True)
+    dev, HD = eng.device, g.head_dim
+    rng = np.random.default_rng(41)
+    n_pages = n_seq * max_pages + 2
+    table = torch.from_numpy(rng.permutation(n_pages)[:n_seq * max_pages].reshape(n_seq, max_pages).astype(np.int32)).to(dev)
+    pa, pak, pav = eng.alloc_pages(n_pages, page_len, table, fill=0x7F)
+    for i, n in enumerate(lens):
+        if n:
+            _, k, v = draw_qkv(g, n, 1, 170 + i)
+            kd, vd = torch.from_numpy(k).to(dev), torch.from_numpy(v).to(dev)
+            for a in range(0, n, 512):
+                b = min(n, a + 512)
+                eng.kv_append_paged(pa, kd[a:b], vd[a:b], dev_i32([a], dev), ktab=dev_i32([i], dev), rows=b - a)
+    torch.cuda.synchronize()
+    pb, pbk, pbv = eng.alloc_pages(n_pages, page_len, table)
+    pbk.copy_(pak)
+    pbv.copy_(pav)
+    part = eng.alloc_part(n_seq, 1)
+    ktab = dev_i32(range(n_seq), dev)
+    sqk = torch.from_numpy((8.0 + rng.standard_normal((g.n_head, HD))).astype(np.float32)).to(dev)
+    cs, sn = torch.zeros((n_seq, HD), device=dev), torch.zeros((n_seq, HD), device=dev)
+    for s in range(steps):
+        act_np = np.ones(n_seq, dtype=np.int32)
+        act_np[s % n_seq] = 0
+        q = torch.from_numpy(rng.standard_normal((n_seq, 1, g.n_head, HD), dtype=np.float32)).to(dev)
+        k = torch.from_numpy(rng.standard_normal((n_seq, 1, g.n_kv, HD), dtype=np.float32)).to(dev)
+        v = torch.from_numpy(rng.standard_normal((n_seq, 1, g.n_kv, HD), dtype=np.float32)).to(dev)
+        pos, act = dev_i32(lens, dev), dev_i32(act_np, dev)
+        eng.rope_tables(cs, sn, pos, rows=1)
+        qp = torch.zeros((n_seq, 1, g.n_head, HD), dtype=eng.q_torch, device=dev)
+        oa, ob = new_out(eng, n_seq, g.n_head, HD), new_out(eng, n_seq, g.n_head, HD)
+        eng.qkv_prep_paged(qp, q, k, v, sqk, cs, sn, pa, pos, ktab=ktab, act=act, rows=1)
+        eng.attn_paged(oa, qp, pa, pos, part, rows=1, ktab=ktab, act=act)
+        eng.qkv_decode_paged(ob, q, k, v, sqk, cs, sn, pb, pos, part, ktab=ktab, act=act)
+        torch.cuda.synchronize()
+        assert eng.device_status() == 0
+        assert torch.equal(_bits(oa), _bits(ob)), f"step {s}: outputs differ"
+        lens = [n + int(a) for n, a in zip(lens, act_np)]
+    assert torch.equal(pak, pbk) and torch.equal(pav, pbv)
